@@ -1,0 +1,158 @@
+"""Compiles the CUDA sources of this folder into one shared library for sm_100a.
+
+`nvcc -gencode arch=compute_100a,code=sm_100a` on every `.cu` file here, one
+object per file (in parallel), linked into `_build/libimp_b200-<hash>.so` next
+to the sources; the hash covers the sources, the headers and the flags, so an
+edited file rebuilds and an unchanged tree loads at once.  When the source
+tree cannot be written (an installed, read-only copy), the library goes to
+`$IMP_B200_BUILD_DIR` or a per-user folder under the system's temporary
+directory.  Progress goes to stderr, one line per file.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import List, Optional
+
+CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "--expt-relaxed-constexpr",
+]
+LINK_FLAGS = ["-shared", "-Xcompiler", "-fPIC"]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _log(msg: str) -> None:
+    print(f"[imp_b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    cands = []
+    for var in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(var):
+            cands.append(os.path.join(os.environ[var], "bin", "nvcc"))
+    w = shutil.which("nvcc")
+    if w:
+        cands.append(w)
+    cands.append("/usr/local/cuda/bin/nvcc")
+    for c in cands:
+        if os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("nvcc not found (looked at $CUDA_HOME/bin, PATH and /usr/local/cuda/bin); "
+                     "the CUDA kernels cannot be compiled")
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+
+
+def headers() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+
+
+def source_hash() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS + LINK_FLAGS).encode())
+    for f in sources() + headers():
+        h.update(f.encode())
+        with open(os.path.join(CSRC_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def _writable_dir(path: str) -> bool:
+    try:
+        os.makedirs(path, exist_ok=True)
+        probe = os.path.join(path, f".probe-{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return True
+    except OSError:
+        return False
+
+
+def build_dir() -> str:
+    env = os.environ.get("IMP_B200_BUILD_DIR")
+    if env:
+        if not _writable_dir(env):
+            raise BuildError(f"IMP_B200_BUILD_DIR={env} cannot be written")
+        return env
+    local = os.path.join(CSRC_DIR, "_build")
+    if _writable_dir(local):
+        return local
+    fallback = os.path.join(tempfile.gettempdir(), f"imp_b200-build-{os.getuid()}")
+    if _writable_dir(fallback):
+        return fallback
+    raise BuildError(f"neither {local} nor {fallback} can be written; set IMP_B200_BUILD_DIR")
+
+
+def library_path(create: bool = True) -> str:
+    return os.path.join(build_dir(), f"libimp_b200-{source_hash()}.so")
+
+
+def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> None:
+    cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    t0 = time.time()
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    if p.returncode != 0:
+        raise BuildError(f"nvcc failed on {src}:\n{p.stdout}\n{p.stderr}")
+    _log(f"compiled {src} in {time.time() - t0:.1f}s")
+    if verbose and p.stderr:
+        sys.stderr.write(p.stderr)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Build (if needed) and return the path of the shared library."""
+    out = library_path()
+    if os.path.exists(out) and not force:
+        return out
+    nvcc = find_nvcc()
+    bdir = build_dir()
+    tag = source_hash()
+    objdir = os.path.join(bdir, f"obj-{tag}-{os.getpid()}")
+    os.makedirs(objdir, exist_ok=True)
+    srcs = sources()
+    _log(f"compiling {len(srcs)} CUDA files for sm_100a with {nvcc} (first use; this takes a minute)")
+    objs = [os.path.join(objdir, s[:-3] + ".o") for s in srcs]
+    try:
+        with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+            futs = [ex.submit(_compile_one, nvcc, s, o, verbose) for s, o in zip(srcs, objs)]
+            for f in futs:
+                f.result()
+        tmp = out + f".tmp-{os.getpid()}"
+        p = subprocess.run([nvcc, *LINK_FLAGS, "-o", tmp, *objs], capture_output=True, text=True)
+        if p.returncode != 0:
+            raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
+        os.replace(tmp, out)  # atomic: concurrent builders race benignly
+        _log(f"linked {os.path.basename(out)}")
+    finally:
+        shutil.rmtree(objdir, ignore_errors=True)
+    # Drop libraries of older source states.
+    for f in os.listdir(bdir):
+        if f.startswith("libimp_b200-") and f.endswith(".so") and os.path.join(bdir, f) != out:
+            try:
+                os.remove(os.path.join(bdir, f))
+            except OSError:
+                pass
+    return out
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,110 @@
+// Shared helpers of the sm_100a kernels: element types, loads/stores through
+// float, block reductions with a fixed order, and the device status word.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define IMP_API extern "C" __attribute__((visibility("default")))
+
+// Element type codes used across the C ABI.
+enum ImpDType : int { IMP_F32 = 0, IMP_BF16 = 1 };
+
+// Codes written to the device status word (first error wins; 0 = ok).
+enum ImpStatus : int {
+    IMP_OK = 0,
+    IMP_BAD_TOKEN_ID = 1,      // embedding: id outside [0, vocab)
+    IMP_BAD_PAGE = 2,          // cache write / attention: page id outside the pool
+    IMP_BAD_POSITION = 3,      // position outside the rotary table or the block table
+    IMP_BAD_SEQUENCE = 4,      // token names a sequence outside the batch
+    IMP_WAIT_TIMEOUT = 5,      // a bounded device-side wait ran out
+};
+
+// Host-side error codes returned by launchers (negative = argument errors, positive = cudaError_t).
+#define IMP_ERR_ARG (-1)
+#define IMP_ERR_UNSUPPORTED (-2)
+
+void imp_set_error(const char* fmt, ...);
+
+#define IMP_CHECK_ARG(cond, ...)            \
+    do {                                    \
+        if (!(cond)) {                      \
+            imp_set_error(__VA_ARGS__);     \
+            return IMP_ERR_ARG;             \
+        }                                   \
+    } while (0)
+
+#define IMP_RETURN_LAUNCH()                                            \
+    do {                                                               \
+        cudaError_t e__ = cudaGetLastError();                          \
+        if (e__ != cudaSuccess) {                                      \
+            imp_set_error("%s: %s", __func__, cudaGetErrorString(e__)); \
+            return (int)e__;                                           \
+        }                                                              \
+        return 0;                                                      \
+    } while (0)
+
+__device__ __forceinline__ void imp_report(int* status, int code) {
+    if (status) atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// Load element i of a buffer whose element type is only known at run time.
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+    return dtype == IMP_F32 ? reinterpret_cast<const float*>(p)[i]
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; every thread gets the result.  The order of additions is
+// fixed by blockDim alone, so a row reduces the same way in every batch.
+// `scratch` holds at least 33 floats.  blockDim.x must be a multiple of 32.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

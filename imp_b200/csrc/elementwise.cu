@@ -1,0 +1,97 @@
+// Embedding gather, SwiGLU and dtype casts.
+//
+// Reference counterparts: embedding_lookup_* (src/compute/embedding.cu:15-112),
+// swiglu_* (src/compute/activation.cu:15-87).  Differences: the gather writes
+// the 32-bit residual stream directly, the activation uses the IEEE expf
+// (the reference compiles __expf under --use_fast_math), and both take any
+// width.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                 const int* __restrict__ ids, int d, int vocab, float scale,
+                                 int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (int64_t)t * d;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) imp_report(status, IMP_BAD_TOKEN_ID);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const TW* row = table + (int64_t)id * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]) * scale;
+}
+
+// out[t, :] = table[ids[t], :] * scale, as 32-bit floats.
+IMP_API int imp_embedding(float* out, const void* table, const int* ids, int n_tokens, int d, int vocab,
+                          int table_dtype, float scale, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(out && table && ids && d > 0 && vocab > 0, "imp_embedding: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = d >= 1024 ? 256 : 128;
+    if (table_dtype == IMP_F32)
+        embedding_kernel<float><<<n_tokens, block, 0, s>>>(out, (const float*)table, ids, d, vocab, scale, status);
+    else
+        embedding_kernel<__nv_bfloat16><<<n_tokens, block, 0, s>>>(out, (const __nv_bfloat16*)table, ids, d,
+                                                                  vocab, scale, status);
+    IMP_RETURN_LAUNCH();
+}
+
+// ------------------------------------------------------------------- swiglu
+// out[t, f] = silu(gu[t, f]) * gu[t, F + f]; the activation is computed in 32-bit.
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_tokens, int F) {
+    const int64_t total = n_tokens * (int64_t)F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / F;
+        const int f = (int)(i - t * F);
+        const float g = to_float(gu[t * 2 * F + f]);
+        const float u = to_float(gu[t * 2 * F + F + f]);
+        const float a = g / (1.f + expf(-g));
+        out[i] = from_float<T>(a * u);
+    }
+}
+
+IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(out && gate_up && F > 0, "imp_swiglu: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)n_tokens * F;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block < 148 * 16 ? (total + block - 1) / block : 148 * 16);
+    if (dtype == IMP_F32)
+        swiglu_kernel<float><<<grid, block, 0, s>>>((float*)out, (const float*)gate_up, n_tokens, F);
+    else
+        swiglu_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
+                                                             n_tokens, F);
+    IMP_RETURN_LAUNCH();
+}
+
+// --------------------------------------------------------------------- cast
+template <typename TS, typename TD>
+__global__ void cast_kernel(TD* __restrict__ dst, const TS* __restrict__ src, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = from_float<TD>(to_float(src[i]));
+}
+
+IMP_API int imp_cast(void* dst, int dst_dtype, const void* src, int src_dtype, int64_t n, void* stream) {
+    if (n == 0) return 0;
+    IMP_CHECK_ARG(dst && src, "imp_cast: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = 256;
+    const int64_t want = (n + block - 1) / block;
+    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (src_dtype == IMP_F32 && dst_dtype == IMP_BF16)
+        cast_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>((__nv_bfloat16*)dst, (const float*)src, n);
+    else if (src_dtype == IMP_BF16 && dst_dtype == IMP_F32)
+        cast_kernel<__nv_bfloat16, float><<<grid, block, 0, s>>>((float*)dst, (const __nv_bfloat16*)src, n);
+    else if (src_dtype == IMP_F32 && dst_dtype == IMP_F32)
+        cast_kernel<float, float><<<grid, block, 0, s>>>((float*)dst, (const float*)src, n);
+    else
+        cast_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>((__nv_bfloat16*)dst,
+                                                                       (const __nv_bfloat16*)src, n);
+    IMP_RETURN_LAUNCH();
+}

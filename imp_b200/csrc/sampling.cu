@@ -1,0 +1,257 @@
+// Token selection from 32-bit logits: argmax, repetition/frequency/presence
+// penalties, and temperature sampling with min-p, top-k and top-p filters.
+//
+// Reference counterparts (src/compute/sampling.cu): argmax with the lowest
+// index winning ties (:29-84), penalties (:700-736: divide positive / multiply
+// negative logits of seen tokens by the repetition penalty, subtract
+// frequency*count and presence), min-p as a cut at max + log(min_p) on the raw
+// logits (:767-810), and topk_topp_sample_kernel (:253-557): softmax of
+// logits/T over the whole vocabulary, the k most probable, the shortest prefix
+// of them whose probability reaches top_p, renormalise, one uniform draw.
+// Differences: one block per row for any number of rows at once; k is not
+// capped at 128 (selection is a bitwise search over ordered keys instead of
+// per-thread heaps); ties at a cut are kept; the uniform number is an input
+// (the reference re-seeds an LCG with the same seed on every call, :541-543,
+// which draws the same number at every step); the draw walks the kept tokens in
+// index order.  Every reduction has a fixed order, so a row's result does not
+// depend on the other rows.
+#include "common.cuh"
+
+constexpr int SAMPLE_BLOCK = 1024;
+
+__device__ __forceinline__ unsigned ordered_key(float f) {
+    const unsigned b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ int block_sum_int(int v, int* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        int t = lane < nwarp ? scratch[lane] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// ------------------------------------------------------------------- argmax
+__device__ __forceinline__ void argmax_row(const float* __restrict__ x, int V, float* s_val, int* s_idx,
+                                           float& best_v, int& best_i) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = x[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < nwarp ? s_val[lane] : -INFINITY;
+        bi = lane < nwarp ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { s_val[32] = bv; s_idx[32] = bi; }
+    }
+    __syncthreads();
+    best_v = s_val[32];
+    best_i = s_idx[32];
+}
+
+__global__ void __launch_bounds__(SAMPLE_BLOCK) argmax_kernel(const float* __restrict__ logits, int64_t ld, int V,
+                                                             int* __restrict__ out) {
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    float bv;
+    int bi;
+    argmax_row(logits + (int64_t)blockIdx.x * ld, V, s_val, s_idx, bv, bi);
+    if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+IMP_API int imp_argmax(const float* logits, int64_t ld, int n_rows, int V, int* out, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(logits && out && V > 0 && ld >= V, "imp_argmax: bad argument");
+    argmax_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, out);
+    IMP_RETURN_LAUNCH();
+}
+
+// ---------------------------------------------------------------- penalties
+// counts: [n_rows, V] int32 scratch, zeroed here.  history: tokens of all rows back to back,
+// row r owning history[hist_start[r] .. hist_start[r+1]).
+__global__ void count_history_kernel(int* __restrict__ counts, const int* __restrict__ history,
+                                     const int* __restrict__ hist_start, int V) {
+    const int r = blockIdx.y;
+    const int b = hist_start[r], e = hist_start[r + 1];
+    for (int i = b + blockIdx.x * blockDim.x + threadIdx.x; i < e; i += gridDim.x * blockDim.x) {
+        const int tok = history[i];
+        if (tok >= 0 && tok < V) atomicAdd(&counts[(int64_t)r * V + tok], 1);
+    }
+}
+
+__global__ void apply_penalties_kernel(float* __restrict__ logits, int64_t ld, const int* __restrict__ counts,
+                                       int V, const float* __restrict__ rep, const float* __restrict__ freq,
+                                       const float* __restrict__ pres) {
+    const int r = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= V) return;
+    const int c = counts[(int64_t)r * V + i];
+    if (c == 0) return;
+    float x = logits[(int64_t)r * ld + i];
+    const float rp = rep[r];
+    if (rp != 1.f) x = x > 0.f ? x / rp : x * rp;
+    x -= freq[r] * (float)c;
+    x -= pres[r];
+    logits[(int64_t)r * ld + i] = x;
+}
+
+IMP_API int imp_apply_penalties(float* logits, int64_t ld, int n_rows, int V, const int* history,
+                                const int* hist_start, int max_hist, const float* rep, const float* freq,
+                                const float* pres, int* counts_scratch, void* stream) {
+    if (n_rows == 0 || max_hist == 0) return 0;
+    IMP_CHECK_ARG(logits && history && hist_start && rep && freq && pres && counts_scratch,
+                  "imp_apply_penalties: null pointer");
+    IMP_CHECK_ARG(n_rows <= 65535, "imp_apply_penalties: too many rows");
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(counts_scratch, 0, (size_t)n_rows * V * sizeof(int), s);
+    if (e != cudaSuccess) { imp_set_error("imp_apply_penalties: %s", cudaGetErrorString(e)); return (int)e; }
+    const int gx = (max_hist + 255) / 256;
+    count_history_kernel<<<dim3(gx, n_rows), 256, 0, s>>>(counts_scratch, history, hist_start, V);
+    apply_penalties_kernel<<<dim3((V + 255) / 256, n_rows), 256, 0, s>>>(logits, ld, counts_scratch, V, rep, freq, pres);
+    IMP_RETURN_LAUNCH();
+}
+
+// ------------------------------------------------------------------- sample
+// Per row r: temperature[r] <= 0 or top_k[r] == 1 -> argmax.  Otherwise:
+//   keep i with logit_i >= max + log(min_p)           (min_p > 0)
+//   x_i = logit_i / T, e_i = exp(x_i - max x) over kept i, Z = sum e_i
+//   keep the top_k largest x_i (ties with the k-th kept)  (0 < top_k < V)
+//   keep the most probable tokens until their e-mass reaches top_p * Z (ties kept)  (0 < top_p < 1)
+//   draw: target = u * mass(kept); the first kept i, in index order, whose running mass exceeds target.
+__global__ void __launch_bounds__(SAMPLE_BLOCK) sample_kernel(
+    const float* __restrict__ logits, int64_t ld, int V, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+    const float* __restrict__ uniform, int* __restrict__ out) {
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    __shared__ float scratch[33];
+    __shared__ int iscratch[33];
+    __shared__ float part[SAMPLE_BLOCK];
+    __shared__ int s_pick;
+
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (int64_t)r * ld;
+    float max_logit;
+    int arg;
+    argmax_row(x, V, s_val, s_idx, max_logit, arg);
+    const float T = temperature[r];
+    const int k = top_k[r];
+    if (T <= 0.f || k == 1 || arg == 0x7fffffff) {
+        if (tid == 0) out[r] = (arg == 0x7fffffff) ? 0 : arg;
+        return;
+    }
+    const float inv_T = 1.f / T;
+    const float mp = min_p[r];
+    const float floor_logit = mp > 0.f ? max_logit + logf(mp) : -INFINITY;
+    const float xmax = max_logit * inv_T;
+#define KEPT0(i) (x[i] >= floor_logit)
+#define EVAL(i) expf(x[i] * inv_T - xmax)
+
+    float z = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_BLOCK)
+        if (KEPT0(i)) z += EVAL(i);
+    z = block_sum(z, scratch);
+
+    unsigned tau = 0u;  // keep keys >= tau
+    if (k > 0 && k < V) {
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned cand = tau | (1u << bit);
+            int c = 0;
+            for (int i = tid; i < V; i += SAMPLE_BLOCK)
+                if (KEPT0(i) && ordered_key(x[i]) >= cand) ++c;
+            c = block_sum_int(c, iscratch);
+            if (c >= k) tau = cand;
+        }
+    }
+    const float tp = top_p[r];
+    if (tp > 0.f && tp < 1.f) {
+        const float want = tp * z;
+        unsigned tau_p = 0u;
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned cand = tau_p | (1u << bit);
+            float mass = 0.f;
+            for (int i = tid; i < V; i += SAMPLE_BLOCK)
+                if (KEPT0(i) && ordered_key(x[i]) >= cand) mass += EVAL(i);
+            mass = block_sum(mass, scratch);
+            if (mass >= want) tau_p = cand;
+        }
+        if (tau_p > tau) tau = tau_p;
+    }
+
+    // Draw in index order: thread t owns the contiguous range [t*chunk, (t+1)*chunk).
+    const int chunk = (V + SAMPLE_BLOCK - 1) / SAMPLE_BLOCK;
+    const int lo = tid * chunk, hi = min(V, lo + chunk);
+    float mine = 0.f;
+    for (int i = lo; i < hi; ++i)
+        if (KEPT0(i) && ordered_key(x[i]) >= tau) mine += EVAL(i);
+    part[tid] = mine;
+    if (tid == 0) s_pick = -1;
+    __syncthreads();
+    if (tid == 0) {
+        float run = 0.f;
+        for (int t = 0; t < SAMPLE_BLOCK; ++t) {
+            const float v = part[t];
+            part[t] = run;  // exclusive prefix
+            run += v;
+        }
+        scratch[0] = run;
+    }
+    __syncthreads();
+    const float total = scratch[0];
+    const float target = uniform[r] * total;
+    const float before = part[tid];
+    if (mine > 0.f && before <= target && target < before + mine) {
+        float run = before;
+        int pick = -1, last = -1;
+        for (int i = lo; i < hi; ++i) {
+            if (KEPT0(i) && ordered_key(x[i]) >= tau) {
+                run += EVAL(i);
+                last = i;
+                if (run > target) { pick = i; break; }
+            }
+        }
+        s_pick = pick >= 0 ? pick : last;
+    }
+    __syncthreads();
+    if (tid == 0) out[r] = s_pick >= 0 ? s_pick : arg;  // rounding left no owner: the most probable token
+#undef KEPT0
+#undef EVAL
+}
+
+IMP_API int imp_sample(const float* logits, int64_t ld, int n_rows, int V, const float* temperature,
+                       const int* top_k, const float* top_p, const float* min_p, const float* uniform, int* out,
+                       void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(logits && temperature && top_k && top_p && min_p && uniform && out && V > 0 && ld >= V,
+                  "imp_sample: bad argument");
+    sample_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, top_k, top_p, min_p,
+                                                                    uniform, out);
+    IMP_RETURN_LAUNCH();
+}

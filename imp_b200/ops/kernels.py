@@ -1,0 +1,275 @@
+"""Tensor-level wrappers of the CUDA entry points.
+
+Each function checks shapes and dtypes, then launches on torch's current
+stream.  Nothing here computes with torch: tensors are only memory.  Element
+types are bfloat16 or float32; `linear` picks the matrix kernel by the weight's
+type and the number of rows.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import library as L
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+# Rows up to which the weight-streaming kernel is used for bfloat16 products; above it the
+# library GEMM (cuBLAS through torch.mm) runs, as the reference does for its T>1 products
+# (src/compute/gemm.cu:303-445).
+SMALL_M_MAX = 16
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise L.KernelError(f"unsupported element type {t.dtype} (bfloat16 or float32)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise L.KernelError("kernel arguments must be CUDA tensors (no CPU path exists)")
+
+
+def new_status(device) -> torch.Tensor:
+    """The device status word kernels report bad indices to (0 = ok)."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, what: str = "step") -> None:
+    """Read the status word (synchronises) and raise if a kernel reported a bad index."""
+    code = int(status.item())
+    if code != 0:
+        status.zero_()
+        raise L.KernelError(f"{what}: device reported '{L.load().imp_status_string(code).decode()}' (code {code})")
+
+
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0,
+              status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(out, table, ids)
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    assert table.dim() == 2 and table.shape[1] == d and table.is_contiguous()
+    assert ids.dtype == torch.int32 and ids.numel() == T and ids.is_contiguous()
+    lib = L.load()
+    L.check(lib.imp_embedding(out.data_ptr(), table.data_ptr(), ids.data_ptr(), T, d, table.shape[0], _dt(table),
+                              float(scale), _ptr(status), _stream()), "embedding")
+    return out
+
+
+def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    _need_cuda(out, gate_up)
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.dtype == out.dtype
+    assert out.is_contiguous() and gate_up.is_contiguous()
+    L.check(L.load().imp_swiglu(out.data_ptr(), gate_up.data_ptr(), T, F, _dt(out), _stream()), "swiglu")
+    return out
+
+
+def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    _need_cuda(dst, src)
+    assert dst.numel() == src.numel() and dst.is_contiguous() and src.is_contiguous()
+    L.check(L.load().imp_cast(dst.data_ptr(), _dt(dst), src.data_ptr(), _dt(src), src.numel(), _stream()), "cast")
+    return dst
+
+
+def add_rmsnorm(h: torch.Tensor, branch: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, weight_offset: float = 0.0, rows: Optional[torch.Tensor] = None,
+                write_h: bool = True) -> torch.Tensor:
+    """h (+= branch); out = rmsnorm(h) * (weight + offset).  With `rows`, output row r reads stream row rows[r]
+    and h is left untouched."""
+    _need_cuda(h, branch, weight, out, rows)
+    d = h.shape[1]
+    assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous() and out.shape[1] == d
+    assert weight.numel() == d and weight.is_contiguous()
+    if branch is not None:
+        assert branch.shape == h.shape and branch.dtype == out.dtype and branch.is_contiguous()
+    n_out = out.shape[0]
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n_out and rows.is_contiguous()
+        write_h = False
+    else:
+        assert n_out == h.shape[0]
+    L.check(L.load().imp_add_rmsnorm(h.data_ptr(), _ptr(branch), weight.data_ptr(), out.data_ptr(), _ptr(rows),
+                                     n_out, d, float(eps), float(weight_offset), _dt(out), _dt(weight),
+                                     1 if write_h else 0, _stream()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+                 weight_offset: float = 0.0) -> torch.Tensor:
+    """Row-wise RMSNorm of a 2-D tensor whose rows may be strided."""
+    _need_cuda(x, weight, out)
+    n, d = x.shape
+    assert out.shape == x.shape and out.dtype == x.dtype and x.stride(1) == 1 and out.stride(1) == 1
+    assert weight.numel() == d and weight.is_contiguous()
+    L.check(L.load().imp_rmsnorm_rows(x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0),
+                                      n, d, float(eps), float(weight_offset), _dt(x), _dt(weight), _stream()),
+            "rmsnorm_rows")
+    return out
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                          q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int,
+                          positions: torch.Tensor, seq_of_token: Optional[torch.Tensor],
+                          block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], status: Optional[torch.Tensor] = None,
+                          weight_offset: float = 0.0) -> None:
+    _need_cuda(qkv, q_norm_w, k_norm_w, cos, sin, positions, seq_of_token, block_table, k_cache, v_cache)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] >= (n_q_heads + 2 * n_kv_heads) * head_dim
+    assert positions.dtype == torch.int32 and positions.numel() == T
+    w_dtype = _dt(q_norm_w) if q_norm_w is not None else F32
+    if q_norm_w is not None:
+        assert q_norm_w.numel() == head_dim and k_norm_w.numel() == head_dim and k_norm_w.dtype == q_norm_w.dtype
+    max_pos = 0
+    if cos is not None:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape
+        assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] * 2 == rot_dim
+        max_pos = cos.shape[0]
+    bt_stride = n_seqs = page_size = num_pages = 0
+    if k_cache is not None:
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape
+        num_pages, hk, page_size, dh = k_cache.shape
+        assert hk == n_kv_heads and dh == head_dim
+        assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1
+        assert seq_of_token.dtype == torch.int32 and seq_of_token.numel() == T
+        n_seqs, bt_stride = block_table.shape[0], block_table.stride(0)
+    L.check(L.load().imp_qk_norm_rope_kv_write(
+        qkv.data_ptr(), qkv.stride(0), T, n_q_heads, n_kv_heads, head_dim,
+        _ptr(q_norm_w), _ptr(k_norm_w), float(eps), float(weight_offset), w_dtype,
+        _ptr(cos), _ptr(sin), int(rot_dim), max_pos,
+        positions.data_ptr(), _ptr(seq_of_token), _ptr(block_table), bt_stride, n_seqs,
+        _ptr(k_cache), _ptr(v_cache), page_size, num_pages, _dt(qkv), _ptr(status), _stream()),
+        "qk_norm_rope_kv_write")
+
+
+def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                            k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0,
+                            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(out, q, k_cache, v_cache, block_table, seq_of_token, positions)
+    T = q.shape[0]
+    assert out.shape[0] == T and out.stride(1) == 1 and q.stride(1) == 1 and out.dtype == q.dtype
+    assert k_cache.dtype == q.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and v_cache.shape == k_cache.shape
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    assert seq_of_token.dtype == torch.int32 and positions.dtype == torch.int32
+    L.check(L.load().imp_paged_attention_generic(
+        out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
+        block_table.shape[0], n_q_heads, n_kv_heads, head_dim, page_size, num_pages, float(scale), int(window),
+        _dt(q), _ptr(status), _stream()), "paged_attention_generic")
+    return out
+
+
+def gemm_f32(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ w[N,K]^T, true 32-bit."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.dtype == w.dtype == out.dtype == torch.float32
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    L.check(L.load().imp_gemm_f32(out.data_ptr(), out.stride(0), a.data_ptr(), a.stride(0), w.data_ptr(),
+                                  w.stride(0), M, N, K, _stream()), "gemm_f32")
+    return out
+
+
+def gemm_bf16_small_m(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.dtype == w.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    L.check(L.load().imp_gemm_bf16_small_m(out.data_ptr(), out.stride(0), _dt(out), a.data_ptr(), a.stride(0),
+                                           w.data_ptr(), w.stride(0), M, N, K, _stream()), "gemm_bf16_small_m")
+    return out
+
+
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
+
+    float32 x float32 -> the plain FFMA kernel (never a reduced-precision mode).
+    bfloat16 x bfloat16 -> the weight-streaming kernel for few rows, else the library GEMM.
+    bfloat16 x float32 weight (a tensor the checkpoint stores in 32-bit) -> x is widened, FFMA kernel.
+    `out` may be bfloat16 or float32.
+    """
+    M = x.shape[0]
+    if M == 0:
+        return out
+    if w.dtype == torch.float32:
+        xf = x if x.dtype == torch.float32 else cast(torch.empty(x.shape, dtype=torch.float32, device=x.device),
+                                                     x.contiguous())
+        if out.dtype == torch.float32:
+            return gemm_f32(out, xf, w)
+        tmp = gemm_f32(torch.empty(out.shape, dtype=torch.float32, device=x.device), xf, w)
+        if out.is_contiguous():
+            return cast(out, tmp)
+        out.copy_(tmp)
+        return out
+    if x.dtype != torch.bfloat16:
+        raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
+    if M <= SMALL_M_MAX:
+        return gemm_bf16_small_m(out, x, w)
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    else:
+        out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(logits, out)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if out is None:
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    L.check(L.load().imp_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, history: torch.Tensor, hist_start: torch.Tensor, max_hist: int,
+                    rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor, counts: torch.Tensor) -> None:
+    _need_cuda(logits, history, hist_start, rep, freq, pres, counts)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert history.dtype == torch.int32 and hist_start.dtype == torch.int32 and hist_start.numel() == R + 1
+    assert counts.dtype == torch.int32 and counts.numel() >= R * V and counts.is_contiguous()
+    for t in (rep, freq, pres):
+        assert t.dtype == torch.float32 and t.numel() == R
+    L.check(L.load().imp_apply_penalties(logits.data_ptr(), logits.stride(0), R, V, history.data_ptr(),
+                                         hist_start.data_ptr(), int(max_hist), rep.data_ptr(), freq.data_ptr(),
+                                         pres.data_ptr(), counts.data_ptr(), _stream()), "apply_penalties")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(logits, temperature, top_k, top_p, min_p, uniform, out)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert top_k.dtype == torch.int32
+    for t in (temperature, top_p, min_p, uniform):
+        assert t.dtype == torch.float32 and t.numel() == R
+    if out is None:
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    L.check(L.load().imp_sample(logits.data_ptr(), logits.stride(0), R, V, temperature.data_ptr(), top_k.data_ptr(),
+                                top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(), out.data_ptr(), _stream()),
+            "sample")
+    return out
