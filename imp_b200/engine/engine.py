@@ -1,0 +1,192 @@
+"""The Python entry point: load or make a model, then generate.
+
+In the reference's manner (include/imp/imp.h:34-143): a model handle, a
+context with engine settings, `generate` for whole requests, and the token
+level pair prefill / decode-step, here as `submit` + `step`.  Requests are
+lists of token ids (this engine has no tokenizer).
+
+    from imp_b200 import Engine, EngineConfig, GenerateParams
+    eng = Engine.from_folder("model_dir", EngineConfig(compute_dtype="bfloat16"))
+    outs = eng.generate([[1, 2, 3]], GenerateParams(max_tokens=16, temperature=0.0))
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from ..config.model_config import ModelConfig
+from ..sampling.sampler import Sampler, SamplingParams
+from .loading import load_model, make_cache, random_model
+from .model import DecoderModel
+from .scheduler import Request, RequestStatus, Scheduler, StepPlan
+from .step import StepEntry, Stepper
+
+
+@dataclass
+class GenerateParams:
+    """Per-request generation settings; fields and defaults of the reference's
+    ImpGenerateParams (include/imp/imp.h:61-85, src/api/imp_api.cpp:76-102) that apply here."""
+
+    temperature: float = 0.7
+    top_p: float = 0.9
+    top_k: int = 40
+    max_tokens: int = 256
+    seed: int = -1
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    repeat_last_n: int = 0
+    ignore_eos: bool = False
+
+    def sampling(self) -> SamplingParams:
+        return SamplingParams(temperature=self.temperature, top_p=self.top_p, top_k=self.top_k, min_p=self.min_p,
+                              repetition_penalty=self.repetition_penalty, frequency_penalty=self.frequency_penalty,
+                              presence_penalty=self.presence_penalty, repeat_last_n=self.repeat_last_n,
+                              seed=self.seed)
+
+
+@dataclass
+class StepOutput:
+    rid: Hashable
+    token: int
+    finished: bool
+    status: RequestStatus
+
+
+class Engine:
+    """Model + cache + step function + scheduler + sampler on one GPU."""
+
+    def __init__(self, model: DecoderModel, model_config: ModelConfig, config: Optional[EngineConfig] = None):
+        self.config = config or EngineConfig()
+        self.config.validate()
+        self.model = model
+        self.model_config = model_config
+        cfg = self.config
+        rt = model.rt
+        if cfg.compute_dtype not in ("bfloat16", "float32") or \
+                (cfg.compute_dtype == "float32") != (rt.dtype == torch.float32):
+            raise ValueError(f"engine compute_dtype {cfg.compute_dtype} does not match the model's {rt.dtype}")
+        self.max_seq_len = min(cfg.max_seq_len, model.plan.max_positions)
+        num_pages = self._decide_pages()
+        slots = cfg.state_slots or cfg.max_batch_size
+        self.cache: CacheManager = make_cache(model, cfg.kv_block_size, num_pages, slots)
+        self.stepper = Stepper(model, self.cache, rt, cfg.max_batch_tokens, cfg.max_batch_size, self.max_seq_len)
+        self.scheduler = Scheduler(self.cache, cfg.max_batch_size, cfg.max_batch_tokens, cfg.prefill_chunk_size,
+                                   self.max_seq_len)
+        self.sampler = Sampler(model.vocab_size, cfg.max_batch_size, rt.device)
+        self._ids = itertools.count()
+        eos = model_config.eos_token_id
+        self.eos_token_ids: Tuple[int, ...] = () if eos is None else (int(eos),)
+
+    # ------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir: str, config: Optional[EngineConfig] = None) -> "Engine":
+        config = config or EngineConfig()
+        mc, model = load_model(model_dir, config.compute_dtype, f"cuda:{config.device_id}")
+        return cls(model, mc, config)
+
+    @classmethod
+    def from_random(cls, model_config: ModelConfig, config: Optional[EngineConfig] = None, seed: int = 0,
+                    std: float = 0.02) -> "Engine":
+        config = config or EngineConfig()
+        model = random_model(model_config, seed, std, dtype=config.compute_dtype,
+                             device=f"cuda:{config.device_id}")
+        return cls(model, model_config, config)
+
+    def _decide_pages(self) -> int:
+        """Pages per cache group: explicit, or from a token count, or from free memory
+        (the reference gives 80% of free memory, clamped to 1-2x the configured worst case:
+        src/runtime/engine.cpp:226-243; an explicit block count wins, :531-535)."""
+        cfg = self.config
+        P = cfg.kv_block_size
+        if cfg.kv_cache_max_blocks > 0:
+            return cfg.kv_cache_max_blocks
+        if cfg.kv_cache_tokens > 0:
+            return (cfg.kv_cache_tokens + P - 1) // P
+        worst = ((self.max_seq_len + P - 1) // P) * cfg.max_batch_size
+        probe = CacheManager(self.model.cache_specs, P, 1, 1)
+        per_page = max(1, probe.storage_bytes(torch.empty((), dtype=self.model.rt.dtype).element_size()))
+        free, _ = torch.cuda.mem_get_info(self.model.rt.device)
+        by_memory = int(free * cfg.gpu_memory_fraction) // per_page
+        return max(1, min(worst, by_memory))
+
+    # ---------------------------------------------------------------- requests
+    def submit(self, prompt: Sequence[int], params: Optional[GenerateParams] = None,
+               rid: Optional[Hashable] = None) -> Request:
+        """Queue one request; returns its handle (check `.status` for OUT_OF_MEMORY)."""
+        params = params or GenerateParams()
+        V = self.model.vocab_size
+        for t in prompt:
+            if not 0 <= int(t) < V:
+                raise ValueError(f"token id {t} outside the vocabulary of {V}")
+        req = Request(rid=next(self._ids) if rid is None else rid, prompt=[int(t) for t in prompt],
+                      max_tokens=params.max_tokens, params=params.sampling(), eos_token_ids=self.eos_token_ids,
+                      ignore_eos=params.ignore_eos)
+        return self.scheduler.add(req)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[StepOutput]:
+        """One engine step: schedule, run the batch, sample, finish.  Returns the new tokens."""
+        plan = self.scheduler.schedule()
+        outs = [StepOutput(r.rid, -1, True, r.status) for r in plan.failed]
+        if not plan.entries:
+            return outs
+        entries, rows = [], []
+        for e in plan.entries:
+            toks = e.request.all_tokens()[e.start:e.start + e.n_tokens]
+            entries.append(StepEntry(e.request.rid, toks, [e.n_tokens - 1] if e.samples else []))
+            if e.samples:
+                rows.append(e.request)
+        logits = self.stepper.step(entries)
+        sampled: Dict[Hashable, int] = {}
+        if rows:
+            toks = self.sampler.sample(logits, [r.params for r in rows], [r.seed for r in rows],
+                                       [len(r.output) for r in rows], [r.all_tokens() for r in rows]
+                                       if any(r.params.has_penalties() for r in rows) else None)
+            sampled = {r.rid: t for r, t in zip(rows, toks)}
+        self.stepper.check_device_status()
+        finished = set(id(r) for r in self.scheduler.complete_step(plan, sampled))
+        for r in rows:
+            outs.append(StepOutput(r.rid, sampled[r.rid], id(r) in finished, r.status))
+        return outs
+
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
+        """Generate for every prompt (continuous batching inside); returns the new tokens per prompt.
+
+        `params` is one GenerateParams for all prompts or a list with one per prompt.
+        """
+        if prompts and isinstance(prompts[0], int):
+            raise TypeError("generate takes a list of prompts (each a list of token ids)")
+        plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        reqs = [self.submit(p, q) for p, q in zip(prompts, plist)]
+        for r in reqs:
+            if r.status == RequestStatus.OUT_OF_MEMORY:
+                raise MemoryError(f"request {r.rid!r}: prompt plus max_tokens needs more cache pages than the "
+                                  f"pool of {self.cache.num_pages} holds")
+        while any(not r.done for r in reqs):
+            self.step()
+        failed = [r for r in reqs if r.status != RequestStatus.FINISHED]
+        if failed:
+            raise MemoryError(f"{len(failed)} request(s) ran out of cache pages: "
+                              f"{[r.rid for r in failed]}")
+        return [list(r.output) for r in reqs]
+
+    # ------------------------------------------------------------- token level
+    def step_tokens(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run given tokens as one batch (no scheduling, no sampling); logits of the wanted rows on the host."""
+        logits = self.stepper.step(entries)
+        out = logits.cpu()
+        self.stepper.check_device_status()
+        return out
+
+    def end(self, rid: Hashable) -> None:
+        """Give back what a `step_tokens` request holds."""
+        self.stepper.finish(rid)
