@@ -155,7 +155,7 @@ def greedy_generate(w, cfg, prompt, n_new):
     out = []
     for _ in range(n_new):
         logits = forward(w, cfg, ids)[-1]
-        tok = int(torch.argmax(logits))  # torch.argmax returns the first maximal index
+        tok = int((logits == logits.max()).nonzero()[0])  # the lowest index among equal maxima
         out.append(tok)
         ids.append(tok)
     return out
