@@ -76,7 +76,8 @@ class Engine:
         num_pages = self._decide_pages()
         slots = cfg.state_slots or cfg.max_batch_size
         self.cache: CacheManager = make_cache(model, cfg.kv_block_size, num_pages, slots)
-        self.stepper = Stepper(model, self.cache, rt, cfg.max_batch_tokens, cfg.max_batch_size, self.max_seq_len)
+        self.stepper = Stepper(model, self.cache, rt, cfg.max_batch_tokens, cfg.max_batch_size, self.max_seq_len,
+                               use_cuda_graphs=cfg.enable_cuda_graphs)
         self.scheduler = Scheduler(self.cache, cfg.max_batch_size, cfg.max_batch_tokens, cfg.prefill_chunk_size,
                                    self.max_seq_len)
         self.sampler = Sampler(model.vocab_size, cfg.max_batch_size, rt.device)

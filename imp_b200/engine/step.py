@@ -96,8 +96,11 @@ class Stepper:
     """Owns the batch buffers and runs steps of a model against a cache manager."""
 
     def __init__(self, model: DecoderModel, cache: CacheManager, rt: Runtime, max_tokens: int, max_seqs: int,
-                 max_seq_len: int):
+                 max_seq_len: int, use_cuda_graphs: bool = False):
         self.model, self.cache, self.rt = model, cache, rt
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graphs = {}        # batch size -> (graph, static logits)
+        self._graph_uses = {}    # batch size -> eager runs so far
         self.max_tokens, self.max_seqs, self.max_seq_len = max_tokens, max_seqs, max_seq_len
         self.max_pages = (max_seq_len + cache.page_size - 1) // cache.page_size
         self.buffers = BatchBuffers(max_tokens, max_seqs, self.max_pages, len(cache.paged), rt.device)
@@ -223,9 +226,35 @@ class Stepper:
         """Run one batch.  Returns float32 logits [wanted rows, vocab] on the device, in the
         order of the entries and of each entry's `want`."""
         ctx = self.prepare(entries)
-        logits = self.model.forward(ctx)
+        if self.use_cuda_graphs and ctx.decode_only and ctx.n_rows == ctx.n_seqs:
+            logits = self._forward_decode_graph(ctx)
+        else:
+            logits = self.model.forward(ctx)
         self.commit(ctx)
         return logits
+
+    def _forward_decode_graph(self, ctx: StepContext) -> torch.Tensor:
+        """Decode-only batches of a given size replay one captured CUDA graph.
+
+        The batch arrays live at fixed addresses, so a graph captured for B sequences serves
+        every later step of B sequences; only the arrays' contents change.  The first step of a
+        size runs eagerly (it also warms the library GEMM up), the second is captured.
+        The returned logits are the graph's own buffer: read them before the next step.
+        """
+        B = ctx.n_seqs
+        hit = self._graphs.get(B)
+        if hit is None:
+            uses = self._graph_uses.get(B, 0)
+            self._graph_uses[B] = uses + 1
+            if uses == 0:
+                return self.model.forward(ctx)
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.current_stream().synchronize()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx)
+            hit = self._graphs[B] = (graph, static_logits)
+        hit[0].replay()
+        return hit[1]
 
     def finish(self, rid: Hashable) -> None:
         """The request is over: its pages and its slot go back."""

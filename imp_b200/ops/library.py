@@ -118,7 +118,12 @@ def require_device() -> None:
     _arch_checked = True
 
 
+launch_calls = 0   # launcher calls made through `check` (each enqueues at least one kernel of this library)
+
+
 def check(rc: int, what: str) -> None:
+    global launch_calls
+    launch_calls += 1
     if rc != 0:
         msg = load().imp_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed ({rc}): {msg}")
