@@ -16,6 +16,7 @@ import shutil
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
@@ -76,7 +77,7 @@ def source_hash() -> str:
 def _writable_dir(path: str) -> bool:
     try:
         os.makedirs(path, exist_ok=True)
-        probe = os.path.join(path, f".probe-{os.getpid()}")
+        probe = os.path.join(path, f".probe-{os.getpid()}-{threading.get_ident()}")
         with open(probe, "w"):
             pass
         os.remove(probe)
@@ -85,7 +86,17 @@ def _writable_dir(path: str) -> bool:
         return False
 
 
+_build_dir_cache = {}
+
+
 def build_dir() -> str:
+    key = os.environ.get("IMP_B200_BUILD_DIR", "")
+    if key not in _build_dir_cache:
+        _build_dir_cache[key] = _find_build_dir()
+    return _build_dir_cache[key]
+
+
+def _find_build_dir() -> str:
     env = os.environ.get("IMP_B200_BUILD_DIR")
     if env:
         if not _writable_dir(env):
@@ -154,5 +165,71 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return out
 
 
+# ---------------------------------------------------------------------------
+# Variant libraries: one source compiled with given macro values (e.g. the attention
+# kernels per head size).  Built on first use of that variant, cached like the base library.
+# ---------------------------------------------------------------------------
+VARIANT_DIR = os.path.join(CSRC_DIR, "variants")
+
+
+def variant_hash(source: str, defines: dict) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS + LINK_FLAGS).encode())
+    h.update(repr(sorted(defines.items())).encode())
+    for path in [os.path.join(VARIANT_DIR, source)] + [os.path.join(CSRC_DIR, f) for f in headers()]:
+        with open(path, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def build_variant(source: str, defines: dict, force: bool = False, verbose: bool = False) -> str:
+    """Compile variants/<source> with -D<key>=<value> into its own shared library; returns its path."""
+    tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
+    stem = os.path.splitext(source)[0]
+    bdir = build_dir()
+    out = os.path.join(bdir, f"libimp_{stem}_{tag}-{variant_hash(source, defines)}.so")
+    if os.path.exists(out) and not force:
+        return out
+    nvcc = find_nvcc()
+    _log(f"compiling {source} for {tag} (first use)")
+    t0 = time.time()
+    tmp = out + f".tmp-{os.getpid()}"
+    # error reporting lives in the base library's runtime.cu; a variant carries its own copy
+    cmd = [nvcc, *NVCC_FLAGS, *LINK_FLAGS, "-I", CSRC_DIR, *[f"-D{k}={v}" for k, v in sorted(defines.items())],
+           os.path.join(VARIANT_DIR, source), os.path.join(CSRC_DIR, "runtime.cu"), "-o", tmp]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    if p.returncode != 0:
+        raise BuildError(f"nvcc failed on {source} ({tag}):\n{p.stdout}\n{p.stderr}")
+    os.replace(tmp, out)
+    _log(f"built {os.path.basename(out)} in {time.time() - t0:.1f}s")
+    if verbose and p.stderr:
+        sys.stderr.write(p.stderr)
+    prefix = f"libimp_{stem}_{tag}-"
+    for f in os.listdir(bdir):
+        if f.startswith(prefix) and f.endswith(".so") and os.path.join(bdir, f) != out:
+            try:
+                os.remove(os.path.join(bdir, f))
+            except OSError:
+                pass
+    return out
+
+
+ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))
+
+
+def build_all(force: bool = False) -> List[str]:
+    """The base library and the attention variant of every supported head size."""
+    paths = [build(force)]
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        futs = [ex.submit(build_variant, "attention_mma.cu", {"IMP_ATTN_DH": dh}, force) for dh in ATTENTION_HEAD_DIMS]
+        paths += [f.result() for f in futs]
+    return paths
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--all" in sys.argv:
+        print("\n".join(build_all(force="--force" in sys.argv)))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

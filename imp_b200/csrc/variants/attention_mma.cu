@@ -1,0 +1,532 @@
+// Paged flash attention on warp-level tensor-core MMAs (bfloat16 in, 32-bit softmax and
+// accumulation), compiled once per head size: -DIMP_ATTN_DH=<multiple of 16, at most 256>.
+//
+// Two entry points over the same inner loop:
+//   decode : one query token per sequence.  A CTA owns (token, kv head, split of the keys); its
+//            16-row tile holds the query heads that share the kv head, so every key and value
+//            byte is read once per group.  Splits write unnormalised partial results to scratch
+//            and a second kernel merges them.  Launch shape depends on the batch size only and
+//            key ranges are read from device memory, so a captured graph serves any context.
+//   prefill: a warp owns 16 consecutive query tokens of one sequence and one query head; it walks
+//            the cached keys from the window's start to its last token's position.
+// Keys and values are read straight from the pages into MMA fragments with 16-byte loads (no
+// shared-memory staging): the contraction index of each product is permuted so that what a lane
+// loads contiguously is what its fragment needs.  For S = Q K^T the head dimension is permuted
+// (the same permutation on Q's fragments), for O = P V the value columns are permuted and
+// un-permuted when the result is written.
+//
+// Math as in the reference's kernels (src/compute/attention.cu:158-216 prefill,
+// src/compute/attention_paged.cu:904-1195 split-K decode + reduce): s = scale * q.k, causal and
+// window masks, running max and sum, o = sum p v; the reference's kernels are half-precision
+// WMMA / CUDA-core code over the call's own K,V (prefill) or one query per sequence (decode).
+#include "../common.cuh"
+
+#ifndef IMP_ATTN_DH
+#error "compile with -DIMP_ATTN_DH=<head size>"
+#endif
+
+constexpr int DH = IMP_ATTN_DH;
+static_assert(DH % 16 == 0 && DH >= 16 && DH <= 256, "head size must be a multiple of 16 in [16, 256]");
+constexpr int KSTEPS = DH / 16;       // k-steps of the QK^T product
+constexpr int NTILES = DH / 8;        // 8-wide output tiles of the PV product
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Dimension permutation of the QK^T contraction.  The head dimension is cut into blocks of 32
+// (plus one block of 16 when DH % 32 == 16).  In a 32-block, lane t (= lane & 3) loads the 8
+// contiguous elements [8t, 8t+8) of a row; k-step s (0 or 1) of the block takes elements
+// 4s..4s+3 of them as (k=2t,2t+1) and (k=2t+8,2t+9).  In a 16-block lane t loads [4t, 4t+4).
+template <typename Row>
+__device__ __forceinline__ void load_row_frags(uint32_t (&f)[KSTEPS][2], const Row* __restrict__ row, int t) {
+#pragma unroll
+    for (int b = 0; b < DH / 32; ++b) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row + b * 32 + 8 * t);
+        f[2 * b][0] = v.x; f[2 * b][1] = v.y; f[2 * b + 1][0] = v.z; f[2 * b + 1][1] = v.w;
+    }
+    if (DH % 32) {
+        const uint2 v = *reinterpret_cast<const uint2*>(row + (DH / 32) * 32 + 4 * t);
+        f[KSTEPS - 1][0] = v.x; f[KSTEPS - 1][1] = v.y;
+    }
+}
+
+// Value columns are cut into blocks of 64, then 32, then 16.  In a block of NT tiles (NT = 8, 4, 2)
+// lane g (= lane >> 2) loads the NT contiguous elements [NT*g, NT*g + NT) of a value row; element i
+// is column g of output tile i.  So accumulator (tile i, column c) of the block holds dimension
+// base + NT*c + i.
+struct VBlocks {
+    static constexpr int N64 = DH / 64;
+    static constexpr int HAS32 = (DH % 64) >= 32;
+    static constexpr int HAS16 = (DH % 32) == 16;
+};
+
+// One row of the tile as this lane sees it.
+struct RowInfo {
+    int limit;   // last key position the row may see (its own position); -1 = row unused
+    int first;   // first key position (window), 0 without a window
+};
+
+struct TileState {
+    float o[NTILES][4];   // [tile][c0,c1 (row g), c2,c3 (row g+8)]
+    float m[2], l[2];     // running max (log2 domain) and lane-partial sum for rows g and g+8
+};
+
+__device__ __forceinline__ void tile_init(TileState& s) {
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i) { s.o[i][0] = s.o[i][1] = s.o[i][2] = s.o[i][3] = 0.f; }
+    s.m[0] = s.m[1] = -INFINITY;
+    s.l[0] = s.l[1] = 0.f;
+}
+
+// Row offset (in elements) of key j of kv head hk in a layer's cache.  j is first brought into
+// [j_min, j_max], the keys some row of the tile can see: keys outside are masked anyway, and their
+// pages may already have gone back to the pool.  A bad page id is reported and replaced by page 0.
+__device__ __forceinline__ int64_t key_row_offset(int j, int j_min, int j_max, const int* __restrict__ bt, int P,
+                                                  int Hkv, int hk, int num_pages, int* status) {
+    j = max(j_min, min(j, j_max));
+    const int lp = j / P;
+    int page = bt[lp];
+    if (page < 0 || page >= num_pages) {
+        imp_report(status, IMP_BAD_PAGE);
+        page = 0;
+    }
+    return (((int64_t)page * Hkv + hk) * P + (j - lp * P)) * DH;
+}
+
+// Process the 16 keys j0 .. j0+15 (those beyond j_max are masked) for a 16-row tile.
+__device__ __forceinline__ void process_step(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
+                                             const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                                             const int* __restrict__ bt, int P, int Hkv, int hk, int num_pages,
+                                             int j0, int j_min, int j_max, float scale_log2, int lane, int* status) {
+    const int g = lane >> 2, t = lane & 3;
+    // Lanes 0..15 look up the row of key j0 + lane; the others copy what they need.
+    const int64_t my_off = key_row_offset(j0 + (lane & 15), j_min, j_max, bt, P, Hkv, hk, num_pages, status);
+    const int64_t k_off0 = __shfl_sync(0xffffffffu, my_off, g);
+    const int64_t k_off1 = __shfl_sync(0xffffffffu, my_off, g + 8);
+    const int64_t v_off[4] = {__shfl_sync(0xffffffffu, my_off, 2 * t), __shfl_sync(0xffffffffu, my_off, 2 * t + 1),
+                              __shfl_sync(0xffffffffu, my_off, 2 * t + 8), __shfl_sync(0xffffffffu, my_off, 2 * t + 9)};
+
+    // ---- S = Q K^T for two 8-key tiles -------------------------------------------------------
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+        uint32_t kb[KSTEPS][2];
+        load_row_frags(kb, kc + k_off0, t);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) mma_16816(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][0], kb[ks][1]);
+        load_row_frags(kb, kc + k_off1, t);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) mma_16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][0], kb[ks][1]);
+    }
+    // ---- mask, running max, probabilities -------------------------------------------------------
+    float p[2][4];
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {          // r = 0: row g (c0,c1); r = 1: row g+8 (c2,c3)
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j0 + 8 * nt + 2 * t + e;
+                float v = s[nt][2 * r + e] * scale_log2;
+                if (j > rows[r].limit || j < rows[r].first) v = -INFINITY;
+                s[nt][2 * r + e] = v;
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m[r], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // a row with nothing to see yet
+        corr[r] = exp2f(st.m[r] - m_use);                          // st.m = -inf -> 0
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float pv = exp2f(s[nt][2 * r + e] - m_use);
+                p[nt][2 * r + e] = pv;
+                sum += pv;
+            }
+        st.l[r] = st.l[r] * corr[r] + sum;
+        st.m[r] = m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i) {
+        st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+        st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+    }
+    const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);   // row g,   keys 2t, 2t+1
+    const uint32_t pa1 = pack_bf16(p[0][2], p[0][3]);   // row g+8, keys 2t, 2t+1
+    const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);   // row g,   keys 2t+8, 2t+9
+    const uint32_t pa3 = pack_bf16(p[1][2], p[1][3]);   // row g+8, keys 2t+8, 2t+9
+
+    // ---- O += P V -----------------------------------------------------------------------------
+    int tile = 0;
+#pragma unroll
+    for (int b = 0; b < VBlocks::N64; ++b) {
+        uint4 r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint4*>(vc + v_off[k] + b * 64 + 8 * g);
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            const uint32_t b0 = __byte_perm(w0[i >> 1], w1[i >> 1], sel);
+            const uint32_t b1 = __byte_perm(w2[i >> 1], w3[i >> 1], sel);
+            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, b0, b1);
+        }
+        tile += 8;
+    }
+    if (VBlocks::HAS32) {
+        const int base = VBlocks::N64 * 64;
+        uint2 r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint2*>(vc + v_off[k] + base + 4 * g);
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                      __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+        }
+        tile += 4;
+    }
+    if (VBlocks::HAS16) {
+        const int base = VBlocks::N64 * 64 + VBlocks::HAS32 * 32;
+        uint32_t r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint32_t*>(vc + v_off[k] + base + 2 * g);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(r[0], r[1], sel), __byte_perm(r[2], r[3], sel));
+        }
+    }
+}
+
+// Dimension held by accumulator (tile, column c) -- the inverse of the value-column permutation.
+__device__ __forceinline__ int dim_of(int tile, int c) {
+    if (tile < VBlocks::N64 * 8) return (tile >> 3) * 64 + 8 * c + (tile & 7);
+    tile -= VBlocks::N64 * 8;
+    int base = VBlocks::N64 * 64;
+    if (VBlocks::HAS32) {
+        if (tile < 4) return base + 4 * c + tile;
+        tile -= 4;
+        base += 32;
+    }
+    return base + 2 * c + tile;
+}
+
+// Query fragments of rows g and g+8 (null pointer = unused row -> zeros).
+__device__ __forceinline__ void load_q(uint32_t (&qa)[KSTEPS][4], const __nv_bfloat16* q0, const __nv_bfloat16* q1, int t) {
+    uint32_t f0[KSTEPS][2], f1[KSTEPS][2];
+    if (q0) load_row_frags(f0, q0, t);
+    if (q1) load_row_frags(f1, q1, t);
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        qa[ks][0] = q0 ? f0[ks][0] : 0u;   // row g,   k = 2t, 2t+1
+        qa[ks][1] = q1 ? f1[ks][0] : 0u;   // row g+8, k = 2t, 2t+1
+        qa[ks][2] = q0 ? f0[ks][1] : 0u;   // row g,   k = 2t+8, 2t+9
+        qa[ks][3] = q1 ? f1[ks][1] : 0u;   // row g+8
+    }
+}
+
+// ================================================================================== decode
+// grid (n_splits, Hkv * tiles_per_group, n_tokens), block 128.
+// part_o: [n_tokens, Hq, n_splits, DH] float, part_ml: [n_tokens, Hq, n_splits, 2] float (used when n_splits > 1).
+__global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
+    __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
+    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
+    int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
+    float* __restrict__ part_ml, int* status) {
+    extern __shared__ float smem[];   // (WARPS-1) x (NTILES*4 + 4) x 32 floats
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int G = Hq / Hkv;
+    const int tiles_per_group = (G + 15) / 16;
+    const int split = blockIdx.x;
+    const int hk = blockIdx.y / tiles_per_group;
+    const int row0 = (blockIdx.y % tiles_per_group) * 16;   // first head of the group in this tile
+    const int tok = blockIdx.z;
+    const int seq = seq_of_token[tok];
+    const int pos = positions[tok];
+    if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride) {
+        if (threadIdx.x == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        return;
+    }
+    const int* bt = block_table + (int64_t)seq * bt_stride;
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first16 = first & ~15;
+    const int total_steps = (pos - first16) / 16 + 1;
+    const int per_split = (total_steps + n_splits - 1) / n_splits;
+    const int step_lo = split * per_split;
+    const int step_hi = min(total_steps, step_lo + per_split);
+
+    RowInfo rows[2];
+    const __nv_bfloat16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int hr = row0 + g + 8 * r;
+        const bool used = hr < G;
+        rows[r].limit = used ? pos : -1;
+        rows[r].first = first;
+        qrow[r] = used ? q + (int64_t)tok * q_stride + (int64_t)(hk * G + hr) * DH : nullptr;
+    }
+    uint32_t qa[KSTEPS][4];
+    load_q(qa, qrow[0], qrow[1], t4);
+    TileState st;
+    tile_init(st);
+    for (int s = step_lo + warp; s < step_hi; s += WARPS)
+        process_step(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, scale_log2, lane, status);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+    // ---- merge the four warps (fragment-wise, through shared memory) ---------------------------------
+    constexpr int PER_WARP = NTILES * 4 + 4;
+    if (warp > 0) {
+        float* dst = smem + (size_t)(warp - 1) * PER_WARP * 32;
+#pragma unroll
+        for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[(i * 4 + c) * 32 + lane] = st.o[i][c];
+        dst[(NTILES * 4 + 0) * 32 + lane] = st.m[0];
+        dst[(NTILES * 4 + 1) * 32 + lane] = st.m[1];
+        dst[(NTILES * 4 + 2) * 32 + lane] = st.l[0];
+        dst[(NTILES * 4 + 3) * 32 + lane] = st.l[1];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    for (int w = 1; w < WARPS; ++w) {
+        const float* src = smem + (size_t)(w - 1) * PER_WARP * 32;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float mo = src[(NTILES * 4 + r) * 32 + lane];
+            const float lo = src[(NTILES * 4 + 2 + r) * 32 + lane];
+            const float m_new = fmaxf(st.m[r], mo);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float ca = exp2f(st.m[r] - m_use), cb = exp2f(mo - m_use);
+            st.l[r] = st.l[r] * ca + lo * cb;
+            st.m[r] = m_new;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                st.o[i][2 * r] = st.o[i][2 * r] * ca + src[(i * 4 + 2 * r) * 32 + lane] * cb;
+                st.o[i][2 * r + 1] = st.o[i][2 * r + 1] * ca + src[(i * 4 + 2 * r + 1) * 32 + lane] * cb;
+            }
+        }
+    }
+    // ---- write: final output, or this split's partial ---------------------------------------------
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int hr = row0 + g + 8 * r;
+        if (hr >= G) continue;
+        const int head = hk * G + hr;
+        if (n_splits == 1) {
+            const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+            __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                o[dim_of(i, 2 * t4)] = __float2bfloat16_rn(st.o[i][2 * r] * inv);
+                o[dim_of(i, 2 * t4 + 1)] = __float2bfloat16_rn(st.o[i][2 * r + 1] * inv);
+            }
+        } else {
+            const int64_t slot = ((int64_t)tok * Hq + head) * n_splits + split;
+            float* o = part_o + slot * DH;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                o[dim_of(i, 2 * t4)] = st.o[i][2 * r];
+                o[dim_of(i, 2 * t4 + 1)] = st.o[i][2 * r + 1];
+            }
+            if (t4 == 0) {
+                part_ml[slot * 2] = st.m[r];
+                part_ml[slot * 2 + 1] = st.l[r];
+            }
+        }
+    }
+}
+
+// One warp per (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+__global__ void attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t out_stride, const float* __restrict__ part_o,
+                                  const float* __restrict__ part_ml, int n_tokens, int Hq, int n_splits) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_tokens * Hq) return;
+    const int tok = unit / Hq, head = unit - tok * Hq;
+    const float* ml = part_ml + (int64_t)unit * n_splits * 2;
+    const float* po = part_o + (int64_t)unit * n_splits * DH;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+    constexpr int PER_LANE = (DH + 31) / 32;
+    float acc[PER_LANE];
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.f;
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float m = ml[2 * s];
+        if (m == -INFINITY) continue;
+        const float w = exp2f(m - M);
+        L += ml[2 * s + 1] * w;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int d = lane + 32 * i;
+            if (d < DH) acc[i] += po[(int64_t)s * DH + d] * w;
+        }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < DH) o[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
+static int check_common(const void* out, const void* q, const void* kc, const void* vc, const int* bt,
+                        int64_t out_stride, int64_t q_stride, int Hq, int Hkv, int P, int num_pages) {
+    IMP_CHECK_ARG(out && q && kc && vc && bt, "attention: null pointer");
+    IMP_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
+    IMP_CHECK_ARG(P > 0 && num_pages > 0, "attention: bad cache geometry");
+    IMP_CHECK_ARG(q_stride % 8 == 0 && out_stride % 2 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)kc % 16 == 0 &&
+                      (uintptr_t)vc % 16 == 0,
+                  "attention: q, k and v rows must start on 16-byte boundaries");
+    IMP_CHECK_ARG((int64_t)num_pages * Hkv * P * DH < ((int64_t)1 << 40), "attention: cache too large");
+    return 0;
+}
+
+IMP_API int imp_attn_head_dim(void) { return DH; }
+
+// Scratch floats needed by imp_attn_decode for n_splits > 1: part_o then part_ml.
+IMP_API int64_t imp_attn_decode_scratch_floats(int n_tokens, int Hq, int n_splits) {
+    return n_splits > 1 ? (int64_t)n_tokens * Hq * n_splits * (DH + 2) : 0;
+}
+
+IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+                            const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                            const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages,
+                            float scale, int window, int n_splits, float* scratch, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
+    IMP_CHECK_ARG(seq_of_token && positions && n_splits >= 1 && n_splits <= 65535, "imp_attn_decode: bad argument");
+    IMP_CHECK_ARG(n_splits == 1 || scratch, "imp_attn_decode: splits need scratch memory");
+    IMP_CHECK_ARG(n_tokens <= 65535, "imp_attn_decode: more than 65535 tokens");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int G = Hq / Hkv;
+    const int tiles_per_group = (G + 15) / 16;
+    const size_t smem = (size_t)(WARPS - 1) * (NTILES * 4 + 4) * 32 * sizeof(float);
+    static bool attr_set = false;
+    if (!attr_set && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (int64_t)n_tokens * Hq * n_splits * DH : nullptr;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(n_splits, Hkv * tiles_per_group, n_tokens);
+    attn_decode_kernel<<<grid, WARPS * 32, smem, s>>>(
+        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages,
+        scale_log2, window, n_splits, part_o, part_ml, status);
+    if (n_splits > 1) {
+        const int units = n_tokens * Hq;
+        attn_merge_kernel<<<(units + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, part_o, part_ml, n_tokens, Hq,
+                                                          n_splits);
+    }
+    IMP_RETURN_LAUNCH();
+}
+
+// ================================================================================= prefill
+// Tiles of up to 16 consecutive query tokens of one sequence: tile_tok0[i] is the first token's
+// index in the batch, tile_rows[i] the number of tokens.  A warp owns (tile, query head);
+// warps are numbered tile-major, head-minor, so a CTA's four warps mostly share a kv head.
+__global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(
+    __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
+    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+    const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv,
+    int P, int num_pages, float scale_log2, int window, int* status) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int64_t unit = (int64_t)blockIdx.x * WARPS + warp;
+    if (unit >= (int64_t)n_tiles * Hq) return;
+    const int tile = (int)(unit / Hq), head = (int)(unit - (int64_t)tile * Hq);
+    const int hk = head / (Hq / Hkv);
+    const int tok0 = tile_tok0[tile], n_rows = tile_rows[tile];
+    const int seq = seq_of_token[tok0];
+    const int pos0 = positions[tok0];
+    const int pos_last = pos0 + n_rows - 1;
+    if (seq < 0 || seq >= n_seqs || pos0 < 0 || pos_last / P >= bt_stride || n_rows < 1 || n_rows > 16) {
+        if (lane == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        return;
+    }
+    const int* bt = block_table + (int64_t)seq * bt_stride;
+    RowInfo rows[2];
+    const __nv_bfloat16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int rr = g + 8 * r;
+        const bool used = rr < n_rows;
+        const int pos = pos0 + rr;
+        rows[r].limit = used ? pos : -1;
+        rows[r].first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        qrow[r] = used ? q + (int64_t)(tok0 + rr) * q_stride + (int64_t)head * DH : nullptr;
+    }
+    uint32_t qa[KSTEPS][4];
+    load_q(qa, qrow[0], qrow[1], t4);
+    TileState st;
+    tile_init(st);
+    const int first_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    for (int j0 = first_tile & ~15; j0 <= pos_last; j0 += 16)
+        process_step(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, j0, first_tile, pos_last, scale_log2, lane, status);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        const int rr = g + 8 * r;
+        if (rr >= n_rows) continue;
+        const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        __nv_bfloat16* o = out + (int64_t)(tok0 + rr) * out_stride + (int64_t)head * DH;
+#pragma unroll
+        for (int i = 0; i < NTILES; ++i) {
+            o[dim_of(i, 2 * t4)] = __float2bfloat16_rn(st.o[i][2 * r] * inv);
+            o[dim_of(i, 2 * t4 + 1)] = __float2bfloat16_rn(st.o[i][2 * r + 1] * inv);
+        }
+    }
+}
+
+IMP_API int imp_attn_prefill(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+                             const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                             const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles,
+                             int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale, int window, int* status,
+                             void* stream) {
+    if (n_tiles == 0) return 0;
+    if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
+    IMP_CHECK_ARG(seq_of_token && positions && tile_tok0 && tile_rows, "imp_attn_prefill: null pointer");
+    const int64_t units = (int64_t)n_tiles * Hq;
+    const int64_t blocks = (units + WARPS - 1) / WARPS;
+    IMP_CHECK_ARG(blocks <= 0x7fffffff, "imp_attn_prefill: too many tiles");
+    attn_prefill_kernel<<<(unsigned)blocks, WARPS * 32, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, n_tiles, n_seqs,
+        Hq, Hkv, P, num_pages, scale * 1.4426950408889634f, window, status);
+    IMP_RETURN_LAUNCH();
+}

@@ -28,6 +28,9 @@ from ..parts.base import Runtime
 from .model import DecoderModel
 
 
+ATTENTION_TILE = 16   # query tokens per attention tile (the row count of one tensor-core tile)
+
+
 @dataclass
 class StepEntry:
     """The next tokens of one request, and which of them should yield logits."""
@@ -42,15 +45,17 @@ class StepContext:
 
     __slots__ = ("n_tokens", "n_seqs", "n_rows", "token_ids", "positions", "seq_of_token", "logit_rows",
                  "q_start", "kv_len", "state_slots", "block_tables", "max_q_len", "max_kv_len", "decode_only",
-                 "q_lens", "starts", "rids", "fresh")
+                 "q_lens", "starts", "rids", "fresh", "tile_tok0", "tile_rows")
 
 
 class BatchBuffers:
     """Persistent device arrays of a batch at fixed addresses, with pinned staging.
 
     Layout in int32 words, by capacity (so a view's address does not depend on the
-    batch): tokens | positions | seq_of_token | logit_rows | q_start | kv_len |
-    slots | one block table [max_seqs, max_pages] per cache group.
+    batch): tokens | positions | seq_of_token | logit_rows | attention tiles (first
+    token, rows) | q_start | kv_len | slots | one block table [max_seqs, max_pages]
+    per cache group.  An attention tile is a run of up to 16 consecutive tokens of
+    one sequence.
     """
 
     def __init__(self, max_tokens: int, max_seqs: int, max_pages: int, n_groups: int, device):
@@ -58,6 +63,7 @@ class BatchBuffers:
         o = 0
         self.off = {}
         for name, n in (("tok", max_tokens), ("pos", max_tokens), ("seq", max_tokens), ("rows", max_tokens),
+                        ("tile0", max_tokens), ("tilen", max_tokens),
                         ("q_start", max_seqs + 1), ("kv_len", max_seqs), ("slots", max_seqs)):
             self.off[name] = o
             o += n
@@ -169,6 +175,8 @@ class Stepper:
         ctx = StepContext()
         t = 0
         rows: List[int] = []
+        tiles0: List[int] = []
+        tilesn: List[int] = []
         q_lens, starts, rids, fresh = [], [], [], []
         max_kv = 0
         for s, e in enumerate(entries):
@@ -190,6 +198,9 @@ class Stepper:
                 row[:len(table)] = table
                 row[len(table):] = -1
             rows.extend(t + int(w) for w in e.want)
+            for a in range(0, n, ATTENTION_TILE):
+                tiles0.append(t + a)
+                tilesn.append(min(ATTENTION_TILE, n - a))
             q_lens.append(n)
             starts.append(start)
             rids.append(e.rid)
@@ -200,6 +211,9 @@ class Stepper:
         host[off["q_start"] + B] = t
         R = len(rows)
         host[off["rows"]: off["rows"] + R] = np.asarray(rows, dtype=np.int32) if R else 0
+        n_tiles = len(tiles0)
+        host[off["tile0"]: off["tile0"] + n_tiles] = np.asarray(tiles0, dtype=np.int32)
+        host[off["tilen"]: off["tilen"] + n_tiles] = np.asarray(tilesn, dtype=np.int32)
         buf.upload(i, B)
 
         d = buf.dev
@@ -208,6 +222,8 @@ class Stepper:
         ctx.positions = d[off["pos"]: off["pos"] + t]
         ctx.seq_of_token = d[off["seq"]: off["seq"] + t]
         ctx.logit_rows = d[off["rows"]: off["rows"] + R]
+        ctx.tile_tok0 = d[off["tile0"]: off["tile0"] + n_tiles]
+        ctx.tile_rows = d[off["tilen"]: off["tilen"] + n_tiles]
         ctx.q_start = d[off["q_start"]: off["q_start"] + B + 1]
         ctx.kv_len = d[off["kv_len"]: off["kv_len"] + B]
         ctx.state_slots = d[off["slots"]: off["slots"] + B]

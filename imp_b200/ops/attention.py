@@ -1,13 +1,117 @@
-"""Choice of the attention kernel for a step.
+"""Choice of the attention kernel for a step, and the per-head-size tensor-core kernels.
 
 float32: always the plain kernel (fixed reduction order per token).
-bfloat16: the plain kernel as well, until a faster kernel covers the case.
+bfloat16: the MMA kernels of csrc/variants/attention_mma.cu, compiled on first use for the model's
+head size: the split-key decode kernel when every sequence brings one token, else the tiled
+prefill kernel (a decode token beside prompt portions is a tile of one row).
 """
 from __future__ import annotations
 
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Dict
+
+import torch
+
 from . import kernels as K
+from . import library as L
+
+_variants: Dict[int, ctypes.CDLL] = {}
+
+# CTAs the decode kernel should reach before it stops splitting the keys further: three resident
+# CTAs of 128 threads per SM (register-bound) on 148 SMs.
+DECODE_TARGET_CTAS = 148 * 3
+DECODE_MAX_SPLITS = 32
+
+
+def variant(head_dim: int) -> ctypes.CDLL:
+    lib = _variants.get(head_dim)
+    if lib is None:
+        from ..csrc.build import ATTENTION_HEAD_DIMS, build_variant
+        if head_dim not in ATTENTION_HEAD_DIMS:
+            raise L.KernelError(f"attention kernels exist for head sizes {ATTENTION_HEAD_DIMS[0]}..."
+                                f"{ATTENTION_HEAD_DIMS[-1]} in steps of 16, not {head_dim}")
+        path = build_variant("attention_mma.cu", {"IMP_ATTN_DH": head_dim})
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise L.KernelError(f"cannot load {path}: {e}") from None
+        lib.imp_last_error.restype = ctypes.c_char_p
+        lib.imp_attn_head_dim.restype = c_int
+        assert lib.imp_attn_head_dim() == head_dim
+        lib.imp_attn_decode_scratch_floats.restype = c_int64
+        lib.imp_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int]
+        lib.imp_attn_decode.restype = c_int
+        lib.imp_attn_decode.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                        c_int, c_void_p, c_void_p, c_void_p]
+        lib.imp_attn_prefill.restype = c_int
+        lib.imp_attn_prefill.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_int, c_float, c_int, c_void_p, c_void_p]
+        _variants[head_dim] = lib
+    return lib
+
+
+def _check(lib, rc: int, what: str) -> None:
+    L.launch_calls += 1
+    if rc != 0:
+        raise L.KernelError(f"{what} failed ({rc}): {lib.imp_last_error().decode(errors='replace')}")
+
+
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int) -> int:
+    """Key splits of the decode kernel: a function of the batch size alone (a captured graph must not
+    depend on the context length); short contexts simply leave the later splits empty."""
+    base = n_tokens * n_kv_heads * ((group + 15) // 16)
+    return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_CTAS // max(base, 1)))
+
+
+def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,
+                     scale, window, status, n_splits=None):
+    """One query token per sequence over its cached keys (bfloat16)."""
+    lib = variant(head_dim)
+    T = q.shape[0]
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    if n_splits is None:
+        n_splits = decode_splits(T, n_kv_heads, n_q_heads // n_kv_heads)
+    scratch = None
+    n_floats = lib.imp_attn_decode_scratch_floats(T, n_q_heads, n_splits)
+    if n_floats:
+        scratch = torch.empty(n_floats, dtype=torch.float32, device=q.device)
+    _check(lib, lib.imp_attn_decode(
+        out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
+        block_table.shape[0], n_q_heads, n_kv_heads, page_size, num_pages, float(scale), int(window), n_splits,
+        None if scratch is None else scratch.data_ptr(), None if status is None else status.data_ptr(),
+        torch.cuda.current_stream().cuda_stream), "attention decode")
+    return out
+
+
+def prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,
+                      tile_tok0, tile_rows, scale, window, status):
+    """Tiles of up to 16 consecutive query tokens of one sequence over the cached keys (bfloat16)."""
+    lib = variant(head_dim)
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert tile_tok0.dtype == torch.int32 and tile_rows.dtype == torch.int32 and tile_tok0.numel() == tile_rows.numel()
+    _check(lib, lib.imp_attn_prefill(
+        out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(),
+        tile_tok0.data_ptr(), tile_rows.data_ptr(), tile_tok0.numel(), block_table.shape[0], n_q_heads, n_kv_heads,
+        page_size, num_pages, float(scale), int(window), None if status is None else status.data_ptr(),
+        torch.cuda.current_stream().cuda_stream), "attention prefill")
+    return out
 
 
 def paged_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx, scale, window, rt):
-    return K.paged_attention_generic(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
-                                     ctx.seq_of_token, ctx.positions, scale, window, rt.status)
+    if rt.is_float32:
+        return K.paged_attention_generic(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
+                                         ctx.seq_of_token, ctx.positions, scale, window, rt.status)
+    if ctx.decode_only:
+        return decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
+                                ctx.seq_of_token, ctx.positions, scale, window, rt.status)
+    return prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
+                             ctx.seq_of_token, ctx.positions, ctx.tile_tok0, ctx.tile_rows, scale, window, rt.status)

@@ -1,0 +1,497 @@
+"""Each CUDA kernel alone against a plain float32/float64 computation of the same op, at sizes other
+than the engine tests use (widths and vocabularies that are no power of two, every head size in
+steps of 16, odd head groups, page sizes 1..64)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+from plain import sampling_plain as S
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from imp_b200.ops import kernels, library
+    library.require_device()
+    return kernels
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, dtype, scale=None):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = float(want.abs().max()) if scale is None else scale
+    if dtype == torch.float32:
+        atol, rtol = 1e-5 * max(scale, 1.0), 1e-5
+    else:
+        atol, rtol = 0.01 * max(scale, 1e-3), 0.01      # bfloat16 storage: 8 bits of mantissa
+    err = (got - want).abs()
+    assert (err <= atol + rtol * want.abs()).all(), f"max error {err.max().item():.3g} (scale {scale:.3g})"
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_embedding(K, wdtype):
+    V, d = 1003, 200
+    table = rnd(V, d, dtype=wdtype).to(DEV)
+    ids = torch.tensor([0, 1002, 17, 17, 500], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, d, dtype=torch.float32, device=DEV)
+    status = K.new_status(DEV)
+    K.embedding(out, table, ids, 1.0, status)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()])
+    K.embedding(out, table, ids, 2.5, status)
+    assert torch.allclose(out.cpu(), table.float().cpu()[ids.cpu().long()] * 2.5)
+    K.check_status(status)
+    bad = torch.tensor([3, V, 1, 2, 3], dtype=torch.int32, device=DEV)
+    K.embedding(out, table, bad, 1.0, status)
+    with pytest.raises(Exception, match="token id"):
+        K.check_status(status)
+    assert (out[1] == 0).all()
+
+
+# ----------------------------------------------------------------------- norms
+@pytest.mark.parametrize("adtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [64, 200, 4096 + 24])
+def test_add_rmsnorm(K, adtype, wdtype, d):
+    T = 7
+    h = rnd(T, d, seed=1, scale=3.0)
+    br = rnd(T, d, dtype=adtype, seed=2)
+    w = (1 + 0.1 * rnd(d, seed=3)).to(wdtype)
+    hd, out = h.clone().to(DEV), torch.empty(T, d, dtype=adtype, device=DEV)
+    K.add_rmsnorm(hd, br.to(DEV), w.to(DEV), out, 1e-5)
+    hs = h + br.float()
+    assert torch.equal(hd.cpu(), hs)                      # the residual sum itself is exact float32
+    close(out, P.rmsnorm(hs.double(), w.double(), 1e-5), adtype)
+    # no branch; weight offset; eps matters
+    K.add_rmsnorm(hd, None, w.to(DEV), out, 0.5, weight_offset=1.0)
+    assert torch.equal(hd.cpu(), hs)
+    close(out, P.rmsnorm(hs.double(), w.double() + 1.0, 0.5), adtype)
+    # gather mode: chosen rows, h untouched, branch still added
+    rows = torch.tensor([6, 0, 6, 3], dtype=torch.int32, device=DEV)
+    h2 = h.clone().to(DEV)
+    out2 = torch.empty(4, d, dtype=adtype, device=DEV)
+    K.add_rmsnorm(h2, br.to(DEV), w.to(DEV), out2, 1e-5, rows=rows)
+    assert torch.equal(h2.cpu(), h)
+    close(out2, P.rmsnorm(hs.double(), w.double(), 1e-5)[rows.cpu().long()], adtype)
+
+
+@pytest.mark.parametrize("adtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_rows_strided(K, adtype):
+    x = rnd(9, 5 * 48, dtype=adtype, seed=4).to(DEV)
+    w = (1 + 0.1 * rnd(48, seed=5)).to(DEV)
+    view = x.view(9, 5, 48)[:, 2, :]                      # rows 480 apart
+    out = torch.empty(9, 48, dtype=adtype, device=DEV)
+    K.rmsnorm_rows(view, w, out, 1e-6)
+    close(out, P.rmsnorm(view.double().cpu(), w.double().cpu(), 1e-6), adtype)
+
+
+# ---------------------------------------------------------------------- swiglu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_cast(K, dtype):
+    T, F = 5, 333
+    gu = rnd(T, 2 * F, dtype=dtype, seed=6, scale=3.0).to(DEV)
+    out = torch.empty(T, F, dtype=dtype, device=DEV)
+    K.swiglu(out, gu)
+    g, u = gu.double().cpu()[:, :F], gu.double().cpu()[:, F:]
+    close(out, g / (1 + torch.exp(-g)) * u, dtype)
+    src = rnd(1001, seed=7).to(DEV)
+    b = K.cast(torch.empty(1001, dtype=torch.bfloat16, device=DEV), src)
+    assert torch.equal(b.cpu(), src.cpu().to(torch.bfloat16))
+    f = K.cast(torch.empty(1001, dtype=torch.float32, device=DEV), b)
+    assert torch.equal(f.cpu(), b.cpu().float())
+
+
+# ---------------------------------------------------------------------- matmul
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (3, 130, 70), (65, 64, 16), (130, 257, 129), (2, 1000, 4100)])
+def test_gemm_f32(K, M, N, K_):
+    a, w = rnd(M, K_, seed=8).to(DEV), rnd(N, K_, seed=9).to(DEV)
+    out = K.gemm_f32(torch.empty(M, N, device=DEV), a, w)
+    want = a.double().cpu() @ w.double().cpu().T
+    close(out, want, torch.float32)
+    # every output is the same bits whatever other rows are in the product
+    one = K.gemm_f32(torch.empty(1, N, device=DEV), a[M - 1:M], w)
+    assert torch.equal(one[0], out[M - 1])
+    # strided operands (a view of a wider buffer)
+    wide = torch.zeros(M, K_ + 9, device=DEV)
+    wide[:, 3:3 + K_] = a
+    out2 = K.gemm_f32(torch.empty(M, N, device=DEV), wide[:, 3:3 + K_], w)
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K_", [(10, 64), (257, 200), (96, 4104), (50, 100)])
+@pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_small_m(K, M, N, K_, odtype):
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=10).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=11).to(DEV)
+    out = K.gemm_bf16_small_m(torch.empty(M, N, dtype=odtype, device=DEV), a, w)
+    want = a.double().cpu() @ w.double().cpu().T
+    if odtype == torch.float32:
+        close(out, want, torch.float32, scale=float(want.abs().max()) * 4)   # float32 sums of bf16 products
+    else:
+        close(out, want, torch.bfloat16)
+    one = K.gemm_bf16_small_m(torch.empty(1, N, dtype=odtype, device=DEV), a[M - 1:M], w)
+    assert torch.equal(one[0], out[M - 1])                # the same bits for a row, alone or in a batch
+
+
+def test_linear_dispatch(K):
+    x = rnd(40, 96, dtype=torch.bfloat16, seed=12).to(DEV)
+    w = rnd(50, 96, dtype=torch.bfloat16, seed=13).to(DEV)
+    want = x.double().cpu() @ w.double().cpu().T
+    close(K.linear(torch.empty(40, 50, dtype=torch.bfloat16, device=DEV), x, w), want, torch.bfloat16)
+    close(K.linear(torch.empty(40, 50, dtype=torch.float32, device=DEV), x, w), want, torch.float32, scale=40.0)
+    close(K.linear(torch.empty(3, 50, dtype=torch.float32, device=DEV), x[:3], w), want[:3], torch.float32, scale=40.0)
+    # a weight the checkpoint stores in 32 bits stays so: the product runs in float32
+    w32 = rnd(50, 96, seed=14).to(DEV)
+    want32 = x.double().cpu() @ w32.double().cpu().T
+    close(K.linear(torch.empty(40, 50, dtype=torch.float32, device=DEV), x, w32), want32, torch.float32)
+    close(K.linear(torch.empty(40, 50, dtype=torch.bfloat16, device=DEV), x, w32), want32, torch.bfloat16)
+
+
+# ---------------------------------------------------- q/k norm + rotary + cache write
+def paged_layout(lengths, page_size, n_extra_pages=3, seed=0):
+    """A shuffled assignment of pages to sequences: (block table [B, max_pages] with -1 padding, num_pages)."""
+    rng = np.random.default_rng(seed)
+    need = [(n + page_size - 1) // page_size for n in lengths]
+    num_pages = sum(need) + n_extra_pages
+    perm = rng.permutation(num_pages)
+    bt = -np.ones((len(lengths), max(need) + 2), dtype=np.int32)
+    k = 0
+    for s, n in enumerate(need):
+        bt[s, :n] = perm[k:k + n]
+        k += n
+    return torch.from_numpy(bt), num_pages
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,Dh,rot,page", [(4, 2, 16, 16, 4), (6, 3, 32, 32, 16), (5, 5, 48, 24, 3), (8, 1, 128, 128, 16)])
+def test_qk_norm_rope_kv_write(K, dtype, Hq, Hkv, Dh, rot, page):
+    lengths = [11, 1, 30]
+    starts = [4, 0, 17]                                    # tokens of this step continue sequences at these positions
+    bt, num_pages = paged_layout(lengths, page)
+    toks = [(s, p) for s, (st, n) in enumerate(zip(starts, lengths)) for p in range(st, n)]
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32)
+    width = (Hq + 2 * Hkv) * Dh
+    qkv = rnd(T, width, dtype=dtype, seed=15)
+    qw, kw = (1 + 0.2 * rnd(Dh, seed=16)), (1 + 0.2 * rnd(Dh, seed=17))
+    max_pos = 64
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-2.0 * i / rot))[None, :]
+    cos, sin = ang.cos().float(), ang.sin().float()
+    kc = torch.zeros(num_pages, Hkv, page, Dh, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    status = K.new_status(DEV)
+    qd = qkv.clone().to(DEV)
+    K.qk_norm_rope_kv_write(qd, Hq, Hkv, Dh, qw.to(DEV), kw.to(DEV), 1e-6, cos.to(DEV), sin.to(DEV), rot,
+                            pos.to(DEV), seq.to(DEV), bt.to(DEV), kc, vc, status)
+    K.check_status(status)
+    x = qkv.double()
+    q = P.rmsnorm(x[:, :Hq * Dh].view(T, Hq, Dh), qw.double(), 1e-6)
+    k = P.rmsnorm(x[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh), kw.double(), 1e-6)
+    v = x[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+
+    def rot_part(z):
+        return torch.cat([P.rope(z[..., :rot].contiguous(), pos.tolist(), 1e4), z[..., rot:]], dim=-1)
+    q, k = rot_part(q), rot_part(k)
+    close(qd[:, :Hq * Dh].view(T, Hq, Dh), q, dtype)
+    assert torch.equal(qd[:, (Hq + Hkv) * Dh:].cpu(), qkv[:, (Hq + Hkv) * Dh:])     # v is left in place
+    kc_c, vc_c = kc.cpu(), vc.cpu()
+    touched = torch.zeros(num_pages, page, dtype=torch.bool)
+    for n, (s, p) in enumerate(toks):
+        pg, sl = int(bt[s, p // page]), p % page
+        close(kc_c[pg, :, sl, :], k[n], dtype)
+        assert torch.equal(vc_c[pg, :, sl, :].double(), v[n])
+        touched[pg, sl] = True
+    assert (kc_c[~touched.unsqueeze(1).expand(-1, Hkv, -1)] == 0).all()             # nothing else was written
+    # without norm weights and without a table: plain copy of k and v into the pages
+    kc.zero_(); vc.zero_()
+    qd = qkv.clone().to(DEV)
+    K.qk_norm_rope_kv_write(qd, Hq, Hkv, Dh, None, None, 1e-6, None, None, 0, pos.to(DEV), seq.to(DEV), bt.to(DEV),
+                            kc, vc, status)
+    n, (s, p) = T - 1, toks[-1]
+    assert torch.equal(kc.cpu()[int(bt[s, p // page]), :, p % page, :].reshape(-1), qkv[n, Hq * Dh:(Hq + Hkv) * Dh])
+    assert torch.equal(qd.cpu()[:, :Hq * Dh], qkv[:, :Hq * Dh])
+    # a position outside the table and a page outside the pool are reported, not written
+    badpos = pos.clone(); badpos[0] = max_pos
+    K.qk_norm_rope_kv_write(qd, Hq, Hkv, Dh, qw.to(DEV), kw.to(DEV), 1e-6, cos.to(DEV), sin.to(DEV), rot,
+                            badpos.to(DEV), seq.to(DEV), bt.to(DEV), kc, vc, status)
+    with pytest.raises(Exception, match="position"):
+        K.check_status(status)
+    badbt = bt.clone(); badbt[0, starts[0] // page] = num_pages
+    K.qk_norm_rope_kv_write(qd, Hq, Hkv, Dh, None, None, 1e-6, None, None, 0, pos.to(DEV), seq.to(DEV),
+                            badbt.to(DEV), kc, vc, status)
+    with pytest.raises(Exception, match="page"):
+        K.check_status(status)
+
+
+# ------------------------------------------------------------------- attention
+def attention_case(lengths, q_counts, Hq, Hkv, Dh, page, dtype, seed=0, spike=None):
+    """Dense K/V per sequence scattered into shuffled pages; queries are the last q_counts[s] tokens."""
+    bt, num_pages = paged_layout(lengths, page, seed=seed)
+    kc = torch.zeros(num_pages, Hkv, page, Dh, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    dense, toks, qs = [], [], []
+    for s, n in enumerate(lengths):
+        k = rnd(n, Hkv, Dh, dtype=dtype, seed=seed * 100 + 3 * s)
+        v = rnd(n, Hkv, Dh, dtype=dtype, seed=seed * 100 + 3 * s + 1)
+        q = rnd(n, Hq, Dh, dtype=dtype, seed=seed * 100 + 3 * s + 2)
+        if spike is not None:
+            # one far key that the last query must find: its score stands out by a wide margin
+            j = spike(n)
+            k[j] = (q[n - 1].view(Hkv, Hq // Hkv, Dh)[:, 0, :] * 4.0).to(dtype)
+            v[j] = 5.0
+        for p in range(n):
+            kc[int(bt[s, p // page]), :, p % page, :] = k[p]
+            vc[int(bt[s, p // page]), :, p % page, :] = v[p]
+        dense.append((q, k, v))
+        for p in range(n - q_counts[s], n):
+            toks.append((s, p))
+            qs.append(q[p])
+    return bt, num_pages, kc, vc, dense, toks, torch.stack(qs)
+
+
+def attention_reference(dense, toks, window):
+    out = []
+    cache = {}
+    for s, p in toks:
+        if s not in cache:
+            q, k, v = dense[s]
+            cache[s] = P.attention(q.double(), k.double(), v.double(), window)
+        out.append(cache[s][p])
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 2, 16, 4, 0), (6, 3, 32, 16, 24), (3, 1, 80, 5, 0), (8, 8, 64, 1, 7),
+                                                   (2, 1, 256, 64, 0)])
+def test_attention_generic(K, dtype, Hq, Hkv, Dh, page, window):
+    lengths, q_counts = [37, 1, 150, 64], [37, 1, 9, 1]
+    bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, q_counts, Hq, Hkv, Dh, page, dtype)
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, Hq * Dh, dtype=dtype, device=DEV)
+    status = K.new_status(DEV)
+    K.paged_attention_generic(out, q.reshape(T, Hq * Dh).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV),
+                              seq, pos, 1 / math.sqrt(Dh), window, status)
+    K.check_status(status)
+    close(out.view(T, Hq, Dh), attention_reference(dense, toks, window), dtype)
+
+
+ALL_HEAD_DIMS = list(range(16, 257, 16))
+
+
+@pytest.mark.parametrize("Dh", ALL_HEAD_DIMS)
+def test_attention_mma_every_head_size(K, Dh):
+    """Decode and prefill tensor-core kernels at every head size the configuration allows."""
+    from imp_b200.ops import attention as A
+    Hq, Hkv, page = 6, 2, 16
+    lengths = [70, 33, 1, 129]
+    status = K.new_status(DEV)
+    # decode: one query per sequence, with and without key splits
+    bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, [1, 1, 1, 1], Hq, Hkv, Dh, page, torch.bfloat16, seed=Dh)
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    want = attention_reference(dense, toks, 0)
+    for splits in (1, 3, None):
+        out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        A.decode_attention(out, q.reshape(T, Hq * Dh).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
+                           1 / math.sqrt(Dh), 0, status, n_splits=splits)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), want, torch.bfloat16)
+    # prefill: portions of 20, 33, 1 and 40 tokens at the ends of the sequences
+    counts = [20, 33, 1, 40]
+    bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, counts, Hq, Hkv, Dh, page, torch.bfloat16, seed=Dh + 1)
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    tiles0, tilesn, t = [], [], 0
+    for n in counts:
+        for a in range(0, n, 16):
+            tiles0.append(t + a); tilesn.append(min(16, n - a))
+        t += n
+    out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    A.prefill_attention(out, q.reshape(T, Hq * Dh).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
+                        torch.tensor(tiles0, dtype=torch.int32, device=DEV),
+                        torch.tensor(tilesn, dtype=torch.int32, device=DEV), 1 / math.sqrt(Dh), 0, status)
+    K.check_status(status)
+    close(out.view(T, Hq, Dh), attention_reference(dense, toks, 0), torch.bfloat16)
+
+
+@pytest.mark.parametrize("Hq,Hkv,page,window", [(4, 4, 16, 0), (5, 1, 4, 0), (12, 3, 1, 0), (40, 2, 16, 0), (8, 2, 8, 19),
+                                                (3, 3, 64, 100), (4, 1, 3, 16)])
+def test_attention_mma_groups_pages_windows(K, Hq, Hkv, page, window):
+    from imp_b200.ops import attention as A
+    Dh = 64
+    lengths = [300, 17, 64, 100]
+    status = K.new_status(DEV)
+    for counts in ([1, 1, 1, 1], [50, 17, 2, 33]):
+        bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, counts, Hq, Hkv, Dh, page, torch.bfloat16, seed=7)
+        T = len(toks)
+        seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+        pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+        want = attention_reference(dense, toks, window)
+        btd = bt.clone()
+        if window:
+            # pages wholly behind every query's window are gone, as the cache manager leaves them
+            for s, n in enumerate(lengths):
+                first = max(0, (n - counts[s]) - window + 1)
+                btd[s, :first // page] = -1
+        out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qd = q.reshape(T, Hq * Dh).to(DEV)
+        if counts == [1, 1, 1, 1]:
+            for splits in (1, 4, None):
+                A.decode_attention(out, qd, Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), btd.to(DEV), seq, pos,
+                                   1 / math.sqrt(Dh), window, status, n_splits=splits)
+                K.check_status(status)
+                close(out.view(T, Hq, Dh), want, torch.bfloat16)
+        tiles0, tilesn, t = [], [], 0
+        for n in counts:
+            for a in range(0, n, 16):
+                tiles0.append(t + a); tilesn.append(min(16, n - a))
+            t += n
+        out.fill_(float("nan"))
+        A.prefill_attention(out, qd, Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), btd.to(DEV), seq, pos,
+                            torch.tensor(tiles0, dtype=torch.int32, device=DEV),
+                            torch.tensor(tilesn, dtype=torch.int32, device=DEV), 1 / math.sqrt(Dh), window, status)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), want, torch.bfloat16)
+        # the plain kernel agrees on the same pages
+        out.fill_(float("nan"))
+        K.paged_attention_generic(out, qd, Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), btd.to(DEV), seq, pos,
+                                  1 / math.sqrt(Dh), window, status)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("where", ["first", "page_edge", "far"])
+def test_attention_finds_one_far_key_among_hundreds(K, where):
+    """Random keys would hide a wrong page or a dropped key; here one key's score stands out, and its
+    value (5.0 everywhere) must dominate the output."""
+    from imp_b200.ops import attention as A
+    Hq, Hkv, Dh, page = 4, 2, 64, 16
+    spike = {"first": lambda n: 0, "page_edge": lambda n: 16 * (n // 32) - 1, "far": lambda n: n // 7}[where]
+    lengths = [700, 333]
+    bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, [1, 1], Hq, Hkv, Dh, page, torch.bfloat16, seed=3,
+                                                           spike=spike)
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    want = attention_reference(dense, toks, 0)
+    assert (want.view(T, Hkv, Hq // Hkv, Dh)[:, :, 0, :] > 4.5).all()        # the spike dominates head 0 of each group
+    status = K.new_status(DEV)
+    qd = q.reshape(T, Hq * Dh).to(DEV)
+    for splits in (1, 7, None):
+        out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        A.decode_attention(out, qd, Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos, 1 / math.sqrt(Dh), 0,
+                           status, n_splits=splits)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), want, torch.bfloat16)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((T, Hq * Dh), float("nan"), dtype=dtype, device=DEV)
+        K.paged_attention_generic(out, qd.to(dtype), Hq, Hkv, Dh, kc.to(DEV).to(dtype), vc.to(DEV).to(dtype),
+                                  bt.to(DEV), seq, pos, 1 / math.sqrt(Dh), 0, status)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), want, dtype)
+
+
+def test_attention_reports_a_bad_page(K):
+    from imp_b200.ops import attention as A
+    Hq, Hkv, Dh, page = 2, 1, 32, 16
+    bt, num_pages, kc, vc, dense, toks, q = attention_case([40], [1], Hq, Hkv, Dh, page, torch.bfloat16)
+    bt[0, 1] = num_pages + 5
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([39], dtype=torch.int32, device=DEV)
+    status = K.new_status(DEV)
+    out = torch.empty(1, Hq * Dh, dtype=torch.bfloat16, device=DEV)
+    A.decode_attention(out, q.reshape(1, -1).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos, 0.1, 0,
+                       status, n_splits=1)
+    with pytest.raises(Exception, match="page"):
+        K.check_status(status)
+    K.paged_attention_generic(out, q.reshape(1, -1).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
+                              0.1, 0, status)
+    with pytest.raises(Exception, match="page"):
+        K.check_status(status)
+
+
+# -------------------------------------------------------------------- sampling
+def test_argmax_ties_and_large_vocab(K):
+    V = 151936 + 7
+    x = rnd(3, V, seed=20).to(DEV)
+    x[0, 100] = x[0, 90000] = 50.0                        # tie: the lowest index wins
+    x[1, V - 1] = 60.0
+    x[2] = -1e30
+    x[2, 12345] = -5.0
+    assert K.argmax(x).tolist() == [100, V - 1, 12345]
+    wide = torch.zeros(2, 300, device=DEV)                # rows of a wider buffer
+    wide[0, 7] = 1.0
+    wide[1, 250] = 1.0
+    assert K.argmax(wide[:, :200]).tolist() == [7, 0]
+
+
+def run_sample(K, logits, temperature, u, top_k=0, top_p=1.0, min_p=0.0):
+    R = logits.shape[0]
+    f = lambda v: torch.full((R,), float(v), dtype=torch.float32, device=DEV)  # noqa: E731
+    return K.sample(logits.to(DEV), f(temperature), torch.full((R,), int(top_k), dtype=torch.int32, device=DEV),
+                    f(top_p), f(min_p), torch.as_tensor(u, dtype=torch.float32, device=DEV)).tolist()
+
+
+@pytest.mark.parametrize("filters", [{}, {"top_k": 5}, {"top_p": 0.7}, {"min_p": 0.1}, {"top_k": 40, "top_p": 0.9},
+                                     {"top_k": 7, "top_p": 0.5, "min_p": 0.02}])
+def test_sample_matches_the_plain_twin(K, filters):
+    V, R = 1003, 64
+    logits = rnd(1, V, seed=21, scale=2.0).repeat(R, 1)
+    us = np.random.default_rng(1).random(R).astype(np.float32)
+    got = run_sample(K, logits, 0.8, us, **filters)
+    x = logits[0].numpy()
+    keep, _ = S.kept_set(x, 0.8, **filters)
+    for tok, u in zip(got, us):
+        assert keep[tok], f"token {tok} is outside the kept set of {filters}"
+        lo, hi, _ = S.draw_interval(x, 0.8, tok, **filters)
+        assert lo - 1e-5 <= u <= hi + 1e-5, f"u={u} does not select token {tok} (interval [{lo}, {hi}))"
+    if filters.get("top_k"):
+        assert len(set(got)) <= filters["top_k"]
+
+
+def test_sample_greedy_paths_and_distribution(K):
+    V = 200
+    logits = rnd(1, V, seed=22, scale=1.5)
+    am = int(logits[0].argmax())
+    assert run_sample(K, logits, 0.0, [0.7]) == [am]
+    assert run_sample(K, logits, 1.0, [0.7], top_k=1) == [am]
+    R = 20000
+    us = np.random.default_rng(2).random(R).astype(np.float32)
+    got = np.array(run_sample(K, logits.repeat(R, 1), 1.0, us))
+    freq = np.bincount(got, minlength=V) / R
+    p = torch.softmax(logits[0].double(), 0).numpy()
+    assert np.abs(freq - p).max() < 0.012
+    # rows are independent of one another: a row alone gives what it gives in a batch
+    assert run_sample(K, logits, 1.0, [us[17]]) == [got[17]]
+
+
+def test_penalties(K):
+    V = 300
+    logits = rnd(3, V, seed=23, scale=2.0)
+    hist = [[5, 5, 7, 299], [], [1, 2, 3, 1, 1]]
+    flat = torch.tensor([t for h in hist for t in h], dtype=torch.int32, device=DEV)
+    start = torch.tensor([0, 4, 4, 9], dtype=torch.int32, device=DEV)
+    rep = torch.tensor([1.3, 1.0, 1.0], device=DEV)
+    freq = torch.tensor([0.2, 0.0, 0.5], device=DEV)
+    pres = torch.tensor([0.1, 0.0, 0.0], device=DEV)
+    x = logits.clone().to(DEV)
+    K.apply_penalties(x, flat, start, 5, rep, freq, pres, torch.empty(3 * V, dtype=torch.int32, device=DEV))
+    for r in range(3):
+        want = S.penalize(logits[r].numpy(), hist[r], float(rep[r]), float(freq[r]), float(pres[r]))
+        assert np.allclose(x[r].cpu().numpy(), want, atol=1e-5)
