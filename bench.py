@@ -195,11 +195,11 @@ def run_ours(args):
     mc = config_from_dict(cfgd)
     torch.cuda.set_device(0)
     B = args.batch
-    maxB = max(B, 64)
+    maxB = max(B, 64) if not args.only else B
     _, _, kv_per_tok = model_numbers(cfgd, n_layers)
     ecfg = EngineConfig(max_batch_size=maxB, max_seq_len=CONTEXT, kv_block_size=PAGE,
                         kv_cache_tokens=maxB * CONTEXT + 4 * CONTEXT, max_batch_tokens=PREFILL_TOKENS,
-                        compute_dtype="bfloat16", enable_cuda_graphs=True)
+                        compute_dtype="bfloat16", enable_cuda_graphs=not args.no_graphs)
     t0 = time.time()
     eng = Engine.from_random(mc, ecfg, seed=0, std=0.02)
     for g in eng.cache.paged:          # stand-in cache contents for sequences that are not really prefilled
@@ -208,8 +208,13 @@ def run_ours(args):
     setup_s = time.time() - t0
     _, weight_bytes, _ = model_numbers(cfgd, n_layers)
 
-    # ---- prefill: one prompt of 2,048 tokens in one step --------------------------------------------
     gen = torch.Generator().manual_seed(0)
+    if args.only == "decode":
+        ms, calls = time_decode(eng, B, CONTEXT, args.steps, args.warmup, torch, K, StepEntry)
+        print(json.dumps({"only": "decode", "batch": B, "layers": n_layers, "ms_per_step": round(ms, 4),
+                          "launcher_calls_per_step": calls}))
+        return 0
+    # ---- prefill: one prompt of 2,048 tokens in one step --------------------------------------------
     prompt = torch.randint(0, mc.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
     pf_ms = []
     for i in range(1 + 3):
@@ -224,6 +229,9 @@ def run_ours(args):
             pf_ms.append(e0.elapsed_time(e1))
     eng.stepper.check_device_status("prefill bench")
     pf = statistics.median(pf_ms)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PREFILL_TOKENS, "ms": round(pf, 3)}))
+        return 0
     pf_flops = prefill_flops(cfgd, n_layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pf * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
                "frac": round(pf_flops / (pf * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
@@ -314,6 +322,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run one phase only and print its timing (for profiling small cases)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

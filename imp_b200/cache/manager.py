@@ -26,6 +26,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """Not enough free pages (or state slots) for what was asked."""
@@ -104,17 +106,41 @@ class SlotPool(PagePool):
 # Groups
 # ---------------------------------------------------------------------------
 class PagedGroup:
-    """Layers that share page ids: same kv heads, head size and window."""
+    """Layers that share page ids: same kv heads, head size and window.
 
-    def __init__(self, gid: int, spec: PagedKVSpec, layers: List[int], page_size: int, num_pages: int):
+    Block tables live in one int32 matrix [slots, max_pages_per_seq] (-1 = no page), so that a
+    batch's table is one gather by slot.  Invariant: for a live request of committed length n, every
+    entry in [first_live_page(n), n_entries) holds a page and every entry outside holds -1.
+    """
+
+    def __init__(self, gid: int, spec: PagedKVSpec, layers: List[int], page_size: int, num_pages: int,
+                 num_slots: int, max_pages_per_seq: int):
         self.gid = gid
         self.spec = spec
         self.layers = layers
         self.page_size = page_size
         self.pool = PagePool(num_pages)
-        # request -> page id per logical page index (position // page_size); -1 = already given back
-        self.tables: Dict[Hashable, List[int]] = {}
+        self.table_np = np.full((num_slots, max_pages_per_seq), -1, dtype=np.int32)
+        self.n_entries = np.zeros(num_slots, dtype=np.int64)   # logical pages per slot (held or given back)
+        self.slot_of: Dict[Hashable, int] = {}
         self.storage = None  # torch tensor [n_layers, 2, num_pages, kv_heads, page_size, head_dim]
+
+    @property
+    def tables(self) -> Dict[Hashable, "np.ndarray"]:
+        """request -> its block table (a view: page id per logical page, -1 = already given back)."""
+        return {rid: self.table_np[s, :self.n_entries[s]] for rid, s in self.slot_of.items()}
+
+    def ensure_width(self, n_logical: int) -> None:
+        """Widen the table matrix so that a row can hold `n_logical` logical pages."""
+        width = self.table_np.shape[1]
+        if n_logical > width:
+            wider = np.full((self.table_np.shape[0], max(n_logical, 2 * width)), -1, dtype=np.int32)
+            wider[:, :width] = self.table_np
+            self.table_np = wider
+
+    def table(self, rid: Hashable):
+        s = self.slot_of[rid]
+        return self.table_np[s, :self.n_entries[s]]
 
     def first_live_page(self, length: int) -> int:
         """Index of the first logical page a query at position >= `length` can still read."""
@@ -123,14 +149,13 @@ class PagedGroup:
         first_pos = max(0, length - self.spec.window + 1)
         return first_pos // self.page_size
 
-    def pages_needed(self, table: List[int], cur_len: int, new_len: int) -> int:
+    def pages_needed_n(self, n_entries: int, cur_len: int, new_len: int) -> int:
+        """Pages to allocate for a request with `n_entries` logical pages to grow from cur_len to new_len."""
         n_logical = (new_len + self.page_size - 1) // self.page_size
-        lo = self.first_live_page(cur_len)
-        need = 0
-        for i in range(lo, n_logical):
-            if i >= len(table) or table[i] < 0:
-                need += 1
-        return need
+        return max(0, n_logical - max(n_entries, self.first_live_page(cur_len)))
+
+    def pages_needed(self, table, cur_len: int, new_len: int) -> int:
+        return self.pages_needed_n(len(table), cur_len, new_len)
 
 
 class StateGroup:
@@ -160,11 +185,13 @@ class CacheManager:
     """
 
     def __init__(self, layer_specs: Sequence[Optional[object]], page_size: int, num_pages: int,
-                 num_state_slots: int = 1):
+                 num_state_slots: int = 1, max_pages_per_seq: Optional[int] = None):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.num_pages = num_pages
+        self.max_pages_per_seq = max_pages_per_seq or num_pages
+        n_slots = max(1, num_state_slots)
         self.paged: List[PagedGroup] = []
         self.state: List[StateGroup] = []
         self.layer_ref: List[Optional[LayerCacheRef]] = []
@@ -176,7 +203,7 @@ class CacheManager:
             grp = by_spec.get(spec)
             if grp is None:
                 if isinstance(spec, PagedKVSpec):
-                    grp = PagedGroup(len(self.paged), spec, [], page_size, num_pages)
+                    grp = PagedGroup(len(self.paged), spec, [], page_size, num_pages, n_slots, self.max_pages_per_seq)
                     self.paged.append(grp)
                 elif isinstance(spec, StateSpec):
                     grp = StateGroup(len(self.state), spec, [])
@@ -186,7 +213,7 @@ class CacheManager:
                 by_spec[spec] = grp
             grp.layers.append(layer)
             self.layer_ref.append(LayerCacheRef(grp.gid, len(grp.layers) - 1, spec.kind))
-        self.slots = SlotPool(max(1, num_state_slots))
+        self.slots = SlotPool(n_slots)
         self._slot_of: Dict[Hashable, int] = {}
         self._length: Dict[Hashable, int] = {}     # tokens committed per request
         self._reserved: Dict[Hashable, int] = {}   # tokens reserved (>= committed) per request
@@ -213,7 +240,8 @@ class CacheManager:
         self._length[rid] = 0
         self._reserved[rid] = 0
         for g in self.paged:
-            g.tables[rid] = []
+            g.slot_of[rid] = slot
+            g.n_entries[slot] = 0
         return slot
 
     def slot_of(self, rid: Hashable) -> int:
@@ -222,7 +250,8 @@ class CacheManager:
     def pages_needed(self, rid: Hashable, new_len: int) -> int:
         """Most pages any group lacks for `rid` to grow to `new_len` tokens."""
         cur = self._length[rid]
-        return max((g.pages_needed(g.tables[rid], cur, new_len) for g in self.paged), default=0)
+        slot = self._slot_of[rid]
+        return max((g.pages_needed_n(int(g.n_entries[slot]), cur, new_len) for g in self.paged), default=0)
 
     def pages_for_new_request(self, n_tokens: int) -> int:
         """Pages per group that a fresh request needs for its first `n_tokens` tokens."""
@@ -234,7 +263,8 @@ class CacheManager:
 
     def can_reserve(self, rid: Hashable, new_len: int) -> bool:
         cur = self._length[rid]
-        return all(g.pages_needed(g.tables[rid], cur, new_len) <= g.pool.n_free for g in self.paged)
+        slot = self._slot_of[rid]
+        return all(g.pages_needed_n(int(g.n_entries[slot]), cur, new_len) <= g.pool.n_free for g in self.paged)
 
     def reserve(self, rid: Hashable, new_len: int) -> None:
         """Make sure every paged group has pages for positions < new_len that later queries can see.
@@ -246,20 +276,21 @@ class CacheManager:
         cur = self._length[rid]
         if new_len < cur:
             raise CacheError(f"request {rid!r}: cannot reserve {new_len} tokens below its length {cur}")
+        slot = self._slot_of[rid]
         for g in self.paged:
-            need = g.pages_needed(g.tables[rid], cur, new_len)
+            n_logical = (new_len + g.page_size - 1) // g.page_size
+            g.ensure_width(n_logical)
+            need = g.pages_needed_n(int(g.n_entries[slot]), cur, new_len)
             if need > g.pool.n_free:
                 raise OutOfPages(f"group {g.gid}: request {rid!r} needs {need} more pages for {new_len} tokens, "
                                  f"{g.pool.n_free} free")
         for g in self.paged:
-            table = g.tables[rid]
             n_logical = (new_len + g.page_size - 1) // g.page_size
-            lo = g.first_live_page(cur)
-            while len(table) < n_logical:
-                table.append(-1)
-            for i in range(lo, n_logical):
-                if table[i] < 0:
-                    table[i] = g.pool.alloc()
+            row = g.table_np[slot]
+            for i in range(max(int(g.n_entries[slot]), g.first_live_page(cur)), n_logical):
+                row[i] = g.pool.alloc()
+            if n_logical > g.n_entries[slot]:
+                g.n_entries[slot] = n_logical
         self._reserved[rid] = max(self._reserved[rid], new_len)
 
     def commit(self, rid: Hashable, new_len: int) -> List[Tuple[int, int]]:
@@ -271,17 +302,21 @@ class CacheManager:
             raise CacheError(f"request {rid!r}: commit of {new_len} tokens beyond the reserved {self._reserved[rid]}")
         if new_len < self._length[rid]:
             raise CacheError(f"request {rid!r}: length cannot shrink from {self._length[rid]} to {new_len}")
+        old_len = self._length[rid]
         self._length[rid] = new_len
         freed = []
         for g in self.paged:
             if g.spec.window <= 0:
                 continue
-            table = g.tables[rid]
-            for i in range(min(g.first_live_page(new_len), len(table))):
-                if table[i] >= 0:
-                    g.pool.free(table[i])
-                    freed.append((g.gid, table[i]))
-                    table[i] = -1
+            slot = self._slot_of[rid]
+            row = g.table_np[slot]
+            hi = min(g.first_live_page(new_len), int(g.n_entries[slot]))
+            lo = g.first_live_page(old_len)
+            for i in range(min(lo, hi), hi):
+                if row[i] >= 0:
+                    g.pool.free(int(row[i]))
+                    freed.append((g.gid, int(row[i])))
+                    row[i] = -1
         return freed
 
     def release(self, rid: Hashable) -> None:
@@ -289,15 +324,20 @@ class CacheManager:
         if rid not in self._length:
             raise CacheError(f"release of unknown request {rid!r} (released twice?)")
         for g in self.paged:
-            for p in g.tables.pop(rid):
-                if p >= 0:
-                    g.pool.free(p)
+            slot = g.slot_of.pop(rid)
+            row = g.table_np[slot]
+            for i in range(g.first_live_page(self._length[rid]), int(g.n_entries[slot])):
+                if row[i] >= 0:
+                    g.pool.free(int(row[i]))
+            row[:int(g.n_entries[slot])] = -1
+            g.n_entries[slot] = 0
         self.slots.free(self._slot_of.pop(rid))
         del self._length[rid]
         del self._reserved[rid]
 
     def block_table(self, group: int, rid: Hashable) -> List[int]:
-        return self.paged[group].tables[rid]
+        """The request's block table in `group` as a list (page id per logical page, -1 = given back)."""
+        return [int(p) for p in self.paged[group].table(rid)]
 
     # ---------------------------------------------------------------- invariants
     def check_invariants(self) -> None:

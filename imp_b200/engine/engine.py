@@ -142,7 +142,7 @@ class Engine:
             return outs
         entries, rows = [], []
         for e in plan.entries:
-            toks = e.request.all_tokens()[e.start:e.start + e.n_tokens]
+            toks = e.request.tokens_slice(e.start, e.n_tokens)
             entries.append(StepEntry(e.request.rid, toks, [e.n_tokens - 1] if e.samples else []))
             if e.samples:
                 rows.append(e.request)

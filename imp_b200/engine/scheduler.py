@@ -69,6 +69,15 @@ class Request:
     def all_tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def tokens_slice(self, start: int, n: int) -> List[int]:
+        """Tokens [start, start+n) of prompt followed by output, without joining the two lists."""
+        np_ = len(self.prompt)
+        if start >= np_:
+            return self.output[start - np_: start - np_ + n]
+        if start + n <= np_:
+            return self.prompt[start: start + n]
+        return self.prompt[start:] + self.output[: start + n - np_]
+
     @property
     def n_total(self) -> int:
         return len(self.prompt) + len(self.output)
@@ -91,6 +100,7 @@ class StepPlan:
     entries: List[ScheduledEntry]
     preempted: List[Request] = field(default_factory=list)
     failed: List[Request] = field(default_factory=list)
+    pages: int = 0    # pages the entries so far will take from the pool
 
     @property
     def n_tokens(self) -> int:
@@ -168,6 +178,7 @@ class Scheduler:
         self.running.remove(victim)
         plan.entries = [e for e in plan.entries if e.request is not victim]
         self._release(victim)
+        plan.pages = sum(self._pages_needed(e.request, e.start + e.n_tokens) for e in plan.entries)
         victim.status = RequestStatus.WAITING
         victim.n_preempted += 1
         self.waiting.appendleft(victim)
@@ -176,12 +187,11 @@ class Scheduler:
     def _pages_needed(self, req: Request, new_len: int) -> int:
         if self.cache.has(req.rid):
             return self.cache.pages_needed(req.rid, new_len)
-        return max((g.pages_needed([], 0, new_len) for g in self.cache.paged), default=0)
+        return max((g.pages_needed_n(0, 0, new_len) for g in self.cache.paged), default=0)
 
     def _free_after(self, plan: StepPlan) -> int:
         """Free pages left once everything already in the plan has been reserved."""
-        return self.cache.free_pages() - sum(self._pages_needed(e.request, e.start + e.n_tokens)
-                                             for e in plan.entries)
+        return self.cache.free_pages() - plan.pages
 
     def _largest_fit(self, req: Request, n: int, free: int) -> int:
         """The most tokens <= n that `req` can take next with `free` pages."""
@@ -220,6 +230,7 @@ class Scheduler:
                     self._preempt(req, plan)
                 return 0
             self._preempt(victim, plan)
+        plan.pages += self._pages_needed(req, req.n_computed + n)
         plan.entries.append(ScheduledEntry(req, req.n_computed, n, req.n_computed + n == req.n_total))
         return n
 
@@ -258,6 +269,7 @@ class Scheduler:
             req.status = RequestStatus.RUNNING
             req.n_computed = 0
             self.running.append(req)
+            plan.pages += self._pages_needed(req, n)
             plan.entries.append(ScheduledEntry(req, 0, n, n == req.n_total))
             budget -= n
         return plan

@@ -114,113 +114,110 @@ class Stepper:
             rt.status = K.new_status(rt.device)
         model.attach_cache(cache)
 
-    # ------------------------------------------------------------------ checks
-    def validate(self, entries: Sequence[StepEntry]) -> None:
-        """Host-side checks of a batch before anything is reserved or launched."""
-        if not entries:
-            raise ValueError("a step needs at least one entry")
-        if len(entries) > self.max_seqs:
-            raise ValueError(f"{len(entries)} requests in one step; the engine was made for {self.max_seqs}")
-        total = 0
-        seen = set()
-        V = self.model.vocab_size
-        for e in entries:
-            if e.rid in seen:
-                raise ValueError(f"request {e.rid!r} appears twice in one step")
-            seen.add(e.rid)
-            n = len(e.tokens)
-            if n == 0:
-                raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
-            total += n
-            for t in e.tokens:
-                if not 0 <= int(t) < V:
-                    raise ValueError(f"request {e.rid!r}: token id {t} outside the vocabulary of {V}")
-            for w in e.want:
-                if not 0 <= int(w) < n:
-                    raise ValueError(f"request {e.rid!r}: wanted row {w} outside its {n} tokens")
-            cur = self.cache.length(e.rid) if self.cache.has(e.rid) else 0
-            if cur + n > self.max_seq_len:
-                raise ValueError(f"request {e.rid!r}: {cur + n} tokens exceed the maximum sequence length "
-                                 f"{self.max_seq_len}")
-        if total > self.max_tokens:
-            raise ValueError(f"{total} tokens in one step; the engine was made for {self.max_tokens}")
-
+    # -------------------------------------------------------------------- step
     def pages_short(self, entries: Sequence[StepEntry]) -> int:
         """How many pages the scarcest group lacks for this batch (0 = it fits)."""
+        cache = self.cache
         short = 0
-        for g in self.cache.paged:
+        for g in cache.paged:
             need = 0
             for e in entries:
-                if self.cache.has(e.rid):
-                    cur = self.cache.length(e.rid)
-                    need += g.pages_needed(g.tables[e.rid], cur, cur + len(e.tokens))
+                if cache.has(e.rid):
+                    cur = cache.length(e.rid)
+                    need += g.pages_needed_n(int(g.n_entries[cache.slot_of(e.rid)]), cur, cur + len(e.tokens))
                 else:
-                    need += g.pages_needed([], 0, len(e.tokens))
+                    need += g.pages_needed_n(0, 0, len(e.tokens))
             short = max(short, need - g.pool.n_free)
         return short
 
-    # -------------------------------------------------------------------- step
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserve cache, fill and upload the batch arrays; returns the device views."""
-        self.validate(entries)
-        if self.pages_short(entries) > 0:
-            raise OutOfPages(f"the batch needs {self.pages_short(entries)} more pages than are free")
-        cache = self.cache
-        new_slots = sum(1 for e in entries if not cache.has(e.rid))
+        """Check the batch on the host, reserve cache, fill and upload the batch arrays."""
+        cache, buf = self.cache, self.buffers
+        B = len(entries)
+        if B == 0:
+            raise ValueError("a step needs at least one entry")
+        if B > self.max_seqs:
+            raise ValueError(f"{B} requests in one step; the engine was made for {self.max_seqs}")
+        rids = [e.rid for e in entries]
+        if len(set(rids)) != B:
+            raise ValueError("a request appears twice in one step")
+        q_lens = [len(e.tokens) for e in entries]
+        if min(q_lens) == 0:
+            raise ValueError("an entry needs at least one token")
+        T = sum(q_lens)
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens in one step; the engine was made for {self.max_tokens}")
+        flat = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        V = self.model.vocab_size
+        if flat.min() < 0 or flat.max() >= V:
+            bad = int(flat[(flat < 0) | (flat >= V)][0])
+            raise ValueError(f"token id {bad} outside the vocabulary of {V}")
+        starts = [cache.length(r) if cache.has(r) else 0 for r in rids]
+        for e, st, n in zip(entries, starts, q_lens):
+            if st + n > self.max_seq_len:
+                raise ValueError(f"request {e.rid!r}: {st + n} tokens exceed the maximum sequence length "
+                                 f"{self.max_seq_len}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"request {e.rid!r}: wanted row {w} outside its {n} tokens")
+        short = self.pages_short(entries)
+        if short > 0:
+            raise OutOfPages(f"the batch needs {short} more pages than are free")
+        new_slots = sum(1 for r in rids if not cache.has(r))
         if new_slots > cache.slots.n_free:
             raise OutOfPages(f"{new_slots} new requests but only {cache.slots.n_free} free state slots")
-        buf = self.buffers
+
+        for r, st, n in zip(rids, starts, q_lens):
+            if not cache.has(r):
+                cache.zero_state(cache.add_request(r))
+            cache.reserve(r, st + n)
+        slots = np.fromiter((cache.slot_of(r) for r in rids), dtype=np.int64, count=B)
+
         i, host = buf.staging()
         off = buf.off
-        ctx = StepContext()
-        t = 0
-        rows: List[int] = []
-        tiles0: List[int] = []
-        tilesn: List[int] = []
-        q_lens, starts, rids, fresh = [], [], [], []
-        max_kv = 0
-        for s, e in enumerate(entries):
-            if not cache.has(e.rid):
-                slot = cache.add_request(e.rid)
-                cache.zero_state(slot)
-            start = cache.length(e.rid)
-            n = len(e.tokens)
-            cache.reserve(e.rid, start + n)
-            host[off["tok"] + t: off["tok"] + t + n] = np.asarray(e.tokens, dtype=np.int32)
-            host[off["pos"] + t: off["pos"] + t + n] = np.arange(start, start + n, dtype=np.int32)
-            host[off["seq"] + t: off["seq"] + t + n] = s
-            host[off["q_start"] + s] = t
-            host[off["kv_len"] + s] = start + n
-            host[off["slots"] + s] = cache.slot_of(e.rid)
-            for g, bo in enumerate(buf.bt_off):
-                table = cache.block_table(g, e.rid)
-                row = host[bo + s * buf.max_pages: bo + (s + 1) * buf.max_pages]
-                row[:len(table)] = table
-                row[len(table):] = -1
-            rows.extend(t + int(w) for w in e.want)
-            for a in range(0, n, ATTENTION_TILE):
-                tiles0.append(t + a)
-                tilesn.append(min(ATTENTION_TILE, n - a))
-            q_lens.append(n)
-            starts.append(start)
-            rids.append(e.rid)
-            fresh.append(start == 0)
-            max_kv = max(max_kv, start + n)
-            t += n
-        B = len(entries)
-        host[off["q_start"] + B] = t
+        ql = np.asarray(q_lens, dtype=np.int64)
+        st_np = np.asarray(starts, dtype=np.int64)
+        q_start = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(ql, out=q_start[1:])
+        decode_only = T == B
+        host[off["tok"]: off["tok"] + T] = flat
+        if decode_only:
+            host[off["pos"]: off["pos"] + T] = st_np
+            host[off["seq"]: off["seq"] + T] = np.arange(B)
+        else:
+            host[off["pos"]: off["pos"] + T] = np.arange(T) + np.repeat(st_np - q_start[:-1], ql)
+            host[off["seq"]: off["seq"] + T] = np.repeat(np.arange(B), ql)
+        host[off["q_start"]: off["q_start"] + B + 1] = q_start
+        host[off["kv_len"]: off["kv_len"] + B] = st_np + ql
+        host[off["slots"]: off["slots"] + B] = slots
+        for g, bo in zip(cache.paged, buf.bt_off):
+            view = host[bo: bo + B * buf.max_pages].reshape(B, buf.max_pages)
+            width = min(g.table_np.shape[1], buf.max_pages)
+            view[:, :width] = g.table_np[slots, :width]
+            view[:, width:] = -1
+        rows = [int(q_start[s]) + int(w) for s, e in enumerate(entries) for w in e.want]
         R = len(rows)
-        host[off["rows"]: off["rows"] + R] = np.asarray(rows, dtype=np.int32) if R else 0
-        n_tiles = len(tiles0)
-        host[off["tile0"]: off["tile0"] + n_tiles] = np.asarray(tiles0, dtype=np.int32)
-        host[off["tilen"]: off["tilen"] + n_tiles] = np.asarray(tilesn, dtype=np.int32)
+        if R:
+            host[off["rows"]: off["rows"] + R] = rows
+        n_tiles = 0
+        if not decode_only:
+            tiles0, tilesn = [], []
+            for s, n in enumerate(q_lens):
+                t0 = int(q_start[s])
+                for a in range(0, n, ATTENTION_TILE):
+                    tiles0.append(t0 + a)
+                    tilesn.append(min(ATTENTION_TILE, n - a))
+            n_tiles = len(tiles0)
+            host[off["tile0"]: off["tile0"] + n_tiles] = tiles0
+            host[off["tilen"]: off["tilen"] + n_tiles] = tilesn
         buf.upload(i, B)
 
         d = buf.dev
-        ctx.n_tokens, ctx.n_seqs, ctx.n_rows = t, B, R
-        ctx.token_ids = d[off["tok"]: off["tok"] + t]
-        ctx.positions = d[off["pos"]: off["pos"] + t]
-        ctx.seq_of_token = d[off["seq"]: off["seq"] + t]
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_seqs, ctx.n_rows = T, B, R
+        ctx.token_ids = d[off["tok"]: off["tok"] + T]
+        ctx.positions = d[off["pos"]: off["pos"] + T]
+        ctx.seq_of_token = d[off["seq"]: off["seq"] + T]
         ctx.logit_rows = d[off["rows"]: off["rows"] + R]
         ctx.tile_tok0 = d[off["tile0"]: off["tile0"] + n_tiles]
         ctx.tile_rows = d[off["tilen"]: off["tilen"] + n_tiles]
@@ -228,9 +225,10 @@ class Stepper:
         ctx.kv_len = d[off["kv_len"]: off["kv_len"] + B]
         ctx.state_slots = d[off["slots"]: off["slots"] + B]
         ctx.block_tables = [d[bo: bo + B * buf.max_pages].view(B, buf.max_pages) for bo in buf.bt_off]
-        ctx.max_q_len, ctx.max_kv_len = max(q_lens), max_kv
-        ctx.decode_only = all(n == 1 for n in q_lens)
-        ctx.q_lens, ctx.starts, ctx.rids, ctx.fresh = q_lens, starts, rids, fresh
+        ctx.max_q_len, ctx.max_kv_len = max(q_lens), int((st_np + ql).max())
+        ctx.decode_only = decode_only
+        ctx.q_lens, ctx.starts, ctx.rids = q_lens, starts, rids
+        ctx.fresh = [st == 0 for st in starts]
         return ctx
 
     def commit(self, ctx: StepContext) -> None:

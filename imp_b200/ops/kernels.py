@@ -203,6 +203,23 @@ def gemm_bf16_small_m(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> to
     return out
 
 
+def gemm_bf16_stream(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16 on the tensor cores, streaming w once.  Falls back to
+    the scalar-load kernel when K or the row strides do not allow 16-byte loads."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and M <= SMALL_M_MAX
+    assert a.dtype == w.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    rc = L.load().imp_gemm_bf16_stream(out.data_ptr(), out.stride(0), _dt(out), a.data_ptr(), a.stride(0),
+                                       w.data_ptr(), w.stride(0), M, N, K, _stream())
+    if rc == -2:
+        return gemm_bf16_small_m(out, a, w)
+    L.check(rc, "gemm_bf16_stream")
+    return out
+
+
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
 
@@ -227,7 +244,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.bfloat16:
         raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
     if M <= SMALL_M_MAX:
-        return gemm_bf16_small_m(out, x, w)
+        return gemm_bf16_stream(out, x, w)
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:

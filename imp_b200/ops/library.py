@@ -45,6 +45,8 @@ _SIGNATURES = {
     "imp_gemm_f32": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "imp_gemm_bf16_small_m": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
                                       c_int, c_void_p]),
+    "imp_gemm_bf16_stream": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
+                                     c_int, c_void_p]),
     "imp_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "imp_apply_penalties": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p]),

@@ -143,6 +143,26 @@ def test_gemm_bf16_small_m(K, M, N, K_, odtype):
     assert torch.equal(one[0], out[M - 1])                # the same bits for a row, alone or in a batch
 
 
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 13, 16])
+@pytest.mark.parametrize("N,K_", [(16, 64), (10, 64), (257, 200), (96, 4104), (50, 104), (4096, 1024)])
+@pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_stream(K, M, N, K_, odtype):
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=10).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=11).to(DEV)
+    out = K.gemm_bf16_stream(torch.full((M, N), float("nan"), dtype=odtype, device=DEV), a, w)
+    want = a.double().cpu() @ w.double().cpu().T
+    if odtype == torch.float32:
+        close(out, want, torch.float32, scale=float(want.abs().max()) * 4)
+    else:
+        close(out, want, torch.bfloat16)
+    one = K.gemm_bf16_stream(torch.empty(1, N, dtype=odtype, device=DEV), a[M - 1:M], w)
+    assert torch.equal(one[0], out[M - 1])                # the same bits for a row, alone or in a batch
+    # operands inside wider buffers (row strides that still allow 16-byte loads)
+    wide_w = torch.zeros(N, K_ + 16, dtype=torch.bfloat16, device=DEV)
+    wide_w[:, 8:8 + K_] = w
+    out2 = K.gemm_bf16_stream(torch.empty(M, N, dtype=odtype, device=DEV), a, wide_w[:, 8:8 + K_])
+    assert torch.equal(out2, out)
+
+
 def test_linear_dispatch(K):
     x = rnd(40, 96, dtype=torch.bfloat16, seed=12).to(DEV)
     w = rnd(50, 96, dtype=torch.bfloat16, seed=13).to(DEV)
