@@ -28,6 +28,8 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages,
     float scale, int window, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float q_s[ATT_MAX_DH];
     __shared__ float p_s[ATT_BLOCK];
     __shared__ int64_t off_s[ATT_BLOCK];

@@ -45,6 +45,34 @@ void imp_set_error(const char* fmt, ...);
         return 0;                                                      \
     } while (0)
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of this library starts with pdl_wait() before it touches memory an earlier kernel
+// of the stream may have written, and calls pdl_launch_dependents() so that the next kernel's
+// blocks may become resident while this one still runs (they stop at their own pdl_wait()).
+// Launched without the attribute (or after a kernel of another library) both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1 unless the environment variable IMP_B200_NO_PDL is set (read once).
+int imp_pdl_enabled();
+
+// Launch with the programmatic-stream-serialization attribute (when enabled).
+template <typename... KArgs, typename... Args>
+inline cudaError_t imp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = imp_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ void imp_report(int* status, int code) {
     if (status) atomicCAS(status, 0, code);
 }

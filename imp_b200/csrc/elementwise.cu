@@ -12,6 +12,8 @@ template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ ids, int d, int vocab, float scale,
                                  int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (int64_t)t * d;
@@ -40,39 +42,48 @@ IMP_API int imp_embedding(float* out, const void* table, const int* ids, int n_t
 }
 
 // ------------------------------------------------------------------- swiglu
-// out[t, f] = silu(gu[t, f]) * gu[t, F + f]; the activation is computed in 32-bit.
+// out[t, f] = silu(gate) * up; the activation is computed in 32-bit.  Layout of gu[t, 2F]:
+// block == 0: gate columns 0..F-1, then up columns F..2F-1;
+// block == b: gate and up interleaved in runs of b columns (b gate, b up, b gate, ...).
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_tokens, int F) {
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_tokens, int F, int block) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int64_t total = n_tokens * (int64_t)F;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / F;
         const int f = (int)(i - t * F);
-        const float g = to_float(gu[t * 2 * F + f]);
-        const float u = to_float(gu[t * 2 * F + F + f]);
+        const int gi = block ? (f / block) * 2 * block + f % block : f;
+        const int ui = block ? gi + block : F + f;
+        const float g = to_float(gu[t * 2 * F + gi]);
+        const float u = to_float(gu[t * 2 * F + ui]);
         const float a = g / (1.f + expf(-g));
         out[i] = from_float<T>(a * u);
     }
 }
 
-IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int dtype, void* stream) {
+IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int block, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(out && gate_up && F > 0, "imp_swiglu: bad argument");
+    IMP_CHECK_ARG(block >= 0 && (block == 0 || F % block == 0), "imp_swiglu: width %d is not a multiple of the interleave %d", F, block);
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t total = (int64_t)n_tokens * F;
-    const int block = 256;
-    const int grid = (int)((total + block - 1) / block < 148 * 16 ? (total + block - 1) / block : 148 * 16);
+    const int threads = 256;
+    const int grid = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == IMP_F32)
-        swiglu_kernel<float><<<grid, block, 0, s>>>((float*)out, (const float*)gate_up, n_tokens, F);
+        swiglu_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)gate_up, n_tokens, F, block);
     else
-        swiglu_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
-                                                             n_tokens, F);
+        swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
+                                                               n_tokens, F, block);
     IMP_RETURN_LAUNCH();
 }
 
 // --------------------------------------------------------------------- cast
 template <typename TS, typename TD>
 __global__ void cast_kernel(TD* __restrict__ dst, const TS* __restrict__ src, int64_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         dst[i] = from_float<TD>(to_float(src[i]));
 }

@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ C, in
                                                        const float* __restrict__ A, int64_t lda,
                                                        const float* __restrict__ W, int64_t ldw,
                                                        int M, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float As[GF_BK][GF_BM + 4];
     __shared__ float Ws[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) gemm_small_m_vec_kernel(TO* __restrict__ 
                                                                const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                const __nv_bfloat16* __restrict__ W, int64_t ldw,
                                                                int M, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int m0 = blockIdx.y * MT;
@@ -61,6 +63,8 @@ template <typename TO>
 __global__ void gemm_small_m_scalar_kernel(TO* __restrict__ C, int64_t ldc, const __nv_bfloat16* __restrict__ A,
                                            int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw, int M,
                                            int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int m = blockIdx.y;

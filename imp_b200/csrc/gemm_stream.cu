@@ -3,20 +3,30 @@
 //
 // The product is turned round: 16 weight rows are the M side of an m16n8k16 MMA and 8 tokens its N
 // side, so the weight matrix streams through the tensor cores once while the few activation rows
-// stay in L1/L2.  A CTA owns 16 weight rows; its 8 warps take the 64-wide blocks of K in turn
-// (warp w: blocks w, w+8, ...), so the CTA reads each row as contiguous 1 KiB stretches, and the
-// warps' partial sums are added through shared memory in a fixed order.  Fragments are loaded
-// straight from global memory with 16-byte loads: within a 64-block, lane t (= lane & 3) of a row
-// loads elements [16t, 16t+16), and each k-step of the MMA takes four of them on both operands,
-// which is a permutation of the contraction index and leaves the product unchanged.
-// The summation order of an output element does not depend on M.
+// stay in L2.  A tile is 16 weight rows; it is walked along K in stages of 256 elements, and a
+// stage (8 KiB of weights and the same slice of the activation rows) arrives in shared memory
+// through a 6-deep cp.async ring.  A CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ... and
+// the ring runs on across tile borders, so it keeps about 40 KiB of weight reads in flight from
+// its first instruction to its last and the kernel runs at the rate of the memory, not of its
+// round trips.  Each of the 4 warps takes one 64-wide block of every stage; within a block, lane t (= lane & 3) of a row takes elements [16t, 16t+16) for both
+// operands, which is a permutation of the contraction index and leaves the product unchanged.
+// The warps' partial sums are added through shared memory in a fixed order; the summation order
+// of an output element does not depend on M.  The first stages are requested before the kernel
+// waits for its predecessor in the stream (the weights do not depend on it).
 //
 // Reference counterpart: gemv_fp16_kernel / gemv_bf16_kernel for M == 1 (src/compute/gemm.cu:
 // 496-649, CUDA cores, one warp per output row) and cuBLASLt for 2 <= M <= 64 (:148-156).
 #include "common.cuh"
 
-constexpr int GS_WARPS = 8;
-constexpr int GS_KB = 64;   // elements of K per block
+constexpr int GS_WARPS = 4;
+constexpr int GS_KB = 64;                          // elements of K per warp and stage
+constexpr int GS_STAGE_K = GS_KB * GS_WARPS;       // 256 elements of K per stage
+constexpr int gs_stages(int nt) { return 6; }
+constexpr int GS_RED_BYTES = 4 * 8 * 32 * 4;      // reduction buffer: 4 warps x (up to 8 slots) x 32 lanes
+constexpr int GS_ROW_BYTES = GS_STAGE_K * 2 + 16;  // 528: rows 16 bytes apart modulo 128 -> conflict-free 16-byte reads
+constexpr int GS_W_BYTES = 16 * GS_ROW_BYTES;      // weight part of a stage; 8*NT activation rows follow
+constexpr int gs_stage_bytes(int nt) { return (16 + 8 * nt) * GS_ROW_BYTES; }
+constexpr int gs_smem_bytes(int nt) { return gs_stages(nt) * gs_stage_bytes(nt) + GS_RED_BYTES; }
 
 __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -25,85 +35,187 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 gs_ld_stream(const __nv_bfloat16* p) {
-    // weights are read once: keep them from displacing the activations in L1
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 fills the destination with zeros.
+__device__ __forceinline__ void gs_cp_async(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void gs_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void gs_wait_group() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-template <int NT, typename TO>
+// SWIGLU: the 16 rows of a CTA are 8 gate rows followed by their 8 up rows (the caller interleaves
+// the two matrices in blocks of 8 rows), so accumulator slots c and c+2 of a lane hold gate and up
+// of the same output column and token; the epilogue writes silu(gate) * up into C[M, N/2].
+template <int NT, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restrict__ C, int64_t ldc,
                                                                     const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                     const __nv_bfloat16* __restrict__ W, int64_t ldw,
                                                                     int M, int N, int K) {
-    __shared__ float red[GS_WARPS][NT * 4][32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ __align__(128) unsigned char gs_smem[];
+    constexpr int STAGES = gs_stages(NT);
+    constexpr int STAGE_BYTES = gs_stage_bytes(NT);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
-    const __nv_bfloat16* w0 = W + (int64_t)min(n0 + g, N - 1) * ldw + 16 * t;
-    const __nv_bfloat16* w1 = W + (int64_t)min(n0 + g + 8, N - 1) * ldw + 16 * t;
-    const __nv_bfloat16* ap[NT];
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(gs_smem);
+    float(*red)[NT * 4][32] = reinterpret_cast<float(*)[NT * 4][32]>(gs_smem + STAGES * STAGE_BYTES);
+    const int n_stages = (K + GS_STAGE_K - 1) / GS_STAGE_K;
+    const int n_tiles = (N + 15) / 16;
+    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total = my_tiles * n_stages;       // steps of this CTA: (tile, stage) pairs in order
+
+    // Producer side: step q_issue is (tile i_tile, stage i_stage).
+    int q_issue = 0, i_tile = blockIdx.x, i_stage = 0;
+    // Weight copies of a step: 16 rows x 32 chunks of 16 bytes = 512 chunks, 4 per thread; chunk c ->
+    // row c / 32, column chunk c % 32, so a warp copies one row's 512 contiguous bytes.
+    auto issue_w = [&]() {
+        if (q_issue < total) {
+            const uint32_t sbase = smem_base + (q_issue % STAGES) * STAGE_BYTES;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) ap[nt] = A + (int64_t)min(8 * nt + g, M - 1) * lda + 16 * t;
+            for (int i = 0; i < 4; ++i) {
+                const int c = tid + i * (GS_WARPS * 32);
+                const int row = c >> 5, col = c & 31;
+                const int k = i_stage * GS_STAGE_K + col * 8;
+                const __nv_bfloat16* src = W + (int64_t)min(i_tile * 16 + row, N - 1) * ldw + min(k, K - 8);
+                gs_cp_async(sbase + row * GS_ROW_BYTES + col * 16, src, k + 8 <= K ? 16 : 0);
+            }
+        }
+    };
+    // Activation copies: 8*NT rows x 32 chunks, 2*NT per thread; rows past M and columns past K are zeros.
+    auto issue_a = [&]() {
+        if (q_issue < total) {
+            const uint32_t sbase = smem_base + (q_issue % STAGES) * STAGE_BYTES + GS_W_BYTES;
+#pragma unroll
+            for (int i = 0; i < 2 * NT; ++i) {
+                const int c = tid + i * (GS_WARPS * 32);
+                const int row = c >> 5, col = c & 31;
+                const int k = i_stage * GS_STAGE_K + col * 8;
+                const __nv_bfloat16* src = A + (int64_t)min(row, M - 1) * lda + min(k, K - 8);
+                gs_cp_async(sbase + row * GS_ROW_BYTES + col * 16, src, (k + 8 <= K && row < M) ? 16 : 0);
+            }
+        }
+    };
+    auto advance = [&]() {
+        ++q_issue;
+        if (++i_stage == n_stages) { i_stage = 0; i_tile += gridDim.x; }
+    };
+    // The weights of the first steps do not depend on the kernel before this one: request them, then
+    // wait for it, then request the activations of the same steps.
+    {
+        const int q0 = q_issue, t0 = i_tile, s0 = i_stage;
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) { issue_w(); advance(); }
+        q_issue = q0; i_tile = t0; i_stage = s0;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        issue_a();
+        gs_commit();           // group s: activations of step s (group 0 also holds all the early weight copies)
+        advance();
+    }
 
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-    const int nkb = (K + GS_KB - 1) / GS_KB;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 2
-    for (int kb = warp; kb < nkb; kb += GS_WARPS) {
-        const int k = kb * GS_KB + 16 * t;             // this lane's first element of the block
-        const bool in0 = k + 8 <= K, in1 = k + 16 <= K;   // K is a multiple of 8: a chunk is all in or all out
-        const int64_t o = (int64_t)kb * GS_KB;
-        const uint4 wa0 = in0 ? gs_ld_stream(w0 + o) : zero;
-        const uint4 wa1 = in1 ? gs_ld_stream(w0 + o + 8) : zero;
-        const uint4 wb0 = in0 ? gs_ld_stream(w1 + o) : zero;
-        const uint4 wb1 = in1 ? gs_ld_stream(w1 + o + 8) : zero;
-        uint4 x0[NT], x1[NT];
+    int c_tile = blockIdx.x, c_stage = 0;      // consumer side
+    for (int q = 0; q < total; ++q) {
+        gs_wait_group<STAGES - 2>();   // step q has landed (for this thread's copies)
+        __syncthreads();               // ... and for everyone's; the slot of step q-1 is free again
+        issue_w();
+        issue_a();
+        gs_commit();                   // an empty group keeps the group count in step with the step count
+        advance();
+        const unsigned char* sp = gs_smem + (q % STAGES) * STAGE_BYTES + warp * (GS_KB * 2) + 32 * t;
+        const uint4 wa0 = *reinterpret_cast<const uint4*>(sp + g * GS_ROW_BYTES);
+        const uint4 wa1 = *reinterpret_cast<const uint4*>(sp + g * GS_ROW_BYTES + 16);
+        const uint4 wb0 = *reinterpret_cast<const uint4*>(sp + (g + 8) * GS_ROW_BYTES);
+        const uint4 wb1 = *reinterpret_cast<const uint4*>(sp + (g + 8) * GS_ROW_BYTES + 16);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            x0[nt] = in0 ? *reinterpret_cast<const uint4*>(ap[nt] + o) : zero;
-            x1[nt] = in1 ? *reinterpret_cast<const uint4*>(ap[nt] + o + 8) : zero;
+            const uint4 c0 = *reinterpret_cast<const uint4*>(sp + GS_W_BYTES + (8 * nt + g) * GS_ROW_BYTES);
+            const uint4 c1 = *reinterpret_cast<const uint4*>(sp + GS_W_BYTES + (8 * nt + g) * GS_ROW_BYTES + 16);
+            gs_mma(acc[nt], wa0.x, wb0.x, wa0.y, wb0.y, c0.x, c0.y);
+            gs_mma(acc[nt], wa0.z, wb0.z, wa0.w, wb0.w, c0.z, c0.w);
+            gs_mma(acc[nt], wa1.x, wb1.x, wa1.y, wb1.y, c1.x, c1.y);
+            gs_mma(acc[nt], wa1.z, wb1.z, wa1.w, wb1.w, c1.z, c1.w);
         }
+        if (++c_stage < n_stages) continue;
+        // ---- the tile is complete: add the four warps' sums in a fixed order and write ------------------
+        const int n0 = c_tile * 16;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            gs_mma(acc[nt], wa0.x, wb0.x, wa0.y, wb0.y, x0[nt].x, x0[nt].y);
-            gs_mma(acc[nt], wa0.z, wb0.z, wa0.w, wb0.w, x0[nt].z, x0[nt].w);
-            gs_mma(acc[nt], wa1.x, wb1.x, wa1.y, wb1.y, x1[nt].x, x1[nt].y);
-            gs_mma(acc[nt], wa1.z, wb1.z, wa1.w, wb1.w, x1[nt].z, x1[nt].w);
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                red[warp][nt * 4 + c][lane] = acc[nt][c];
+                acc[nt][c] = 0.f;
+            }
+        __syncthreads();
+        if (SWIGLU) {
+            // 8 columns x 8*NT tokens; thread i takes (tile nt, slot c in {0,1}) = i / 32 and lane i % 32.
+            for (int i = tid; i < NT * 64; i += GS_WARPS * 32) {
+                const int r = i >> 5, l = i & 31;
+                const int nt = r >> 1, c = r & 1;
+                float gate = 0.f, up = 0.f;
+#pragma unroll
+                for (int w = 0; w < GS_WARPS; ++w) {
+                    gate += red[w][nt * 4 + c][l];
+                    up += red[w][nt * 4 + c + 2][l];
+                }
+                const int col = c_tile * 8 + (l >> 2);
+                const int tok = 8 * nt + 2 * (l & 3) + c;
+                if (n0 + (l >> 2) + 8 < N && tok < M)
+                    C[(int64_t)tok * ldc + col] = from_float<TO>(gate / (1.f + expf(-gate)) * up);
+            }
+        } else {
+            // 16 rows x 8*NT tokens = NT*128 sums; thread i takes register slot i / 32 of lane i % 32.
+            for (int i = tid; i < NT * 128; i += GS_WARPS * 32) {
+                const int r = i >> 5, l = i & 31;
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < GS_WARPS; ++w) s += red[w][r][l];
+                const int nt = r >> 2, c = r & 3;
+                const int row = n0 + (l >> 2) + ((c & 2) ? 8 : 0);
+                const int tok = 8 * nt + 2 * (l & 3) + (c & 1);
+                if (row < N && tok < M) C[(int64_t)tok * ldc + row] = from_float<TO>(s);
+            }
         }
+        c_stage = 0;
+        c_tile += gridDim.x;
+        // `red` is written again only after the next tile's steps, each of which passes a barrier
     }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) red[warp][nt * 4 + c][lane] = acc[nt][c];
-    __syncthreads();
-    // 16 rows x 8*NT tokens = NT*128 sums; thread i takes register slot i / 32 of lane i % 32.
-    for (int i = threadIdx.x; i < NT * 128; i += GS_WARPS * 32) {
-        const int r = i >> 5, l = i & 31;
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < GS_WARPS; ++w) s += red[w][r][l];
-        const int nt = r >> 2, c = r & 3;
-        const int row = n0 + (l >> 2) + ((c & 2) ? 8 : 0);
-        const int tok = 8 * nt + 2 * (l & 3) + (c & 1);
-        if (row < N && tok < M) C[(int64_t)tok * ldc + row] = from_float<TO>(s);
-    }
+    gs_wait_group<0>();
 }
 
-template <typename TO>
+template <int NT, typename TO, bool SWIGLU>
+static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+                                    int64_t ldw, int M, int N, int K, cudaStream_t s) {
+    static bool attr_set = false;   // once per instantiation (one device per process)
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gs_smem_bytes(NT));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int n_tiles = (N + 15) / 16;
+    // One tile per CTA measured faster than two persistent CTAs per SM on every shape of the 8B model
+    // (the kernel itself takes any grid size: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...).
+    const int grid = n_tiles;
+    return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU>, dim3(grid), dim3(GS_WARPS * 32), gs_smem_bytes(NT), s, C, ldc,
+                      A, lda, W, ldw, M, N, K);
+}
+
+template <typename TO, bool SWIGLU>
 static int launch_stream(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W, int64_t ldw,
                          int M, int N, int K, cudaStream_t s) {
-    const int grid = (N + 15) / 16;
-    if (M <= 8)
-        gemm_stream_kernel<1, TO><<<grid, GS_WARPS * 32, 0, s>>>(C, ldc, A, lda, W, ldw, M, N, K);
-    else
-        gemm_stream_kernel<2, TO><<<grid, GS_WARPS * 32, 0, s>>>(C, ldc, A, lda, W, ldw, M, N, K);
+    const cudaError_t e = (M <= 8) ? launch_stream_nt<1, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s)
+                                   : launch_stream_nt<2, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    if (e != cudaSuccess) {
+        imp_set_error("gemm_stream: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     IMP_RETURN_LAUNCH();
 }
 
@@ -118,7 +230,22 @@ IMP_API int imp_gemm_bf16_stream(void* C, int64_t ldc, int out_dtype, const void
     if (K % 8 || lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16) return IMP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == IMP_F32)
-        return launch_stream<float>((float*)C, ldc, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, M, N, K, s);
-    return launch_stream<__nv_bfloat16>((__nv_bfloat16*)C, ldc, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W,
-                                        ldw, M, N, K, s);
+        return launch_stream<float, false>((float*)C, ldc, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, M,
+                                           N, K, s);
+    return launch_stream<__nv_bfloat16, false>((__nv_bfloat16*)C, ldc, (const __nv_bfloat16*)A, lda,
+                                               (const __nv_bfloat16*)W, ldw, M, N, K, s);
+}
+
+// C[M, N/2] = silu(gate) * up where W[N, K] holds gate and up rows interleaved in blocks of 8
+// (rows 16j..16j+7 = gate rows 8j..8j+7, rows 16j+8..16j+15 = up rows 8j..8j+7); bfloat16 output.
+IMP_API int imp_gemm_bf16_stream_swiglu(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                        int M, int N, int K, void* stream) {
+    if (M == 0 || N == 0) return 0;
+    IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_stream_swiglu: bad argument");
+    IMP_CHECK_ARG(M <= 16, "imp_gemm_bf16_stream_swiglu: M %d exceeds 16", M);
+    IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_stream_swiglu: %d interleaved rows are not a multiple of 16", N);
+    IMP_CHECK_ARG(ldc >= N / 2 && lda >= K && ldw >= K, "imp_gemm_bf16_stream_swiglu: leading dimension too small");
+    if (K % 8 || lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16) return IMP_ERR_UNSUPPORTED;
+    return launch_stream<__nv_bfloat16, true>((__nv_bfloat16*)C, ldc, (const __nv_bfloat16*)A, lda,
+                                              (const __nv_bfloat16*)W, ldw, M, N, K, (cudaStream_t)stream);
 }

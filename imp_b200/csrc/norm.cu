@@ -22,6 +22,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
                                    const TW* __restrict__ w, TA* __restrict__ out,
                                    const int* __restrict__ rows, int d, float eps, float weight_offset,
                                    int write_h) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int64_t src = rows ? rows[r] : r;
@@ -44,6 +46,93 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
     }
 }
 
+// Fast path for rows of up to 8192 floats whose width is a multiple of 4: the row is read once
+// with 16-byte loads issued together, kept in registers, and written from there.  The per-thread
+// partial sums and the block reduction add in an order fixed by the width alone.
+constexpr int NORM_MAX_V4 = 8;   // float4 per thread: 256 threads x 8 x 4 = 8192 columns
+
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch,
+                                                                     const TW* __restrict__ w, TA* __restrict__ out,
+                                                                     const int* __restrict__ rows, int d, float eps,
+                                                                     float weight_offset, int write_h) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int64_t src = rows ? rows[r] : r;
+    float* hrow = h + src * d;
+    const TA* brow = branch ? branch + src * d : nullptr;
+    const int nv = d >> 2;
+    float4 v[NORM_MAX_V4], wv[NORM_MAX_V4];
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_V4; ++i) {
+        const int c = threadIdx.x + i * NORM_BLOCK;
+        if (c < nv) {
+            v[i] = Vec4<float>::load(hrow + 4 * c);
+            wv[i] = Vec4<TW>::load(w + 4 * c);
+        }
+    }
+    if (brow) {
+#pragma unroll
+        for (int i = 0; i < NORM_MAX_V4; ++i) {
+            const int c = threadIdx.x + i * NORM_BLOCK;
+            if (c < nv) {
+                const float4 b = Vec4<TA>::load(brow + 4 * c);
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_V4; ++i) {
+        const int c = threadIdx.x + i * NORM_BLOCK;
+        if (c < nv) {
+            if (write_h && brow) Vec4<float>::store(hrow + 4 * c, v[i]);
+            ss += v[i].x * v[i].x;
+            ss += v[i].y * v[i].y;
+            ss += v[i].z * v[i].z;
+            ss += v[i].w * v[i].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    TA* orow = out + (int64_t)r * d;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_V4; ++i) {
+        const int c = threadIdx.x + i * NORM_BLOCK;
+        if (c < nv) {
+            float4 o;
+            o.x = v[i].x * inv * (wv[i].x + weight_offset);
+            o.y = v[i].y * inv * (wv[i].y + weight_offset);
+            o.z = v[i].z * inv * (wv[i].z + weight_offset);
+            o.w = v[i].w * inv * (wv[i].w + weight_offset);
+            Vec4<TA>::store(orow + 4 * c, o);
+        }
+    }
+}
+
 IMP_API int imp_add_rmsnorm(float* h, const void* branch, const void* w, void* out, const int* rows,
                             int n_out_rows, int d, float eps, float weight_offset, int act_dtype,
                             int w_dtype, int write_h, void* stream) {
@@ -51,9 +140,17 @@ IMP_API int imp_add_rmsnorm(float* h, const void* branch, const void* w, void* o
     IMP_CHECK_ARG(h && w && out && d > 0, "imp_add_rmsnorm: bad argument");
     IMP_CHECK_ARG(!(rows && write_h), "imp_add_rmsnorm: write_h with a row list is not allowed");
     cudaStream_t s = (cudaStream_t)stream;
-#define LAUNCH(TA, TW)                                                                               \
-    add_rmsnorm_kernel<TA, TW><<<n_out_rows, NORM_BLOCK, 0, s>>>(h, (const TA*)branch, (const TW*)w, \
-                                                                 (TA*)out, rows, d, eps, weight_offset, write_h)
+    const bool vec = d % 4 == 0 && d <= NORM_BLOCK * NORM_MAX_V4 * 4 && (uintptr_t)h % 16 == 0 &&
+                     (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 && (!branch || (uintptr_t)branch % 16 == 0);
+#define LAUNCH(TA, TW)                                                                                     \
+    do {                                                                                                   \
+        if (vec)                                                                                           \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,        \
+                       (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h);   \
+        else                                                                                               \
+            add_rmsnorm_kernel<TA, TW><<<n_out_rows, NORM_BLOCK, 0, s>>>(                                  \
+                h, (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h);       \
+    } while (0)
     if (act_dtype == IMP_F32 && w_dtype == IMP_F32) LAUNCH(float, float);
     else if (act_dtype == IMP_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dtype == IMP_F32) LAUNCH(__nv_bfloat16, float);
@@ -67,6 +164,8 @@ template <typename TA, typename TW>
 __global__ void rmsnorm_rows_kernel(const TA* __restrict__ x, int64_t x_stride, const TW* __restrict__ w,
                                     TA* __restrict__ out, int64_t out_stride, int d, float eps,
                                     float weight_offset) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const TA* xr = x + (int64_t)blockIdx.x * x_stride;
     float ss = 0.f;

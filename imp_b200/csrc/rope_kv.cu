@@ -25,6 +25,8 @@ __global__ void qk_norm_rope_kv_kernel(
     const int* __restrict__ block_table, int bt_stride, int n_seqs,
     TA* __restrict__ k_cache, TA* __restrict__ v_cache, int page_size, int num_pages,
     int n_tokens, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int heads_per_token = Hq + 2 * Hkv;
@@ -133,7 +135,7 @@ IMP_API int imp_qk_norm_rope_kv_write(
     const int grid = (int)((units + warps - 1) / warps);
     if (cos_tab == nullptr) rot_dim = 0;
 #define LAUNCH(TA, TW)                                                                                      \
-    qk_norm_rope_kv_kernel<TA, TW><<<grid, warps * 32, 0, s>>>(                                             \
+    imp_launch(qk_norm_rope_kv_kernel<TA, TW>, dim3(grid), dim3(warps * 32), 0, s,                          \
         (TA*)qkv, row_stride, Hq, Hkv, Dh, (const TW*)q_norm_w, (const TW*)k_norm_w, eps, weight_offset,    \
         cos_tab, sin_tab, rot_dim, max_pos, positions, seq_of_token, block_table, bt_stride, n_seqs,        \
         (TA*)k_cache, (TA*)v_cache, page_size, num_pages, n_tokens, status)

@@ -3,6 +3,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 static thread_local char g_last_error[512] = "";
@@ -15,6 +16,12 @@ void imp_set_error(const char* fmt, ...) {
 }
 
 IMP_API const char* imp_last_error(void) { return g_last_error; }
+
+int imp_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) enabled = getenv("IMP_B200_NO_PDL") ? 0 : 1;
+    return enabled;
+}
 
 IMP_API int imp_abi_version(void) { return 1; }
 

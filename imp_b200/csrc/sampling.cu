@@ -78,6 +78,8 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ x, int V, f
 
 __global__ void __launch_bounds__(SAMPLE_BLOCK) argmax_kernel(const float* __restrict__ logits, int64_t ld, int V,
                                                              int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float s_val[33];
     __shared__ int s_idx[33];
     float bv;
@@ -86,10 +88,78 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK) argmax_kernel(const float* __res
     if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
-IMP_API int imp_argmax(const float* logits, int64_t ld, int n_rows, int V, int* out, void* stream) {
+// Two-stage form for large vocabularies: ARGMAX_CHUNKS blocks per row each reduce a contiguous
+// slice, a second kernel reduces the per-slice winners (lowest index on ties in both stages).
+constexpr int ARGMAX_CHUNKS = 32;
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int64_t ld, int V,
+                                                             float* __restrict__ pval, int* __restrict__ pidx) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    const int r = blockIdx.y, c = blockIdx.x;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = c * per, hi = min(V, lo + per);
+    const float* x = logits + (int64_t)r * ld;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = x[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < nwarp ? s_val[lane] : -INFINITY;
+        bi = lane < nwarp ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { pval[r * ARGMAX_CHUNKS + c] = bv; pidx[r * ARGMAX_CHUNKS + c] = bi; }
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x, lane = threadIdx.x;
+    float bv = lane < ARGMAX_CHUNKS ? pval[r * ARGMAX_CHUNKS + lane] : -INFINITY;
+    int bi = lane < ARGMAX_CHUNKS ? pidx[r * ARGMAX_CHUNKS + lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[r] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// Words of scratch (4 bytes each) imp_argmax wants for `n_rows` rows; without scratch it runs one block per row.
+IMP_API int imp_argmax_scratch_words(int n_rows) { return 2 * ARGMAX_CHUNKS * n_rows; }
+
+IMP_API int imp_argmax(const float* logits, int64_t ld, int n_rows, int V, int* out, void* scratch, void* stream) {
     if (n_rows == 0) return 0;
     IMP_CHECK_ARG(logits && out && V > 0 && ld >= V, "imp_argmax: bad argument");
-    argmax_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, out);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (scratch && V >= 8192 && n_rows <= 65535) {
+        float* pval = (float*)scratch;
+        int* pidx = (int*)scratch + (size_t)ARGMAX_CHUNKS * n_rows;
+        imp_launch(argmax_partial_kernel, dim3(ARGMAX_CHUNKS, n_rows), dim3(256), 0, s, logits, ld, V, pval, pidx);
+        imp_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)pval, (const int*)pidx, out);
+    } else {
+        argmax_kernel<<<n_rows, SAMPLE_BLOCK, 0, s>>>(logits, ld, V, out);
+    }
     IMP_RETURN_LAUNCH();
 }
 
@@ -98,6 +168,8 @@ IMP_API int imp_argmax(const float* logits, int64_t ld, int n_rows, int V, int* 
 // row r owning history[hist_start[r] .. hist_start[r+1]).
 __global__ void count_history_kernel(int* __restrict__ counts, const int* __restrict__ history,
                                      const int* __restrict__ hist_start, int V) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int b = hist_start[r], e = hist_start[r + 1];
     for (int i = b + blockIdx.x * blockDim.x + threadIdx.x; i < e; i += gridDim.x * blockDim.x) {
@@ -109,6 +181,8 @@ __global__ void count_history_kernel(int* __restrict__ counts, const int* __rest
 __global__ void apply_penalties_kernel(float* __restrict__ logits, int64_t ld, const int* __restrict__ counts,
                                        int V, const float* __restrict__ rep, const float* __restrict__ freq,
                                        const float* __restrict__ pres) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= V) return;
@@ -149,6 +223,8 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK) sample_kernel(
     const float* __restrict__ logits, int64_t ld, int V, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const float* __restrict__ uniform, int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float s_val[33];
     __shared__ int s_idx[33];
     __shared__ float scratch[33];

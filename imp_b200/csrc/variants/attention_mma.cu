@@ -257,6 +257,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
     int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
     float* __restrict__ part_ml, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float smem[];   // (WARPS-1) x (NTILES*4 + 4) x 32 floats
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
@@ -364,39 +366,60 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
     }
 }
 
-// One warp per (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-__global__ void attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t out_stride, const float* __restrict__ part_o,
-                                  const float* __restrict__ part_ml, int n_tokens, int Hq, int n_splits) {
-    const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (unit >= n_tokens * Hq) return;
+// One block per (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// Warp 0 turns the splits' (m, l) into weights in shared memory; then every thread sums its
+// dimensions over the splits in split order with independent loads.
+constexpr int MERGE_MAX_SPLITS = 256;
+
+__global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t out_stride,
+                                                         const float* __restrict__ part_o,
+                                                         const float* __restrict__ part_ml, int Hq, int n_splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float w_s[MERGE_MAX_SPLITS];
+    __shared__ float inv_s;
+    const int unit = blockIdx.x;
     const int tok = unit / Hq, head = unit - tok * Hq;
     const float* ml = part_ml + (int64_t)unit * n_splits * 2;
     const float* po = part_o + (int64_t)unit * n_splits * DH;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
-    constexpr int PER_LANE = (DH + 31) / 32;
-    float acc[PER_LANE];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, ml[2 * s]);
 #pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.f;
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float m = ml[2 * s];
-        if (m == -INFINITY) continue;
-        const float w = exp2f(m - M);
-        L += ml[2 * s + 1] * w;
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 32) {        // fixed order: chunks of 32 splits, tree inside a chunk
+            const int s = s0 + lane;
+            float w = 0.f, l = 0.f;
+            if (s < n_splits) {
+                const float m = ml[2 * s];
+                w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+                l = ml[2 * s + 1] * w;
+                w_s[s] = w;
+            }
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) {
-            const int d = lane + 32 * i;
-            if (d < DH) acc[i] += po[(int64_t)s * DH + d] * w;
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            L += l;
         }
+        if (lane == 0) inv_s = L > 0.f ? 1.f / L : 0.f;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    __syncthreads();
+    const float inv = inv_s;
     __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
-#pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) {
-        const int d = lane + 32 * i;
-        if (d < DH) o[d] = __float2bfloat16_rn(acc[i] * inv);
+    for (int d = threadIdx.x; d < DH; d += 128) {
+        float acc = 0.f;
+        int s = 0;
+        for (; s + 4 <= n_splits; s += 4) {
+            const float a0 = po[(int64_t)s * DH + d], a1 = po[(int64_t)(s + 1) * DH + d];
+            const float a2 = po[(int64_t)(s + 2) * DH + d], a3 = po[(int64_t)(s + 3) * DH + d];
+            acc += a0 * w_s[s];
+            acc += a1 * w_s[s + 1];
+            acc += a2 * w_s[s + 2];
+            acc += a3 * w_s[s + 3];
+        }
+        for (; s < n_splits; ++s) acc += po[(int64_t)s * DH + d] * w_s[s];
+        o[d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -425,7 +448,9 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
                             float scale, int window, int n_splits, float* scratch, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
-    IMP_CHECK_ARG(seq_of_token && positions && n_splits >= 1 && n_splits <= 65535, "imp_attn_decode: bad argument");
+    IMP_CHECK_ARG(seq_of_token && positions, "imp_attn_decode: null pointer");
+    IMP_CHECK_ARG(n_splits >= 1 && n_splits <= MERGE_MAX_SPLITS, "imp_attn_decode: %d key splits outside [1, %d]", n_splits,
+                  MERGE_MAX_SPLITS);
     IMP_CHECK_ARG(n_splits == 1 || scratch, "imp_attn_decode: splits need scratch memory");
     IMP_CHECK_ARG(n_tokens <= 65535, "imp_attn_decode: more than 65535 tokens");
     cudaStream_t s = (cudaStream_t)stream;
@@ -442,14 +467,13 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
     float* part_ml = scratch ? scratch + (int64_t)n_tokens * Hq * n_splits * DH : nullptr;
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, Hkv * tiles_per_group, n_tokens);
-    attn_decode_kernel<<<grid, WARPS * 32, smem, s>>>(
+    imp_launch(attn_decode_kernel, grid, dim3(WARPS * 32), smem, s,
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages,
         scale_log2, window, n_splits, part_o, part_ml, status);
     if (n_splits > 1) {
-        const int units = n_tokens * Hq;
-        attn_merge_kernel<<<(units + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, part_o, part_ml, n_tokens, Hq,
-                                                          n_splits);
+        imp_launch(attn_merge_kernel, dim3(n_tokens * Hq), dim3(128), 0, s, (__nv_bfloat16*)out, out_stride,
+                   (const float*)part_o, (const float*)part_ml, Hq, n_splits);
     }
     IMP_RETURN_LAUNCH();
 }
@@ -464,6 +488,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv,
     int P, int num_pages, float scale_log2, int window, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int64_t unit = (int64_t)blockIdx.x * WARPS + warp;

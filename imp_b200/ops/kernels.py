@@ -69,13 +69,47 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: 
     return out
 
 
-def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+def swiglu(out: torch.Tensor, gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """out[t, f] = silu(gate) * up.  interleave == 0: gate_up holds gate columns then up columns;
+    interleave == b: runs of b gate columns and b up columns alternate."""
     _need_cuda(out, gate_up)
     T, F = out.shape
     assert gate_up.shape == (T, 2 * F) and gate_up.dtype == out.dtype
     assert out.is_contiguous() and gate_up.is_contiguous()
-    L.check(L.load().imp_swiglu(out.data_ptr(), gate_up.data_ptr(), T, F, _dt(out), _stream()), "swiglu")
+    L.check(L.load().imp_swiglu(out.data_ptr(), gate_up.data_ptr(), T, F, int(interleave), _dt(out), _stream()),
+            "swiglu")
     return out
+
+
+SWIGLU_INTERLEAVE = 8   # rows of gate, then rows of up, alternating, for the fused matrix product
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stack gate[F, d] and up[F, d] as runs of 8 gate rows and their 8 up rows (F a multiple of 8)."""
+    F, d = gate.shape
+    b = SWIGLU_INTERLEAVE
+    assert up.shape == gate.shape and F % b == 0
+    return torch.stack([gate.view(F // b, b, d), up.view(F // b, b, d)], dim=1).reshape(2 * F, d).contiguous()
+
+
+def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """out[M, F] = silu(x Wg^T) * (x Wu^T) with Wg and Wu interleaved by `interleave_gate_up`.
+    Few bfloat16 rows: one fused kernel; otherwise the product, then the activation kernel."""
+    M = x.shape[0]
+    F = out.shape[1]
+    if M == 0:
+        return out
+    if x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and M <= SMALL_M_MAX and out.dtype == x.dtype:
+        assert x.stride(1) == 1 and w_interleaved.stride(1) == 1 and out.stride(1) == 1
+        rc = L.load().imp_gemm_bf16_stream_swiglu(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0),
+                                                  w_interleaved.data_ptr(), w_interleaved.stride(0), M, 2 * F,
+                                                  x.shape[1], _stream())
+        if rc != -2:
+            L.check(rc, "gemm_bf16_stream_swiglu")
+            return out
+    gu = torch.empty((M, 2 * F), dtype=x.dtype, device=x.device)
+    linear(gu, x, w_interleaved)
+    return swiglu(out, gu, SWIGLU_INTERLEAVE)
 
 
 def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
@@ -258,7 +292,10 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
-    L.check(L.load().imp_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _stream()), "argmax")
+    lib = L.load()
+    scratch = torch.empty(lib.imp_argmax_scratch_words(R), dtype=torch.int32, device=logits.device) if V >= 8192 else None
+    L.check(lib.imp_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _ptr(scratch), _stream()),
+            "argmax")
     return out
 
 

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "imp_device_arch": (c_int, []),
     "imp_device_sm_count": (c_int, []),
     "imp_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
-    "imp_swiglu": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "imp_swiglu": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "imp_cast": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p]),
     "imp_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
                                 c_int, c_int, c_int, c_void_p]),
@@ -47,7 +47,10 @@ _SIGNATURES = {
                                       c_int, c_void_p]),
     "imp_gemm_bf16_stream": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
                                      c_int, c_void_p]),
-    "imp_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "imp_gemm_bf16_stream_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
+                                            c_int, c_void_p]),
+    "imp_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "imp_argmax_scratch_words": (c_int, [c_int]),
     "imp_apply_penalties": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p]),
     "imp_sample": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -186,16 +186,25 @@ class SwiGLU(FeedForward):
     def __init__(self, params, tensors, rt):
         super().__init__(params, tensors, rt)
         self.f = int(params["intermediate_size"])
-        self.w_gu = _cat_rows([tensors["gate_proj"], tensors["up_proj"]])
+        gate, up = tensors["gate_proj"], tensors["up_proj"]
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        # Gate and up rows alternate in runs of 8 so that one kernel can produce the activation
+        # from the fused product; a width that is no multiple of 8 keeps the two halves apart.
+        self.interleaved = self.f % K.SWIGLU_INTERLEAVE == 0
+        self.w_gu = K.interleave_gate_up(gate, up) if self.interleaved else _cat_rows([gate, up])
         self.w_down = tensors["down_proj"]
         tensors.clear()
 
     def forward(self, x, ctx):
         rt, T = self.rt, x.shape[0]
-        gu = rt.empty((T, 2 * self.f))
-        K.linear(gu, x, self.w_gu)
         act = rt.empty((T, self.f))
-        K.swiglu(act, gu)
+        if self.interleaved:
+            K.linear_swiglu(act, x, self.w_gu)
+        else:
+            gu = rt.empty((T, 2 * self.f))
+            K.linear(gu, x, self.w_gu)
+            K.swiglu(act, gu)
         out = rt.empty((T, self.w_down.shape[0]))
         return K.linear(out, act, self.w_down)
 

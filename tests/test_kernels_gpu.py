@@ -104,6 +104,13 @@ def test_swiglu_and_cast(K, dtype):
     K.swiglu(out, gu)
     g, u = gu.double().cpu()[:, :F], gu.double().cpu()[:, F:]
     close(out, g / (1 + torch.exp(-g)) * u, dtype)
+    # interleaved layout: runs of 8 gate columns and 8 up columns alternate
+    F8 = 336
+    gu8 = rnd(T, 2 * F8, dtype=dtype, seed=8, scale=3.0)
+    g8 = gu8.view(T, F8 // 8, 2, 8)[:, :, 0, :].reshape(T, F8).double()
+    u8 = gu8.view(T, F8 // 8, 2, 8)[:, :, 1, :].reshape(T, F8).double()
+    out8 = K.swiglu(torch.empty(T, F8, dtype=dtype, device=DEV), gu8.to(DEV), 8)
+    close(out8, g8 / (1 + torch.exp(-g8)) * u8, dtype)
     src = rnd(1001, seed=7).to(DEV)
     b = K.cast(torch.empty(1001, dtype=torch.bfloat16, device=DEV), src)
     assert torch.equal(b.cpu(), src.cpu().to(torch.bfloat16))
@@ -161,6 +168,20 @@ def test_gemm_bf16_stream(K, M, N, K_, odtype):
     wide_w[:, 8:8 + K_] = w
     out2 = K.gemm_bf16_stream(torch.empty(M, N, dtype=odtype, device=DEV), a, wide_w[:, 8:8 + K_])
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16, 40])
+@pytest.mark.parametrize("F,K_", [(8, 64), (200, 96), (3072, 1024), (24, 100)])
+def test_linear_swiglu_fused(K, M, F, K_):
+    x = rnd(M, K_, dtype=torch.bfloat16, seed=30).to(DEV)
+    wg = rnd(F, K_, dtype=torch.bfloat16, seed=31, scale=0.3).to(DEV)
+    wu = rnd(F, K_, dtype=torch.bfloat16, seed=32, scale=0.3).to(DEV)
+    w = K.interleave_gate_up(wg, wu)
+    assert torch.equal(w[:8], wg[:8]) and torch.equal(w[8:16], wu[:8])
+    out = K.linear_swiglu(torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV), x, w)
+    g = x.double().cpu() @ wg.double().cpu().T
+    u = x.double().cpu() @ wu.double().cpu().T
+    close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
 
 
 def test_linear_dispatch(K):
