@@ -556,3 +556,46 @@ IMP_API int imp_attn_prefill(void* out, int64_t out_stride, const void* q, int64
         Hq, Hkv, P, num_pages, scale * 1.4426950408889634f, window, status);
     IMP_RETURN_LAUNCH();
 }
+
+// ================================================================== decode without allocation
+// See attention_noalloc.h.  The scratch of the split-key decode kernel lives in the library image.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[IMP_ATTN_NOALLOC_SCRATCH_FLOATS];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address: the
+// address is looked up once per device, with that device current, and kept here.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+IMP_API int imp_attn_decode_noalloc(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_table, int bt_stride, const int* seq_of_token,
+                                    const int* positions, int n_tokens, int n_seqs, int n_q_heads, int n_kv_heads,
+                                    int page_size, int num_pages, float scale, int window, int n_splits, int* status,
+                                    void* stream) {
+    IMP_CHECK_ARG(n_tokens >= 0 && n_q_heads > 0 && n_splits >= 1, "imp_attn_decode_noalloc: bad argument");
+    const int64_t need = n_splits > 1 ? (int64_t)n_tokens * n_q_heads * n_splits * (DH + 2) : 0;
+    IMP_CHECK_ARG(need <= IMP_ATTN_NOALLOC_SCRATCH_FLOATS,
+                  "imp_attn_decode_noalloc: %lld floats of scratch needed (tokens %d x heads %d x splits %d x %d), the "
+                  "built-in buffer holds %d; use fewer splits or imp_attn_decode with your own scratch",
+                  (long long)need, n_tokens, n_q_heads, n_splits, DH + 2, IMP_ATTN_NOALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        imp_set_error("imp_attn_decode_noalloc: cannot identify the current device (%s)",
+                      e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+        return e != cudaSuccess ? (int)e : IMP_ERR_ARG;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {   // first call on this device
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            imp_set_error("imp_attn_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : IMP_ERR_ARG;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    return imp_attn_decode(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, seq_of_token,
+                           positions, n_tokens, n_seqs, n_q_heads, n_kv_heads, page_size, num_pages, scale, window,
+                           n_splits, g_noalloc_ptr[dev], status, stream);
+}
