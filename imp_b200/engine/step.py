@@ -45,7 +45,7 @@ class StepContext:
 
     __slots__ = ("n_tokens", "n_seqs", "n_rows", "token_ids", "positions", "seq_of_token", "logit_rows",
                  "q_start", "kv_len", "state_slots", "block_tables", "max_q_len", "max_kv_len", "decode_only",
-                 "q_lens", "starts", "rids", "fresh", "tile_tok0", "tile_rows")
+                 "q_lens", "starts", "rids", "fresh", "slots", "tile_tok0", "tile_rows")
 
 
 class BatchBuffers:
@@ -229,6 +229,7 @@ class Stepper:
         ctx.decode_only = decode_only
         ctx.q_lens, ctx.starts, ctx.rids = q_lens, starts, rids
         ctx.fresh = [st == 0 for st in starts]
+        ctx.slots = [int(x) for x in slots]
         return ctx
 
     def commit(self, ctx: StepContext) -> None:
