@@ -63,6 +63,32 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
     }
 }
 
+// bfloat16, F a multiple of 8, 16-byte aligned rows: a thread turns 8 gate and 8 up values into 8 outputs.
+__global__ void swiglu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
+                                       int64_t n_tokens, int F, int block) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = n_tokens * (int64_t)(F >> 3);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / (F >> 3);
+        const int f = (int)(i - t * (F >> 3)) << 3;
+        const int gi = block ? (f / block) * 2 * block + f % block : f;   // block is a multiple of 8 here
+        const int ui = block ? gi + block : F + f;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * F + gi);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * F + ui);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * F + f) = ov;
+    }
+}
+
 IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int block, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(out && gate_up && F > 0, "imp_swiglu: bad argument");
@@ -71,7 +97,11 @@ IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int 
     const int64_t total = (int64_t)n_tokens * F;
     const int threads = 256;
     const int grid = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == IMP_F32)
+    if (dtype == IMP_BF16 && F % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+        const int64_t work = total >> 3;
+        const int g8 = (int)((work + threads - 1) / threads < 148 * 32 ? (work + threads - 1) / threads : 148 * 32);
+        swiglu_bf16_vec_kernel<<<g8, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n_tokens, F, block);
+    } else if (dtype == IMP_F32)
         swiglu_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)gate_up, n_tokens, F, block);
     else
         swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,

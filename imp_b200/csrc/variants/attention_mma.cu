@@ -7,11 +7,15 @@
 //            byte is read once per group.  Splits write unnormalised partial results to scratch
 //            and a second kernel merges them.  Launch shape depends on the batch size only and
 //            key ranges are read from device memory, so a captured graph serves any context.
-//   prefill: a warp owns 16 consecutive query tokens of one sequence and one query head; it walks
-//            the cached keys from the window's start to its last token's position.
-// Keys and values are read straight from the pages into MMA fragments with 16-byte loads (no
-// shared-memory staging): the contraction index of each product is permuted so that what a lane
-// loads contiguously is what its fragment needs.  For S = Q K^T the head dimension is permuted
+//   prefill: a CTA owns up to 32 consecutive query tokens of one sequence and up to 4 query heads
+//            of one kv head (a warp: 16 tokens of one head); its warps share every staged key and
+//            value tile while they walk the cached keys from the window's start to the last
+//            token's position.
+// In the prefill kernel keys and values travel from the pages to shared memory through a cp.async
+// ring (rows padded so that fragment reads are free of bank conflicts) and are shared by the CTA's
+// warps; in the decode kernel every warp reads its own keys straight from the pages.  Either way
+// fragments are filled with 16-byte loads and no ldmatrix: the contraction index of each product is permuted so that what a lane
+// reads contiguously is what its fragment needs.  For S = Q K^T the head dimension is permuted
 // (the same permutation on Q's fragments), for O = P V the value columns are permuted and
 // un-permuted when the result is written.
 //
@@ -29,7 +33,7 @@ constexpr int DH = IMP_ATTN_DH;
 static_assert(DH % 16 == 0 && DH >= 16 && DH <= 256, "head size must be a multiple of 16 in [16, 256]");
 constexpr int KSTEPS = DH / 16;       // k-steps of the QK^T product
 constexpr int NTILES = DH / 8;        // 8-wide output tiles of the PV product
-constexpr int WARPS = 4;
+constexpr int WARPS = 4;          // decode: warps per CTA, taking 16-key steps in turn
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -104,8 +108,9 @@ __device__ __forceinline__ int64_t key_row_offset(int j, int j_min, int j_max, c
     return (((int64_t)page * Hkv + hk) * P + (j - lp * P)) * DH;
 }
 
-// Process the 16 keys j0 .. j0+15 (those beyond j_max are masked) for a 16-row tile.
-__device__ __forceinline__ void process_step(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
+// Process the 16 keys j0 .. j0+15 (those beyond j_max are masked) for a 16-row tile, reading keys and
+// values straight from the pages into fragments (the decode kernel: every warp walks keys of its own).
+__device__ __forceinline__ void process_step_global(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
                                              const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                                              const int* __restrict__ bt, int P, int Hkv, int hk, int num_pages,
                                              int j0, int j_min, int j_max, float scale_log2, int lane, int* status) {
@@ -221,6 +226,211 @@ __device__ __forceinline__ void process_step(TileState& st, const uint32_t (&qa)
     }
 }
 
+// ---------------------------------------------------------------------------- staging
+// Row strides in shared memory.  Keys: lanes (g, t) read 16 bytes at row g, byte 16t of a 64-byte
+// block, so consecutive rows must fall into the two halves of a 128-byte bank line: stride = 64
+// (mod 128).  Values: lanes (g, t) read 16 bytes at rows 2t.., byte 16g of a 128-byte block, so rows
+// two apart must be 32 bytes apart (mod 128): stride = 16 (mod 64).
+constexpr int SK = DH * 2 + ((64 - (DH * 2) % 128) + 128) % 128;
+constexpr int SV = DH * 2 + ((16 - (DH * 2) % 64) + 64) % 64;
+static_assert(SK % 128 == 64 && SV % 64 == 16 && SK % 16 == 0 && SV % 16 == 0, "padding");
+constexpr int CHUNKS_PER_ROW = DH / 8;   // 16-byte chunks of a key or value row
+
+template <int KEYS> struct StageGeom {
+    static constexpr int K_BYTES = KEYS * SK;
+    static constexpr int BYTES = KEYS * (SK + SV);
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// All THREADS threads of the CTA copy keys and values j0 .. j0+KEYS-1 of kv head hk into one stage.
+// Keys outside [j_min, j_max] (masked for every row of the CTA; their pages may be gone) become zeros.
+// A bad page id is reported and the row zero-filled.
+template <int KEYS, int THREADS>
+__device__ __forceinline__ void load_stage(uint32_t stage_addr, const __nv_bfloat16* __restrict__ kc,
+                                           const __nv_bfloat16* __restrict__ vc, const int* __restrict__ bt, int P,
+                                           int Hkv, int hk, int num_pages, int j0, int j_min, int j_max, int tid,
+                                           int* status) {
+    constexpr int TOTAL = 2 * KEYS * CHUNKS_PER_ROW;
+#pragma unroll
+    for (int c0 = 0; c0 < TOTAL; c0 += THREADS) {
+        const int c = c0 + tid;
+        if (TOTAL % THREADS != 0 && c >= TOTAL) break;
+        const bool is_v = c >= KEYS * CHUNKS_PER_ROW;
+        const int cc = is_v ? c - KEYS * CHUNKS_PER_ROW : c;
+        const int row = cc / CHUNKS_PER_ROW, col = cc - row * CHUNKS_PER_ROW;
+        const int j = j0 + row;
+        bool ok = j >= j_min && j <= j_max;
+        int64_t off = 0;
+        if (ok) {
+            const int lp = j / P;
+            const int page = bt[lp];
+            if (page < 0 || page >= num_pages) {
+                imp_report(status, IMP_BAD_PAGE);
+                ok = false;
+            } else {
+                off = (((int64_t)page * Hkv + hk) * P + (j - lp * P)) * DH;
+            }
+        }
+        const uint32_t dst = stage_addr + (is_v ? KEYS * SK + row * SV : row * SK) + col * 16;
+        cp_async16(dst, (is_v ? vc : kc) + off + col * 8, ok ? 16 : 0);
+    }
+}
+
+// Fragments of one key row from shared memory (same permutation as load_row_frags).
+__device__ __forceinline__ void load_k_frags(uint32_t (&f)[KSTEPS][2], const unsigned char* row, int t) {
+#pragma unroll
+    for (int b = 0; b < DH / 32; ++b) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row + b * 64 + 16 * t);
+        f[2 * b][0] = v.x; f[2 * b][1] = v.y; f[2 * b + 1][0] = v.z; f[2 * b + 1][1] = v.w;
+    }
+    if (DH % 32) {
+        const uint2 v = *reinterpret_cast<const uint2*>(row + (DH / 32) * 64 + 8 * t);
+        f[KSTEPS - 1][0] = v.x; f[KSTEPS - 1][1] = v.y;
+    }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
+    return y;
+}
+
+// Process the 32 keys j0 .. j0+31, staged at rows 0 .. 31 of a stage, for a 16-row tile: scores
+// of all 32 keys first, one softmax update (one rescale of the accumulator), then two P V steps.
+// Scores stay unscaled; the scale (times log2 e) enters as the factor of a fused multiply-add in
+// front of ex2.  `need_mask` (warp-uniform) is false when every key is visible to every row.
+__device__ __forceinline__ void process_stage32(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
+                                                const unsigned char* __restrict__ ksm, const unsigned char* __restrict__ vsm,
+                                                int j0, float scale_log2, bool need_mask, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    // The four 8-key tiles are independent accumulation chains: walk the head dimension in the outer
+    // loop so that consecutive MMAs never wait for one another.
+#pragma unroll
+    for (int b = 0; b < DH / 32; ++b) {
+        uint4 v[4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) v[nt] = *reinterpret_cast<const uint4*>(ksm + (8 * nt + g) * SK + b * 64 + 16 * t);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+            mma_16816(s[nt], qa[2 * b][0], qa[2 * b][1], qa[2 * b][2], qa[2 * b][3], v[nt].x, v[nt].y);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+            mma_16816(s[nt], qa[2 * b + 1][0], qa[2 * b + 1][1], qa[2 * b + 1][2], qa[2 * b + 1][3], v[nt].z, v[nt].w);
+    }
+    if (DH % 32) {
+        uint2 v[4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) v[nt] = *reinterpret_cast<const uint2*>(ksm + (8 * nt + g) * SK + (DH / 32) * 64 + 8 * t);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+            mma_16816(s[nt], qa[KSTEPS - 1][0], qa[KSTEPS - 1][1], qa[KSTEPS - 1][2], qa[KSTEPS - 1][3], v[nt].x, v[nt].y);
+    }
+    if (need_mask) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = j0 + 8 * nt + 2 * t + e;
+                    if (j > rows[r].limit || j < rows[r].first) s[nt][2 * r + e] = -INFINITY;
+                }
+    }
+    float corr[2];
+    uint32_t pa[4][2];   // [n-tile][row g / row g+8] packed probabilities of keys 2t, 2t+1 of the tile
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m[r], mx);                     // unscaled running max
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;    // a row with nothing to see yet
+        const float neg = -m_use * scale_log2;
+        corr[r] = fast_exp2(fmaf(st.m[r], scale_log2, neg));      // st.m = -inf -> 0
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const float p0 = fast_exp2(fmaf(s[nt][2 * r], scale_log2, neg));
+            const float p1 = fast_exp2(fmaf(s[nt][2 * r + 1], scale_log2, neg));
+            sum += p0 + p1;
+            pa[nt][r] = pack_bf16(p0, p1);
+        }
+        st.l[r] = st.l[r] * corr[r] + sum;
+        st.m[r] = m_new;
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // the maxima seldom move after the first tiles
+#pragma unroll
+        for (int i = 0; i < NTILES; ++i) {
+            st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+            st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+        }
+    }
+    // ---- O += P V, 16 keys at a time ---------------------------------------------------------------
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t pa0 = pa[2 * h][0], pa1 = pa[2 * h][1], pa2 = pa[2 * h + 1][0], pa3 = pa[2 * h + 1][1];
+        const int r0 = 16 * h;
+        const unsigned char* vr[4] = {vsm + (r0 + 2 * t) * SV, vsm + (r0 + 2 * t + 1) * SV, vsm + (r0 + 2 * t + 8) * SV,
+                                      vsm + (r0 + 2 * t + 9) * SV};
+        int tile = 0;
+#pragma unroll
+        for (int b = 0; b < VBlocks::N64; ++b) {
+            uint4 r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint4*>(vr[k] + b * 128 + 16 * g);
+            const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+            const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+            const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+            const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+                mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                          __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+            }
+            tile += 8;
+        }
+        if (VBlocks::HAS32) {
+            const int base = VBlocks::N64 * 128;
+            uint2 r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint2*>(vr[k] + base + 8 * g);
+            const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+            const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+            const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+            const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+                mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                          __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+            }
+            tile += 4;
+        }
+        if (VBlocks::HAS16) {
+            const int base = VBlocks::N64 * 128 + VBlocks::HAS32 * 64;
+            uint32_t r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint32_t*>(vr[k] + base + 4 * g);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+                mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(r[0], r[1], sel), __byte_perm(r[2], r[3], sel));
+            }
+        }
+    }
+}
+
 // Dimension held by accumulator (tile, column c) -- the inverse of the value-column permutation.
 __device__ __forceinline__ int dim_of(int tile, int c) {
     if (tile < VBlocks::N64 * 8) return (tile >> 3) * 64 + 8 * c + (tile & 7);
@@ -297,7 +507,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
     TileState st;
     tile_init(st);
     for (int s = step_lo + warp; s < step_hi; s += WARPS)
-        process_step(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, scale_log2, lane, status);
+        process_step_global(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, scale_log2, lane, status);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -456,10 +666,10 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
     cudaStream_t s = (cudaStream_t)stream;
     const int G = Hq / Hkv;
     const int tiles_per_group = (G + 15) / 16;
-    const size_t smem = (size_t)(WARPS - 1) * (NTILES * 4 + 4) * 32 * sizeof(float);
+    constexpr int DEC_SMEM_BYTES = (WARPS - 1) * (NTILES * 4 + 4) * 32 * (int)sizeof(float);   // warp merge buffer
     static bool attr_set = false;
-    if (!attr_set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!attr_set && DEC_SMEM_BYTES > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
         if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
@@ -467,7 +677,7 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
     float* part_ml = scratch ? scratch + (int64_t)n_tokens * Hq * n_splits * DH : nullptr;
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, Hkv * tiles_per_group, n_tokens);
-    imp_launch(attn_decode_kernel, grid, dim3(WARPS * 32), smem, s,
+    imp_launch(attn_decode_kernel, grid, dim3(WARPS * 32), (size_t)DEC_SMEM_BYTES, s,
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages,
         scale_log2, window, n_splits, part_o, part_ml, status);
@@ -479,55 +689,100 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
 }
 
 // ================================================================================= prefill
-// Tiles of up to 16 consecutive query tokens of one sequence: tile_tok0[i] is the first token's
-// index in the batch, tile_rows[i] the number of tokens.  A warp owns (tile, query head);
-// warps are numbered tile-major, head-minor, so a CTA's four warps mostly share a kv head.
-__global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(
+// Tiles of up to 32 consecutive query tokens of one sequence: tile_tok0[i] is the first token's
+// index in the batch, tile_rows[i] the number of tokens.  grid (n_tiles, Hkv * ceil(G / HPC));
+// a CTA has 2 * HPC warps: warp w owns the 16 tokens of sub-tile w / HPC and query head w % HPC of
+// its head group.  Stages of 32 keys go through a three-deep ring shared by all warps.
+constexpr int PRE_KEYS = 32;
+constexpr int PRE_STAGES = 3;
+constexpr int PRE_SMEM_BYTES = PRE_STAGES * StageGeom<PRE_KEYS>::BYTES;
+
+template <int HPC>
+__global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
     __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-    const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv,
-    int P, int num_pages, float scale_log2, int window, int* status) {
+    const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_seqs, int Hq, int Hkv, int P,
+    int num_pages, float scale_log2, int window, int* status) {
     pdl_wait();
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int THREADS = 2 * HPC * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    const int64_t unit = (int64_t)blockIdx.x * WARPS + warp;
-    if (unit >= (int64_t)n_tiles * Hq) return;
-    const int tile = (int)(unit / Hq), head = (int)(unit - (int64_t)tile * Hq);
-    const int hk = head / (Hq / Hkv);
+    const int G = Hq / Hkv;
+    const int groups_per_kv = (G + HPC - 1) / HPC;
+    const int tile = blockIdx.x;
+    const int hk = blockIdx.y / groups_per_kv;
+    const int head_in_group = (blockIdx.y % groups_per_kv) * HPC + warp % HPC;
+    const int sub = warp / HPC;                       // which 16 tokens of the tile
     const int tok0 = tile_tok0[tile], n_rows = tile_rows[tile];
     const int seq = seq_of_token[tok0];
     const int pos0 = positions[tok0];
     const int pos_last = pos0 + n_rows - 1;
-    if (seq < 0 || seq >= n_seqs || pos0 < 0 || pos_last / P >= bt_stride || n_rows < 1 || n_rows > 16) {
-        if (lane == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+    if (seq < 0 || seq >= n_seqs || pos0 < 0 || pos_last / P >= bt_stride || n_rows < 1 || n_rows > 32) {
+        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;
+    const bool warp_used = head_in_group < G && sub * 16 < n_rows;
+    const int head = hk * G + head_in_group;
     RowInfo rows[2];
     const __nv_bfloat16* qrow[2];
+    int my_last = -1;                                 // last position any row of this warp may see
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const int rr = g + 8 * r;
-        const bool used = rr < n_rows;
+        const int rr = sub * 16 + g + 8 * r;
+        const bool used = warp_used && rr < n_rows;
         const int pos = pos0 + rr;
         rows[r].limit = used ? pos : -1;
         rows[r].first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         qrow[r] = used ? q + (int64_t)(tok0 + rr) * q_stride + (int64_t)head * DH : nullptr;
     }
+    if (warp_used) my_last = pos0 + min(n_rows, sub * 16 + 16) - 1;
+    const int my_first = (window > 0 && pos0 + sub * 16 - window + 1 > 0) ? pos0 + sub * 16 - window + 1 : 0;
+    const int my_lo_limit = pos0 + sub * 16;          // the smallest limit among the warp's rows
+    const int my_hi_first = (window > 0 && my_last - window + 1 > 0) ? my_last - window + 1 : 0;   // the largest first
+
+    const int first_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int j_begin = first_tile & ~(PRE_KEYS - 1);
+    const int n_stages = (pos_last - j_begin) / PRE_KEYS + 1;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw);
+#pragma unroll
+    for (int s = 0; s < PRE_STAGES - 1; ++s) {
+        if (s < n_stages)
+            load_stage<PRE_KEYS, THREADS>(ring + s * StageGeom<PRE_KEYS>::BYTES, kc, vc, bt, P, Hkv, hk, num_pages,
+                                          j_begin + PRE_KEYS * s, first_tile, pos_last, tid, status);
+        cp_commit();
+    }
     uint32_t qa[KSTEPS][4];
     load_q(qa, qrow[0], qrow[1], t4);
     TileState st;
     tile_init(st);
-    const int first_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    for (int j0 = first_tile & ~15; j0 <= pos_last; j0 += 16)
-        process_step(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, j0, first_tile, pos_last, scale_log2, lane, status);
+    for (int s = 0; s < n_stages; ++s) {
+        cp_wait<PRE_STAGES - 2>();   // stage s has landed (this thread's part)
+        __syncthreads();             // ... and everyone's; the slot of stage s-1 is free again
+        if (s + PRE_STAGES - 1 < n_stages)
+            load_stage<PRE_KEYS, THREADS>(ring + ((s + PRE_STAGES - 1) % PRE_STAGES) * StageGeom<PRE_KEYS>::BYTES, kc, vc, bt,
+                                          P, Hkv, hk, num_pages, j_begin + PRE_KEYS * (s + PRE_STAGES - 1), first_tile,
+                                          pos_last, tid, status);
+        cp_commit();
+        const int j0 = j_begin + PRE_KEYS * s;
+        const unsigned char* ksm = smem_raw + (s % PRE_STAGES) * StageGeom<PRE_KEYS>::BYTES;
+        const unsigned char* vsm = ksm + StageGeom<PRE_KEYS>::K_BYTES;
+        if (j0 <= my_last && j0 + PRE_KEYS - 1 >= my_first) {
+            // every key of the stage visible to every row of the warp: no mask needed
+            const bool need_mask = j0 + PRE_KEYS - 1 > my_lo_limit || j0 < my_hi_first;
+            process_stage32(st, qa, rows, ksm, vsm, j0, scale_log2, need_mask, lane);
+        }
+    }
+    cp_wait<0>();
+    if (!warp_used) return;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
-        const int rr = g + 8 * r;
+        const int rr = sub * 16 + g + 8 * r;
         if (rr >= n_rows) continue;
         const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
         __nv_bfloat16* o = out + (int64_t)(tok0 + rr) * out_stride + (int64_t)head * DH;
@@ -539,6 +794,30 @@ __global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(
     }
 }
 
+template <int HPC>
+static int launch_prefill(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc, const void* vc,
+                          const int* block_table, int bt_stride, const int* seq_of_token, const int* positions,
+                          const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv, int P,
+                          int num_pages, float scale, int window, int* status, cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set && PRE_SMEM_BYTES > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             PRE_SMEM_BYTES);
+        if (e != cudaSuccess) { imp_set_error("imp_attn_prefill: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    const int G = Hq / Hkv;
+    dim3 grid(n_tiles, Hkv * ((G + HPC - 1) / HPC));
+    imp_launch(attn_prefill_kernel<HPC>, grid, dim3(2 * HPC * 32), (size_t)PRE_SMEM_BYTES, s, (__nv_bfloat16*)out, out_stride,
+               (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_stride,
+               seq_of_token, positions, tile_tok0, tile_rows, n_seqs, Hq, Hkv, P, num_pages,
+               scale * 1.4426950408889634f, window, status);
+    IMP_RETURN_LAUNCH();
+}
+
+// Query tokens per tile that imp_attn_prefill expects at most.
+IMP_API int imp_attn_prefill_tile_tokens(void) { return 32; }
+
 IMP_API int imp_attn_prefill(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
                              const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                              const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles,
@@ -547,14 +826,15 @@ IMP_API int imp_attn_prefill(void* out, int64_t out_stride, const void* q, int64
     if (n_tiles == 0) return 0;
     if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
     IMP_CHECK_ARG(seq_of_token && positions && tile_tok0 && tile_rows, "imp_attn_prefill: null pointer");
-    const int64_t units = (int64_t)n_tiles * Hq;
-    const int64_t blocks = (units + WARPS - 1) / WARPS;
-    IMP_CHECK_ARG(blocks <= 0x7fffffff, "imp_attn_prefill: too many tiles");
-    attn_prefill_kernel<<<(unsigned)blocks, WARPS * 32, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
-        (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, n_tiles, n_seqs,
-        Hq, Hkv, P, num_pages, scale * 1.4426950408889634f, window, status);
-    IMP_RETURN_LAUNCH();
+    const int G = Hq / Hkv;
+    IMP_CHECK_ARG((int64_t)Hkv * ((G + 3) / 4) <= 65535, "imp_attn_prefill: too many head groups");
+    cudaStream_t s = (cudaStream_t)stream;
+#define ARGS out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, \
+             n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale, window, status, s
+    if (G == 1) return launch_prefill<1>(ARGS);
+    if (G == 2) return launch_prefill<2>(ARGS);
+    return launch_prefill<4>(ARGS);
+#undef ARGS
 }
 
 // ================================================================== decode without allocation

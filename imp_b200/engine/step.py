@@ -28,7 +28,7 @@ from ..parts.base import Runtime
 from .model import DecoderModel
 
 
-ATTENTION_TILE = 16   # query tokens per attention tile (the row count of one tensor-core tile)
+ATTENTION_TILE = 32   # query tokens per attention tile (two 16-row tensor-core tiles share staged keys)
 
 
 @dataclass
@@ -54,7 +54,7 @@ class BatchBuffers:
     Layout in int32 words, by capacity (so a view's address does not depend on the
     batch): tokens | positions | seq_of_token | logit_rows | attention tiles (first
     token, rows) | q_start | kv_len | slots | one block table [max_seqs, max_pages]
-    per cache group.  An attention tile is a run of up to 16 consecutive tokens of
+    per cache group.  An attention tile is a run of up to 32 consecutive tokens of
     one sequence.
     """
 

@@ -3,7 +3,8 @@
 float32: always the plain kernel (fixed reduction order per token).
 bfloat16: the MMA kernels of csrc/variants/attention_mma.cu, compiled on first use for the model's
 head size: the split-key decode kernel when every sequence brings one token, else the tiled
-prefill kernel (a decode token beside prompt portions is a tile of one row).
+prefill kernel (a decode token beside prompt portions is a tile of one row).  The step function
+cuts every sequence's new tokens into tiles of `engine.step.ATTENTION_TILE` = 32 tokens.
 """
 from __future__ import annotations
 
@@ -91,7 +92,7 @@ def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, 
 
 def prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,
                       tile_tok0, tile_rows, scale, window, status):
-    """Tiles of up to 16 consecutive query tokens of one sequence over the cached keys (bfloat16)."""
+    """Tiles of up to 32 consecutive query tokens of one sequence over the cached keys (bfloat16)."""
     lib = variant(head_dim)
     num_pages, hk, page_size, dh = k_cache.shape
     assert hk == n_kv_heads and dh == head_dim and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16

@@ -360,8 +360,8 @@ def test_attention_mma_every_head_size(K, Dh):
     pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
     tiles0, tilesn, t = [], [], 0
     for n in counts:
-        for a in range(0, n, 16):
-            tiles0.append(t + a); tilesn.append(min(16, n - a))
+        for a in range(0, n, 32):
+            tiles0.append(t + a); tilesn.append(min(32, n - a))
         t += n
     out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
     A.prefill_attention(out, q.reshape(T, Hq * Dh).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
