@@ -254,6 +254,30 @@ def gemm_bf16_stream(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> tor
     return out
 
 
+TC_OUT_BF16, TC_OUT_F32, TC_OUT_SWIGLU = 0, 1, 2
+
+
+def gemm_bf16_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = None,
+                 status: Optional[torch.Tensor] = None) -> bool:
+    """out = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+    epilogue: TC_OUT_BF16 / TC_OUT_F32 write [M,N]; TC_OUT_SWIGLU writes silu(gate)*up [M,N/2] for
+    interleaved gate/up rows.  Returns False when the operands' alignment rules it out."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    if epilogue is None:
+        epilogue = TC_OUT_F32 if out.dtype == torch.float32 else TC_OUT_BF16
+    assert w.shape[1] == K and a.dtype == w.dtype == torch.bfloat16
+    assert out.shape == (M, N // 2 if epilogue == TC_OUT_SWIGLU else N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    rc = L.load().imp_gemm_bf16_tc(out.data_ptr(), out.stride(0), epilogue, a.data_ptr(), a.stride(0), w.data_ptr(),
+                                   w.stride(0), M, N, K, _ptr(status), _stream())
+    if rc == -2:
+        return False
+    L.check(rc, "gemm_bf16_tc")
+    return True
+
+
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
 

@@ -184,6 +184,47 @@ def test_linear_swiglu_fused(K, M, F, K_):
     close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (1, 8, 8), (130, 264, 72), (300, 520, 200), (257, 1000, 4104),
+                                    (2048, 512, 1024)])
+@pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_tcgen05(K, M, N, K_, odtype):
+    """TMA-fed tcgen05 product: tiles cut by the matrix edges in every dimension, both output types."""
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=40).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=41).to(DEV)
+    status = K.new_status(DEV)
+    out = torch.full((M, N), float("nan"), dtype=odtype, device=DEV)
+    assert K.gemm_bf16_tc(out, a, w, None, status)
+    K.check_status(status)
+    want = a.double().cpu() @ w.double().cpu().T
+    if odtype == torch.float32:
+        close(out, want, torch.float32, scale=float(want.abs().max()) * 8)   # float32 sums of bf16 products
+    else:
+        close(out, want, torch.bfloat16)
+    # operands inside wider buffers, output into a wider buffer
+    wide_a = torch.zeros(M, K_ + 24, dtype=torch.bfloat16, device=DEV)
+    wide_a[:, 8:8 + K_] = a
+    wide_o = torch.full((M, N + 16), 7.0, dtype=odtype, device=DEV)
+    assert K.gemm_bf16_tc(wide_o[:, 8:8 + N], wide_a[:, 8:8 + K_], w, None, status)
+    K.check_status(status)
+    assert torch.equal(wide_o[:, 8:8 + N], out) and (wide_o[:, :8] == 7).all() and (wide_o[:, 8 + N:] == 7).all()
+    # a row stride that does not allow 16-byte tensor copies is declined, not mangled
+    odd = torch.zeros(M, K_ + 3, dtype=torch.bfloat16, device=DEV)
+    assert not K.gemm_bf16_tc(out, odd[:, :K_], w, None, status)
+
+
+@pytest.mark.parametrize("M,F,K_", [(200, 136, 96), (2048, 3072, 1024), (33, 8, 64)])
+def test_gemm_bf16_tcgen05_fused_swiglu(K, M, F, K_):
+    x = rnd(M, K_, dtype=torch.bfloat16, seed=42).to(DEV)
+    wg = rnd(F, K_, dtype=torch.bfloat16, seed=43, scale=0.3).to(DEV)
+    wu = rnd(F, K_, dtype=torch.bfloat16, seed=44, scale=0.3).to(DEV)
+    status = K.new_status(DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert K.gemm_bf16_tc(out, x, K.interleave_gate_up(wg, wu), K.TC_OUT_SWIGLU, status)
+    K.check_status(status)
+    g = x.double().cpu() @ wg.double().cpu().T
+    u = x.double().cpu() @ wu.double().cpu().T
+    close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
+
+
 def test_linear_dispatch(K):
     x = rnd(40, 96, dtype=torch.bfloat16, seed=12).to(DEV)
     w = rnd(50, 96, dtype=torch.bfloat16, seed=13).to(DEV)
