@@ -23,6 +23,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cstdlib>
 
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4, TC_UMMA_K = 16;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
@@ -114,6 +115,57 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Store 32 consecutive accumulator columns of one row (converted as the epilogue asks).
+template <int EPI>
+__device__ __forceinline__ void tc_store32(void* __restrict__ Cv, int64_t ldc, int row, int col0, int M, int N,
+                                           const float (&v)[32]) {
+    if (row >= M || col0 >= N) return;
+    if (EPI == TC_OUT_F32) {
+        float* dst = reinterpret_cast<float*>(Cv) + (int64_t)row * ldc + col0;
+        if (col0 + 32 <= N && (ldc % 4) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = v[i];
+        }
+    } else if (EPI == TC_OUT_BF16) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (int64_t)row * ldc + col0;
+        if (col0 + 32 <= N && (ldc % 8) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                reinterpret_cast<uint4*>(dst)[i] = o;
+            }
+        } else {
+            for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+        }
+    } else {
+        // columns 16j..16j+7 are gate, 16j+8..16j+15 the matching up: 32 columns give 16 outputs
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (int64_t)row * ldc + (col0 >> 1);
+        __align__(16) __nv_bfloat16 o[16];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float gate = v[16 * j + i], up = v[16 * j + 8 + i];
+                o[8 * j + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+            }
+        if (col0 + 32 <= N && (ldc % 8) == 0) {
+            reinterpret_cast<uint4*>(dst)[0] = *reinterpret_cast<uint4*>(&o[0]);
+            reinterpret_cast<uint4*>(dst)[1] = *reinterpret_cast<uint4*>(&o[8]);
+        } else {
+            for (int i = 0; i < 16 && col0 + 2 * i < N; ++i) dst[i] = o[i];
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------- kernel
 template <int EPI>
 __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -202,52 +254,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         for (int c = 0; c < TC_BN / 32; ++c) {
             float v[32];
             tc_ld32(lane_base + (uint32_t)(c * 32), v);
-            const int col0 = n0 + c * 32;
-            if (row >= M || col0 >= N) continue;
-            if (EPI == TC_OUT_F32) {
-                float* dst = reinterpret_cast<float*>(Cv) + (int64_t)row * ldc + col0;
-                if (col0 + 32 <= N && (ldc % 4) == 0) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                } else {
-                    for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = v[i];
-                }
-            } else if (EPI == TC_OUT_BF16) {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (int64_t)row * ldc + col0;
-                if (col0 + 32 <= N && (ldc % 8) == 0) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 o;
-                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
-                        __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                        __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                        o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                        o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                        reinterpret_cast<uint4*>(dst)[i] = o;
-                    }
-                } else {
-                    for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-                }
-            } else {
-                // columns 16j..16j+7 are gate, 16j+8..16j+15 the matching up: 32 columns give 16 outputs
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (int64_t)row * ldc + (col0 >> 1);
-                __nv_bfloat16 o[16];
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float gate = v[16 * j + i], up = v[16 * j + 8 + i];
-                        o[8 * j + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
-                    }
-                if (col0 + 32 <= N && (ldc % 8) == 0) {
-                    reinterpret_cast<uint4*>(dst)[0] = *reinterpret_cast<uint4*>(&o[0]);
-                    reinterpret_cast<uint4*>(dst)[1] = *reinterpret_cast<uint4*>(&o[8]);
-                } else {
-                    for (int i = 0; i < 16 && col0 + 2 * i < N; ++i) dst[i] = o[i];
-                }
-            }
+            tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
         }
     }
     tc_fence_before_sync();
@@ -256,6 +263,301 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         tc_fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS)
                      : "memory");
+    }
+}
+
+// ------------------------------------------------------------------- persistent kernel
+// One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (M index fastest, so the CTAs
+// running together share W tiles in L2).  Six warps: warp 0 produces (lane 0), warp 1 issues the
+// MMAs (lane 0) and owns tensor memory, warps 2-5 are the epilogue.  Tensor memory holds two
+// accumulators of 256 columns: while the epilogue warps drain one, the MMAs of the next tile fill
+// the other, so the tensor cores do not wait for stores.
+constexpr int TCP_THREADS = 192;
+constexpr int TCP_TMEM_COLS = 512;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                            const __grid_constant__ CUtensorMap map_w,
+                                                                            void* __restrict__ Cv, int64_t ldc, int M, int N,
+                                                                            int K, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
+    // bars: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
+    const int total = num_m * num_n;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * TC_STAGES), acce0 = smem_u32(bars + 2 * TC_STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 4);     // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)TCP_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // -------------------------------------------------------------- producer
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int m0 = (t % num_m) * TC_BM, n0 = (t / num_m) * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC_STAGES;
+                    ok = mbar_wait(empty0 + 8 * s, ((it / TC_STAGES) & 1u) ^ 1u, status);
+                    if (!ok) break;
+                    const uint32_t a_dst = smem_u32(tiles + s * TC_STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+                    tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+                }
+            }
+            if (!ok) {   // a bounded chance for the copies still in flight to land before the memory is released
+                for (uint32_t j = it > TC_STAGES ? it - TC_STAGES : 0; j < it; ++j)
+                    mbar_wait(full0 + 8 * (j % TC_STAGES), (j / TC_STAGES) & 1u, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            const uint32_t idesc = tc_instr_desc(TC_BM, TC_BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++local) {
+                const uint32_t buf = local & 1u;
+                ok = mbar_wait(acce0 + 8 * buf, ((local >> 1) & 1u) ^ 1u, status);   // the epilogue has drained it
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC_STAGES;
+                    ok = mbar_wait(full0 + 8 * s, (it / TC_STAGES) & 1u, status);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + s * TC_STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                        tc_mma(d_tmem, tc_smem_desc(a_addr + k * TC_UMMA_K * 2), tc_smem_desc(b_addr + k * TC_UMMA_K * 2),
+                               idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);
+                }
+                if (ok) tc_commit(accf0 + 8 * buf);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;                       // the 32 lanes of tensor memory this warp may read
+        uint32_t local = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++local) {
+            const uint32_t buf = local & 1u;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int m0 = (t % num_m) * TC_BM, n0 = (t / num_m) * TC_BN;
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
+#pragma unroll 1
+            for (int c = 0; c < TC_BN / 32; ++c) {
+                float v[32];
+                tc_ld32(taddr + (uint32_t)(c * 32), v);
+                tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * buf);    // this warp's quarter of the accumulator is free
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TCP_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------- few rows: weights on the M side
+// For 16 < M <= 128 activation rows the product is turned round, as in the decode kernel of
+// gemm_stream.cu: 128 weight rows are the M side of the MMA (one accumulator lane per weight row),
+// the activation rows its N side (BN = 64 or 128 columns of tensor memory).  A CTA streams its 128
+// weight rows through a six-deep TMA ring; with few weight-row tiles the K range is cut into
+// `splits` parts (grid.z) so that every SM pulls on the memory, each part writing a 32-bit partial
+// result that gemm_tc_reduce_kernel adds up in split order.
+// Epilogue: lane r of the accumulator is output column n0 + r, column t is token t, so consecutive
+// lanes write consecutive addresses of C[t, :].  With interleaved gate/up weight rows (SwiGLU,
+// splits == 1) lanes r and r + 8 of every 16 hold gate and up of one output column.
+constexpr int TCS_STAGES = 6;
+constexpr int TCS_W_BYTES = 128 * TC_BK * 2;   // 16 KiB
+
+template <int BN> constexpr int tcs_stage_bytes() { return TCS_W_BYTES + BN * TC_BK * 2; }
+template <int BN> constexpr int tcs_smem_bytes() { return TCS_STAGES * tcs_stage_bytes<BN>() + 1024 + 256; }
+
+// EPI: 0 = bfloat16 C[M,N], 1 = float32 C[M,N] (also the split partials), 2 = SwiGLU bfloat16 C[M,N/2]
+template <int BN, int EPI>
+__global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                              const __grid_constant__ CUtensorMap map_x, void* __restrict__ Cv,
+                                                              int64_t ldc, int64_t split_stride, int M, int N, int K,
+                                                              int kb_per_split, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int STAGE = tcs_stage_bytes<BN>();
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TCS_STAGES * STAGE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TCS_STAGES + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 128;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_lo = blockIdx.z * kb_per_split;
+    const int kb_hi = min(total_kb, kb_lo + kb_per_split);
+    const int k_blocks = max(kb_hi - kb_lo, 0);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TCS_STAGES), accum_bar = smem_u32(bars + 2 * TCS_STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TCS_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        int issued = 0;
+        bool ok = true;
+        for (int i = 0; i < k_blocks; ++i) {
+            const int s = i % TCS_STAGES;
+            ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status);
+            if (!ok) break;
+            const uint32_t w_dst = smem_u32(tiles + s * STAGE), x_dst = w_dst + TCS_W_BYTES;
+            mbar_expect_tx(full0 + 8 * s, STAGE);
+            tma_load_2d(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * s);
+            tma_load_2d(x_dst, &map_x, (kb_lo + i) * TC_BK, 0, full0 + 8 * s);
+            issued = i + 1;
+        }
+        if (!ok)
+            for (int i = issued > TCS_STAGES ? issued - TCS_STAGES : 0; i < issued; ++i)
+                mbar_wait(full0 + 8 * (i % TCS_STAGES), (uint32_t)(i / TCS_STAGES) & 1u, nullptr);
+    } else if (warp == 1 && lane == 0) {
+        const uint32_t idesc = tc_instr_desc(128, BN);
+        bool ok = true;
+        for (int i = 0; i < k_blocks && ok; ++i) {
+            const int s = i % TCS_STAGES;
+            ok = mbar_wait(full0 + 8 * s, (uint32_t)(i / TCS_STAGES) & 1u, status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t w_addr = smem_u32(tiles + s * STAGE), x_addr = w_addr + TCS_W_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                tc_mma(tmem_base, tc_smem_desc(w_addr + k * TC_UMMA_K * 2), tc_smem_desc(x_addr + k * TC_UMMA_K * 2), idesc,
+                       (i > 0 || k > 0) ? 1u : 0u);
+            tc_commit(empty0 + 8 * s);
+        }
+        tc_commit(accum_bar);
+    }
+    __syncwarp();
+
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, status));
+    tc_fence_after_sync();
+    if (acc_ok) {
+        const int r = warp * 32 + lane;             // accumulator lane = weight row of the tile
+        const int col = n0 + r;                     // output column
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            float v[32];
+            if (k_blocks > 0) {
+                tc_ld32(lane_base + (uint32_t)(c * 32), v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;   // an empty K range contributes nothing
+            }
+            if (EPI == TC_OUT_SWIGLU_BF16) {
+                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
+                const bool is_gate = (r & 8) == 0;
+                const int ocol = (col >> 4) * 8 + (r & 7);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float up = __shfl_xor_sync(0xffffffffu, v[i], 8);   // lane r + 8 holds the matching up row
+                    const int tok = c * 32 + i;
+                    if (is_gate && tok < M && col + 8 < N)
+                        base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
+                }
+            } else if (col < N) {
+                if (EPI == TC_OUT_F32) {
+                    float* base = reinterpret_cast<float*>(Cv) + (int64_t)blockIdx.z * split_stride;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int tok = c * 32 + i;
+                        if (tok < M) base[(int64_t)tok * ldc + col] = v[i];
+                    }
+                } else {
+                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int tok = c * 32 + i;
+                        if (tok < M) base[(int64_t)tok * ldc + col] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// out[m, n] = sum over splits of part[s, m, n], in split order.
+template <typename TO>
+__global__ void gemm_tc_reduce_kernel(TO* __restrict__ out, int64_t ldc, const float* __restrict__ part, int64_t split_stride,
+                                      int M, int N, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = (int64_t)M * N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / N;
+        const int n = (int)(i - m * N);
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) acc += part[s * split_stride + i];
+        out[m * ldc + n] = from_float<TO>(acc);
     }
 }
 
@@ -309,8 +611,22 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
-    gemm_tc_kernel<EPI><<<grid, 128, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
+    static int mode = -1, sms = 0;   // IMP_B200_TC_SIMPLE=1 selects the one-tile-per-CTA kernel
+    if (mode < 0) {
+        mode = getenv("IMP_B200_TC_SIMPLE") ? 1 : 0;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); mode = -1; return (int)e; }
+    }
+    const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
+    if (mode == 1) {
+        gemm_tc_kernel<EPI><<<dim3(num_m, num_n), 128, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
+    } else {
+        const int total = num_m * num_n;
+        gemm_tc_persistent_kernel<EPI><<<total < sms ? total : sms, TCP_THREADS, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
+    }
     IMP_RETURN_LAUNCH();
 }
 
@@ -333,4 +649,87 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
     if (epilogue == TC_OUT_BF16) return launch_tc<TC_OUT_BF16>(C, ldc, ma, mw, M, N, K, status, s);
     if (epilogue == TC_OUT_F32) return launch_tc<TC_OUT_F32>(C, ldc, ma, mw, M, N, K, status, s);
     return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, M, N, K, status, s);
+}
+
+// ---- few rows (16 < M <= 128) -----------------------------------------------------------------------
+// Number of K splits imp_gemm_bf16_tc_swap will use, and the floats of scratch it then needs.
+static int tcs_splits(int N, int K, int epilogue) {
+    if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        sms = 148;
+    const int tiles = (N + 127) / 128;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    int splits = (sms + tiles - 1) / tiles;              // enough CTAs for every SM
+    const int max_splits = total_kb / 8 > 0 ? total_kb / 8 : 1;   // at least 8 blocks of K per split
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 16) splits = 16;
+    return splits < 1 ? 1 : splits;
+}
+
+IMP_API int64_t imp_gemm_bf16_tc_swap_scratch_floats(int M, int N, int K, int epilogue) {
+    const int splits = tcs_splits(N, K, epilogue);
+    return splits > 1 ? (int64_t)splits * M * N : 0;
+}
+
+template <int BN, int EPI>
+static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensorMap& mw, const CUtensorMap& mx, int M, int N,
+                      int K, int splits, int kb_per_split, int* status, cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tcs_smem_bytes<BN>());
+        if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    dim3 grid((N + 127) / 128, 1, splits);
+    gemm_tc_swap_kernel<BN, EPI><<<grid, 128, tcs_smem_bytes<BN>(), s>>>(mw, mx, C, ldc, split_stride, M, N, K, kb_per_split,
+                                                                         status);
+    return 0;
+}
+
+// C = A[M,K] * W[N,K]^T for 1 <= M <= 128 with the weights on the M side of the MMA.
+// epilogue as for imp_gemm_bf16_tc.  `scratch` must hold imp_gemm_bf16_tc_swap_scratch_floats() floats.
+IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                  int M, int N, int K, float* scratch, int* status, void* stream) {
+    if (M == 0 || N == 0) return 0;
+    IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_tc_swap: bad argument");
+    IMP_CHECK_ARG(M <= 128, "imp_gemm_bf16_tc_swap: M %d exceeds 128", M);
+    IMP_CHECK_ARG(epilogue >= 0 && epilogue <= 2, "imp_gemm_bf16_tc_swap: unknown epilogue %d", epilogue);
+    if (epilogue == 2) IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_tc_swap: %d interleaved rows are not a multiple of 16", N);
+    IMP_CHECK_ARG(lda >= K && ldw >= K && ldc >= (epilogue == 2 ? N / 2 : N), "imp_gemm_bf16_tc_swap: leading dimension too small");
+    if (K % 8 || lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16) return IMP_ERR_UNSUPPORTED;
+    const int splits = tcs_splits(N, K, epilogue);
+    IMP_CHECK_ARG(splits == 1 || scratch, "imp_gemm_bf16_tc_swap: %d splits of K need scratch memory", splits);
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    const int BN = M <= 64 ? 64 : 128;
+    CUtensorMap mw, mx;
+    if (int rc = make_map(&mw, W, N, K, ldw, 128)) return rc;
+    if (int rc = make_map(&mx, A, M, K, lda, BN)) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc = 0;
+    if (splits > 1) {
+        const int64_t split_stride = (int64_t)M * N;
+        rc = BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
+                      : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s);
+        if (rc) return rc;
+        const int64_t total = (int64_t)M * N;
+        const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        if (epilogue == TC_OUT_F32)
+            gemm_tc_reduce_kernel<float><<<grid, 256, 0, s>>>((float*)C, ldc, scratch, split_stride, M, N, splits);
+        else
+            gemm_tc_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)C, ldc, scratch, split_stride, M, N, splits);
+    } else if (epilogue == TC_OUT_BF16) {
+        rc = BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+                      : launch_tcs<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+    } else if (epilogue == TC_OUT_F32) {
+        rc = BN == 64 ? launch_tcs<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+                      : launch_tcs<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+    } else {
+        rc = BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+                      : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+    }
+    if (rc) return rc;
+    IMP_RETURN_LAUNCH();
 }

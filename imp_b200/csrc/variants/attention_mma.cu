@@ -25,6 +25,8 @@
 // WMMA / CUDA-core code over the call's own K,V (prefill) or one query per sequence (decode).
 #include "../common.cuh"
 
+#include <cstdlib>
+
 #ifndef IMP_ATTN_DH
 #error "compile with -DIMP_ATTN_DH=<head size>"
 #endif
@@ -108,91 +110,123 @@ __device__ __forceinline__ int64_t key_row_offset(int j, int j_min, int j_max, c
     return (((int64_t)page * Hkv + hk) * P + (j - lp * P)) * DH;
 }
 
-// Process the 16 keys j0 .. j0+15 (those beyond j_max are masked) for a 16-row tile, reading keys and
-// values straight from the pages into fragments (the decode kernel: every warp walks keys of its own).
-__device__ __forceinline__ void process_step_global(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
-                                             const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
-                                             const int* __restrict__ bt, int P, int Hkv, int hk, int num_pages,
-                                             int j0, int j_min, int j_max, float scale_log2, int lane, int* status) {
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
+    return y;
+}
+
+// ---- decode: 16 keys at a time, straight from the pages into fragments ------------------------------
+// NR = 2: the tile's 16 rows are all in use (rows g and g+8 of every lane).  NR = 1: at most 8 query
+// heads share the kv head, rows g+8 do not exist; their half of every fragment is zero and their half
+// of the accumulator is not kept, which frees registers for more loads in flight.
+template <int NR> struct DecState {
+    float o[NTILES][2 * NR];
+    float m[NR], l[NR];     // running max (scaled, log2 domain) and lane-partial sum
+};
+struct DecLoads {
+    uint32_t kb0[KSTEPS][2], kb1[KSTEPS][2];   // key fragments of the two 8-key tiles
+    int64_t v_off[4];                          // rows of keys 2t, 2t+1, 2t+8, 2t+9 in the value cache
+};
+
+// Look the 16 keys' rows up and request their key fragments (the loads stay in flight until used).
+__device__ __forceinline__ void dec_fetch(DecLoads& L, const __nv_bfloat16* __restrict__ kc, const int* __restrict__ bt,
+                                          int P, int Hkv, int hk, int num_pages, int j0, int j_min, int j_max, int lane,
+                                          int* status) {
     const int g = lane >> 2, t = lane & 3;
     // Lanes 0..15 look up the row of key j0 + lane; the others copy what they need.
     const int64_t my_off = key_row_offset(j0 + (lane & 15), j_min, j_max, bt, P, Hkv, hk, num_pages, status);
     const int64_t k_off0 = __shfl_sync(0xffffffffu, my_off, g);
     const int64_t k_off1 = __shfl_sync(0xffffffffu, my_off, g + 8);
-    const int64_t v_off[4] = {__shfl_sync(0xffffffffu, my_off, 2 * t), __shfl_sync(0xffffffffu, my_off, 2 * t + 1),
-                              __shfl_sync(0xffffffffu, my_off, 2 * t + 8), __shfl_sync(0xffffffffu, my_off, 2 * t + 9)};
+    L.v_off[0] = __shfl_sync(0xffffffffu, my_off, 2 * t);
+    L.v_off[1] = __shfl_sync(0xffffffffu, my_off, 2 * t + 1);
+    L.v_off[2] = __shfl_sync(0xffffffffu, my_off, 2 * t + 8);
+    L.v_off[3] = __shfl_sync(0xffffffffu, my_off, 2 * t + 9);
+    load_row_frags(L.kb0, kc + k_off0, t);
+    load_row_frags(L.kb1, kc + k_off1, t);
+}
 
-    // ---- S = Q K^T for two 8-key tiles -------------------------------------------------------
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    {
-        uint32_t kb[KSTEPS][2];
-        load_row_frags(kb, kc + k_off0, t);
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) mma_16816(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][0], kb[ks][1]);
-        load_row_frags(kb, kc + k_off1, t);
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) mma_16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][0], kb[ks][1]);
+template <int NR>
+__device__ __forceinline__ void dec_mma(float (&acc)[2 * NR], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    if (NR == 2) {
+        float c[4] = {acc[0], acc[1], acc[2 * NR - 2], acc[2 * NR - 1]};
+        mma_16816(c, a0, a1, a2, a3, b0, b1);
+        acc[0] = c[0]; acc[1] = c[1]; acc[2 * NR - 2] = c[2]; acc[2 * NR - 1] = c[3];
+    } else {
+        float c[4] = {acc[0], acc[1], 0.f, 0.f};
+        mma_16816(c, a0, 0u, a2, 0u, b0, b1);
+        acc[0] = c[0]; acc[1] = c[1];
     }
-    // ---- mask, running max, probabilities -------------------------------------------------------
-    float p[2][4];
-    float corr[2];
+}
+
+// Scores, softmax update and P V for the 16 keys j0 .. j0+15 whose loads `L` holds.
+template <int NR>
+__device__ __forceinline__ void dec_compute(DecState<NR>& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
+                                            const DecLoads& L, const __nv_bfloat16* __restrict__ vc, int j0,
+                                            float scale_log2, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    // the value rows are requested first: they travel while the scores are computed
+    uint4 vr[VBlocks::N64 > 0 ? VBlocks::N64 : 1][4];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {          // r = 0: row g (c0,c1); r = 1: row g+8 (c2,c3)
+    for (int b = 0; b < VBlocks::N64; ++b)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) vr[b][k] = *reinterpret_cast<const uint4*>(vc + L.v_off[k] + b * 64 + 8 * g);
+
+    float s0[2 * NR], s1[2 * NR];
+#pragma unroll
+    for (int i = 0; i < 2 * NR; ++i) s0[i] = s1[i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        dec_mma<NR>(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], L.kb0[ks][0], L.kb0[ks][1]);
+        dec_mma<NR>(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], L.kb1[ks][0], L.kb1[ks][1]);
+    }
+    uint32_t pa[2][NR];    // [8-key tile][row] packed probabilities of keys 2t, 2t+1
+    float corr[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        float v[4] = {s0[2 * r] * scale_log2, s0[2 * r + 1] * scale_log2, s1[2 * r] * scale_log2, s1[2 * r + 1] * scale_log2};
         float mx = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = j0 + 8 * nt + 2 * t + e;
-                float v = s[nt][2 * r + e] * scale_log2;
-                if (j > rows[r].limit || j < rows[r].first) v = -INFINITY;
-                s[nt][2 * r + e] = v;
-                mx = fmaxf(mx, v);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int j = j0 + 8 * (e >> 1) + 2 * t + (e & 1);
+            if (j > rows[r].limit || j < rows[r].first) v[e] = -INFINITY;
+            mx = fmaxf(mx, v[e]);
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(st.m[r], mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // a row with nothing to see yet
-        corr[r] = exp2f(st.m[r] - m_use);                          // st.m = -inf -> 0
-        float sum = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float pv = exp2f(s[nt][2 * r + e] - m_use);
-                p[nt][2 * r + e] = pv;
-                sum += pv;
-            }
-        st.l[r] = st.l[r] * corr[r] + sum;
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[r] = fast_exp2(st.m[r] - m_use);
+        const float p0 = fast_exp2(v[0] - m_use), p1 = fast_exp2(v[1] - m_use);
+        const float p2 = fast_exp2(v[2] - m_use), p3 = fast_exp2(v[3] - m_use);
+        st.l[r] = st.l[r] * corr[r] + (p0 + p1) + (p2 + p3);
         st.m[r] = m_new;
+        pa[0][r] = pack_bf16(p0, p1);
+        pa[1][r] = pack_bf16(p2, p3);
     }
+    bool rescale = corr[0] != 1.f;
+    if (NR == 2) rescale = rescale || corr[NR - 1] != 1.f;
+    if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-    for (int i = 0; i < NTILES; ++i) {
-        st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
-        st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+        for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+            for (int c = 0; c < 2 * NR; ++c) st.o[i][c] *= corr[c >> 1];
     }
-    const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);   // row g,   keys 2t, 2t+1
-    const uint32_t pa1 = pack_bf16(p[0][2], p[0][3]);   // row g+8, keys 2t, 2t+1
-    const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);   // row g,   keys 2t+8, 2t+9
-    const uint32_t pa3 = pack_bf16(p[1][2], p[1][3]);   // row g+8, keys 2t+8, 2t+9
-
-    // ---- O += P V -----------------------------------------------------------------------------
+    const uint32_t pa0 = pa[0][0], pa2 = pa[1][0];
+    const uint32_t pa1 = NR == 2 ? pa[0][NR - 1] : 0u, pa3 = NR == 2 ? pa[1][NR - 1] : 0u;
     int tile = 0;
 #pragma unroll
     for (int b = 0; b < VBlocks::N64; ++b) {
-        uint4 r[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint4*>(vc + v_off[k] + b * 64 + 8 * g);
-        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
-        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
-        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
-        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&vr[b][0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&vr[b][1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&vr[b][2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&vr[b][3]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-            const uint32_t b0 = __byte_perm(w0[i >> 1], w1[i >> 1], sel);
-            const uint32_t b1 = __byte_perm(w2[i >> 1], w3[i >> 1], sel);
-            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, b0, b1);
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                        __byte_perm(w2[i >> 1], w3[i >> 1], sel));
         }
         tile += 8;
     }
@@ -200,7 +234,7 @@ __device__ __forceinline__ void process_step_global(TileState& st, const uint32_
         const int base = VBlocks::N64 * 64;
         uint2 r[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint2*>(vc + v_off[k] + base + 4 * g);
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint2*>(vc + L.v_off[k] + base + 4 * g);
         const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
         const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
         const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
@@ -208,8 +242,8 @@ __device__ __forceinline__ void process_step_global(TileState& st, const uint32_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
-                      __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                        __byte_perm(w2[i >> 1], w3[i >> 1], sel));
         }
         tile += 4;
     }
@@ -217,11 +251,11 @@ __device__ __forceinline__ void process_step_global(TileState& st, const uint32_
         const int base = VBlocks::N64 * 64 + VBlocks::HAS32 * 32;
         uint32_t r[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint32_t*>(vc + v_off[k] + base + 2 * g);
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint32_t*>(vc + L.v_off[k] + base + 2 * g);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-            mma_16816(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(r[0], r[1], sel), __byte_perm(r[2], r[3], sel));
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(r[0], r[1], sel), __byte_perm(r[2], r[3], sel));
         }
     }
 }
@@ -294,11 +328,6 @@ __device__ __forceinline__ void load_k_frags(uint32_t (&f)[KSTEPS][2], const uns
     }
 }
 
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
-    return y;
-}
 
 // Process the 32 keys j0 .. j0+31, staged at rows 0 .. 31 of a stage, for a 16-row tile: scores
 // of all 32 keys first, one softmax update (one rescale of the accumulator), then two P V steps.
@@ -459,9 +488,11 @@ __device__ __forceinline__ void load_q(uint32_t (&qa)[KSTEPS][4], const __nv_bfl
 }
 
 // ================================================================================== decode
-// grid (n_splits, Hkv * tiles_per_group, n_tokens), block 128.
+// grid (n_splits, Hkv * tiles_per_group, n_tokens), block 128.  Each warp takes every fourth 16-key
+// step of the CTA's split; several CTAs per SM keep enough loads in flight.
 // part_o: [n_tokens, Hq, n_splits, DH] float, part_ml: [n_tokens, Hq, n_splits, 2] float (used when n_splits > 1).
-__global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
+template <int NR>
+__global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kernel(
     __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
@@ -469,7 +500,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
     float* __restrict__ part_ml, int* status) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float smem[];   // (WARPS-1) x (NTILES*4 + 4) x 32 floats
+    extern __shared__ float smem[];   // (WARPS-1) x (NTILES*2*NR + 2*NR) x 32 floats
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int G = Hq / Hkv;
@@ -497,43 +528,54 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int hr = row0 + g + 8 * r;
-        const bool used = hr < G;
+        const bool used = r < NR && hr < G;
         rows[r].limit = used ? pos : -1;
         rows[r].first = first;
         qrow[r] = used ? q + (int64_t)tok * q_stride + (int64_t)(hk * G + hr) * DH : nullptr;
     }
+    int s = step_lo + warp;
     uint32_t qa[KSTEPS][4];
     load_q(qa, qrow[0], qrow[1], t4);
-    TileState st;
-    tile_init(st);
-    for (int s = step_lo + warp; s < step_hi; s += WARPS)
-        process_step_global(st, qa, rows, kc, vc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, scale_log2, lane, status);
+    DecState<NR> st;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+        for (int c = 0; c < 2 * NR; ++c) st.o[i][c] = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) { st.m[r] = -INFINITY; st.l[r] = 0.f; }
+    for (; s < step_hi; s += WARPS) {
+        DecLoads cur;
+        dec_fetch(cur, kc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, lane, status);
+        dec_compute<NR>(st, qa, rows, cur, vc, first16 + 16 * s, scale_log2, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
     }
     // ---- merge the four warps (fragment-wise, through shared memory) ---------------------------------
-    constexpr int PER_WARP = NTILES * 4 + 4;
+    constexpr int NACC = NTILES * 2 * NR;
+    constexpr int PER_WARP = NACC + 2 * NR;
     if (warp > 0) {
         float* dst = smem + (size_t)(warp - 1) * PER_WARP * 32;
 #pragma unroll
         for (int i = 0; i < NTILES; ++i)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dst[(i * 4 + c) * 32 + lane] = st.o[i][c];
-        dst[(NTILES * 4 + 0) * 32 + lane] = st.m[0];
-        dst[(NTILES * 4 + 1) * 32 + lane] = st.m[1];
-        dst[(NTILES * 4 + 2) * 32 + lane] = st.l[0];
-        dst[(NTILES * 4 + 3) * 32 + lane] = st.l[1];
+            for (int c = 0; c < 2 * NR; ++c) dst[(i * 2 * NR + c) * 32 + lane] = st.o[i][c];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            dst[(NACC + r) * 32 + lane] = st.m[r];
+            dst[(NACC + NR + r) * 32 + lane] = st.l[r];
+        }
     }
     __syncthreads();
     if (warp != 0) return;
     for (int w = 1; w < WARPS; ++w) {
         const float* src = smem + (size_t)(w - 1) * PER_WARP * 32;
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const float mo = src[(NTILES * 4 + r) * 32 + lane];
-            const float lo = src[(NTILES * 4 + 2 + r) * 32 + lane];
+        for (int r = 0; r < NR; ++r) {
+            const float mo = src[(NACC + r) * 32 + lane];
+            const float lo = src[(NACC + NR + r) * 32 + lane];
             const float m_new = fmaxf(st.m[r], mo);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float ca = exp2f(st.m[r] - m_use), cb = exp2f(mo - m_use);
@@ -541,14 +583,14 @@ __global__ void __launch_bounds__(WARPS * 32) attn_decode_kernel(
             st.m[r] = m_new;
 #pragma unroll
             for (int i = 0; i < NTILES; ++i) {
-                st.o[i][2 * r] = st.o[i][2 * r] * ca + src[(i * 4 + 2 * r) * 32 + lane] * cb;
-                st.o[i][2 * r + 1] = st.o[i][2 * r + 1] * ca + src[(i * 4 + 2 * r + 1) * 32 + lane] * cb;
+                st.o[i][2 * r] = st.o[i][2 * r] * ca + src[(i * 2 * NR + 2 * r) * 32 + lane] * cb;
+                st.o[i][2 * r + 1] = st.o[i][2 * r + 1] * ca + src[(i * 2 * NR + 2 * r + 1) * 32 + lane] * cb;
             }
         }
     }
     // ---- write: final output, or this split's partial ---------------------------------------------
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
         const int hr = row0 + g + 8 * r;
         if (hr >= G) continue;
         const int head = hk * G + hr;
@@ -652,6 +694,366 @@ IMP_API int64_t imp_attn_decode_scratch_floats(int n_tokens, int Hq, int n_split
     return n_splits > 1 ? (int64_t)n_tokens * Hq * n_splits * (DH + 2) : 0;
 }
 
+// ------------------------------------------------------------------ decode, bulk-copy ring
+// The same split-key decode for page sizes that are multiples of 16: the 16 keys of a step then lie
+// in one page, 16 consecutive rows of a kv head = one contiguous run of 32*DH bytes for keys and one
+// for values.  A fifth warp's lane 0 is the producer: per stage of 64 keys it issues up to eight
+// cp.async.bulk copies (global -> shared, completion counted in bytes on the stage's mbarrier) into
+// a three-deep ring; the four consumer warps each take one 16-key step of the stage from shared
+// memory and hand the stage back through a second mbarrier.  A CTA so keeps two stages (up to
+// 64 x DH x 4 bytes each) in flight without holding them in registers.  Every wait is bounded
+// (IMP_WAIT_TIMEOUT in the status word, then the CTA drains and leaves).
+constexpr int DT_KEYS = 64, DT_STAGES = 3, DT_CONSUMERS = 4;
+constexpr int DT_RUN_BYTES = 16 * DH * 2;                 // keys (or values) of one step
+constexpr int DT_STAGE_BYTES = 2 * DT_CONSUMERS * DT_RUN_BYTES;
+constexpr uint32_t DT_WAIT_LIMIT = 1u << 20;
+
+__device__ __forceinline__ bool dt_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (uint32_t i = 0; i < DT_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    imp_report(status, IMP_WAIT_TIMEOUT);
+    return false;
+}
+
+// Scores, softmax update and P V for 16 keys whose rows lie at `ksm` / `vsm` (16 rows of DH bfloat16).
+template <int NR>
+__device__ __forceinline__ void dec_compute_smem(DecState<NR>& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
+                                                 const unsigned char* __restrict__ ksm, const unsigned char* __restrict__ vsm,
+                                                 int j0, float scale_log2, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int RB = DH * 2;   // bytes per row
+    float s0[2 * NR], s1[2 * NR];
+#pragma unroll
+    for (int i = 0; i < 2 * NR; ++i) s0[i] = s1[i] = 0.f;
+    {
+        uint32_t k0[KSTEPS][2], k1[KSTEPS][2];
+        load_row_frags(k0, reinterpret_cast<const __nv_bfloat16*>(ksm + g * RB), t);
+        load_row_frags(k1, reinterpret_cast<const __nv_bfloat16*>(ksm + (g + 8) * RB), t);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            dec_mma<NR>(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], k0[ks][0], k0[ks][1]);
+            dec_mma<NR>(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], k1[ks][0], k1[ks][1]);
+        }
+    }
+    uint32_t pa[2][NR];
+    float corr[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        float v[4] = {s0[2 * r] * scale_log2, s0[2 * r + 1] * scale_log2, s1[2 * r] * scale_log2, s1[2 * r + 1] * scale_log2};
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = j0 + 8 * (e >> 1) + 2 * t + (e & 1);
+            if (j > rows[r].limit || j < rows[r].first) v[e] = -INFINITY;
+            mx = fmaxf(mx, v[e]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m[r], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[r] = fast_exp2(st.m[r] - m_use);
+        const float p0 = fast_exp2(v[0] - m_use), p1 = fast_exp2(v[1] - m_use);
+        const float p2 = fast_exp2(v[2] - m_use), p3 = fast_exp2(v[3] - m_use);
+        st.l[r] = st.l[r] * corr[r] + (p0 + p1) + (p2 + p3);
+        st.m[r] = m_new;
+        pa[0][r] = pack_bf16(p0, p1);
+        pa[1][r] = pack_bf16(p2, p3);
+    }
+    bool rescale = corr[0] != 1.f;
+    if (NR == 2) rescale = rescale || corr[NR - 1] != 1.f;
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+            for (int c = 0; c < 2 * NR; ++c) st.o[i][c] *= corr[c >> 1];
+    }
+    const uint32_t pa0 = pa[0][0], pa2 = pa[1][0];
+    const uint32_t pa1 = NR == 2 ? pa[0][NR - 1] : 0u, pa3 = NR == 2 ? pa[1][NR - 1] : 0u;
+    const unsigned char* vr[4] = {vsm + (2 * t) * RB, vsm + (2 * t + 1) * RB, vsm + (2 * t + 8) * RB, vsm + (2 * t + 9) * RB};
+    int tile = 0;
+#pragma unroll
+    for (int b = 0; b < VBlocks::N64; ++b) {
+        uint4 r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint4*>(vr[k] + b * 128 + 16 * g);
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                        __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+        }
+        tile += 8;
+    }
+    if (VBlocks::HAS32) {
+        const int base = VBlocks::N64 * 128;
+        uint2 r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint2*>(vr[k] + base + 8 * g);
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(w0[i >> 1], w1[i >> 1], sel),
+                        __byte_perm(w2[i >> 1], w3[i >> 1], sel));
+        }
+        tile += 4;
+    }
+    if (VBlocks::HAS16) {
+        const int base = VBlocks::N64 * 128 + VBlocks::HAS32 * 64;
+        uint32_t r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r[k] = *reinterpret_cast<const uint32_t*>(vr[k] + base + 4 * g);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+            dec_mma<NR>(st.o[tile + i], pa0, pa1, pa2, pa3, __byte_perm(r[0], r[1], sel), __byte_perm(r[2], r[3], sel));
+        }
+    }
+}
+
+template <int NR>
+__global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kernel(
+    __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
+    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
+    int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
+    float* __restrict__ part_ml, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(128) unsigned char dt_smem[];
+    __shared__ __align__(8) uint64_t dt_bars[2 * DT_STAGES];     // [0,S) full, [S,2S) empty
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int G = Hq / Hkv;
+    const int tiles_per_group = (G + 15) / 16;
+    const int split = blockIdx.x;
+    const int hk = blockIdx.y / tiles_per_group;
+    const int row0 = (blockIdx.y % tiles_per_group) * 16;
+    const int tok = blockIdx.z;
+    const int seq = seq_of_token[tok];
+    const int pos = positions[tok];
+    if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride) {
+        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        return;
+    }
+    const int* bt = block_table + (int64_t)seq * bt_stride;
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_al = first & ~(DT_KEYS - 1);
+    const int total_stages = (pos - first_al) / DT_KEYS + 1;
+    const int per_split = (total_stages + n_splits - 1) / n_splits;
+    const int stage_lo = split * per_split;
+    const int stage_hi = min(total_stages, stage_lo + per_split);
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dt_smem);
+    const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(dt_bars), empty0 = full0 + 8 * DT_STAGES;
+    if (tid == 0) {
+        for (int i = 0; i < DT_STAGES; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full0 + 8 * i), "r"(1) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * i), "r"(DT_CONSUMERS) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    DecState<NR> st;
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+        for (int c = 0; c < 2 * NR; ++c) st.o[i][c] = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) { st.m[r] = -INFINITY; st.l[r] = 0.f; }
+
+    if (warp == DT_CONSUMERS) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ producer
+            bool ok = true;
+            int issued = 0;
+            for (int s = stage_lo; s < stage_hi && ok; ++s) {
+                const int it = s - stage_lo, slot = it % DT_STAGES;
+                ok = dt_wait(empty0 + 8 * slot, ((uint32_t)(it / DT_STAGES) & 1u) ^ 1u, status);
+                if (!ok) break;
+                const int j_stage = first_al + DT_KEYS * s;
+                uint32_t bytes = 0;
+                int64_t off[DT_CONSUMERS];
+#pragma unroll
+                for (int w = 0; w < DT_CONSUMERS; ++w) {
+                    const int j0 = j_stage + 16 * w;
+                    off[w] = -1;
+                    if (j0 > pos || j0 + 15 < first) continue;          // every key of the step is masked: not fetched
+                    const int lp = j0 / P;
+                    const int page = bt[lp];
+                    if (page < 0 || page >= num_pages) { imp_report(status, IMP_BAD_PAGE); continue; }
+                    off[w] = (((int64_t)page * Hkv + hk) * P + (j0 - lp * P)) * DH;
+                    bytes += 2 * DT_RUN_BYTES;
+                }
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * slot), "r"(bytes) : "memory");
+                const uint32_t sbase = ring + slot * DT_STAGE_BYTES;
+#pragma unroll
+                for (int w = 0; w < DT_CONSUMERS; ++w) {
+                    if (off[w] < 0) continue;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(sbase + w * DT_RUN_BYTES), "l"(kc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(sbase + (DT_CONSUMERS + w) * DT_RUN_BYTES), "l"(vc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
+                }
+                issued = it + 1;
+            }
+            if (!ok) {   // a bounded chance for the copies in flight to land before the memory is released
+                for (int it = issued > DT_STAGES ? issued - DT_STAGES : 0; it < issued; ++it)
+                    dt_wait(full0 + 8 * (it % DT_STAGES), (uint32_t)(it / DT_STAGES) & 1u, nullptr);
+            }
+        }
+    } else {
+        // -------------------------------------------------------------------- consumers
+        RowInfo rows[2];
+        const __nv_bfloat16* qrow[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int hr = row0 + g + 8 * r;
+            const bool used = r < NR && hr < G;
+            rows[r].limit = used ? pos : -1;
+            rows[r].first = first;
+            qrow[r] = used ? q + (int64_t)tok * q_stride + (int64_t)(hk * G + hr) * DH : nullptr;
+        }
+        uint32_t qa[KSTEPS][4];
+        load_q(qa, qrow[0], qrow[1], t4);
+        for (int s = stage_lo; s < stage_hi; ++s) {
+            const int it = s - stage_lo, slot = it % DT_STAGES;
+            const bool ok = __all_sync(0xffffffffu, dt_wait(full0 + 8 * slot, (uint32_t)(it / DT_STAGES) & 1u, status));
+            if (!ok) break;
+            const int j0 = first_al + DT_KEYS * s + 16 * warp;
+            if (j0 <= pos && j0 + 15 >= first) {
+                const unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
+                dec_compute_smem<NR>(st, qa, rows, sb + warp * DT_RUN_BYTES, sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES, j0,
+                                     scale_log2, lane);
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * slot) : "memory");
+        }
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        }
+    }
+    __syncthreads();   // every copy has been consumed (or given up): the ring becomes the merge buffer
+    // ---- merge the four consumer warps (fragment-wise, through shared memory) ------------------------
+    float* smem = reinterpret_cast<float*>(dt_smem);
+    constexpr int NACC = NTILES * 2 * NR;
+    constexpr int PER_WARP = NACC + 2 * NR;
+    if (warp > 0 && warp < DT_CONSUMERS) {
+        float* dst = smem + (size_t)(warp - 1) * PER_WARP * 32;
+#pragma unroll
+        for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+            for (int c = 0; c < 2 * NR; ++c) dst[(i * 2 * NR + c) * 32 + lane] = st.o[i][c];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            dst[(NACC + r) * 32 + lane] = st.m[r];
+            dst[(NACC + NR + r) * 32 + lane] = st.l[r];
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    for (int w = 1; w < DT_CONSUMERS; ++w) {
+        const float* src = smem + (size_t)(w - 1) * PER_WARP * 32;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const float mo = src[(NACC + r) * 32 + lane];
+            const float lo = src[(NACC + NR + r) * 32 + lane];
+            const float m_new = fmaxf(st.m[r], mo);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float ca = exp2f(st.m[r] - m_use), cb = exp2f(mo - m_use);
+            st.l[r] = st.l[r] * ca + lo * cb;
+            st.m[r] = m_new;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                st.o[i][2 * r] = st.o[i][2 * r] * ca + src[(i * 2 * NR + 2 * r) * 32 + lane] * cb;
+                st.o[i][2 * r + 1] = st.o[i][2 * r + 1] * ca + src[(i * 2 * NR + 2 * r + 1) * 32 + lane] * cb;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int hr = row0 + g + 8 * r;
+        if (hr >= G) continue;
+        const int head = hk * G + hr;
+        if (n_splits == 1) {
+            const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+            __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                o[dim_of(i, 2 * t4)] = __float2bfloat16_rn(st.o[i][2 * r] * inv);
+                o[dim_of(i, 2 * t4 + 1)] = __float2bfloat16_rn(st.o[i][2 * r + 1] * inv);
+            }
+        } else {
+            const int64_t slot = ((int64_t)tok * Hq + head) * n_splits + split;
+            float* o = part_o + slot * DH;
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) {
+                o[dim_of(i, 2 * t4)] = st.o[i][2 * r];
+                o[dim_of(i, 2 * t4 + 1)] = st.o[i][2 * r + 1];
+            }
+            if (t4 == 0) {
+                part_ml[slot * 2] = st.m[r];
+                part_ml[slot * 2 + 1] = st.l[r];
+            }
+        }
+    }
+}
+
+template <int NR>
+static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_stride, const void* q, int64_t q_stride,
+                             const void* kc, const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                             const int* positions, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2,
+                             int window, int n_splits, float* part_o, float* part_ml, int* status) {
+    constexpr int MERGE = (DT_CONSUMERS - 1) * (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);
+    constexpr int SMEM = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
+    static bool attr_set = false;
+    if (!attr_set) {   // always: the kernel's static barriers come on top of the ring
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    cudaError_t e = imp_launch(attn_decode_tma_kernel<NR>, grid, dim3((DT_CONSUMERS + 1) * 32), (size_t)SMEM, s,
+                               (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
+                               (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P,
+                               num_pages, scale_log2, window, n_splits, part_o, part_ml, status);
+    if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
+}
+
+template <int NR>
+static int launch_decode(dim3 grid, cudaStream_t s, void* out, int64_t out_stride, const void* q, int64_t q_stride,
+                         const void* kc, const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                         const int* positions, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2,
+                         int window, int n_splits, float* part_o, float* part_ml, int* status) {
+    constexpr int SMEM = (WARPS - 1) * (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);   // warp merge buffer
+    static bool attr_set = false;
+    if (!attr_set && SMEM > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    cudaError_t e = imp_launch(attn_decode_kernel<NR>, grid, dim3(WARPS * 32), (size_t)SMEM, s, (__nv_bfloat16*)out, out_stride,
+                               (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
+                               block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages, scale_log2,
+                               window, n_splits, part_o, part_ml, status);
+    if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
+}
+
 IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
                             const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                             const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages,
@@ -666,21 +1068,27 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
     cudaStream_t s = (cudaStream_t)stream;
     const int G = Hq / Hkv;
     const int tiles_per_group = (G + 15) / 16;
-    constexpr int DEC_SMEM_BYTES = (WARPS - 1) * (NTILES * 4 + 4) * 32 * (int)sizeof(float);   // warp merge buffer
-    static bool attr_set = false;
-    if (!attr_set && DEC_SMEM_BYTES > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
-        if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_set = true;
-    }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (int64_t)n_tokens * Hq * n_splits * DH : nullptr;
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, Hkv * tiles_per_group, n_tokens);
-    imp_launch(attn_decode_kernel, grid, dim3(WARPS * 32), (size_t)DEC_SMEM_BYTES, s,
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
-        (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages,
-        scale_log2, window, n_splits, part_o, part_ml, status);
+    const bool bulk = P % 16 == 0 && getenv("IMP_B200_ATTN_DIRECT") == nullptr;   // whole 16-key steps per page
+#define DEC_ARGS grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, \
+                 Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml, status
+    if (bulk) {
+        if (int rc = (G <= 8) ? launch_decode_tma<1>(DEC_ARGS) : launch_decode_tma<2>(DEC_ARGS)) return rc;
+    } else if (G <= 8) {
+        if (int rc = launch_decode<1>(grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token,
+                                      positions, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, n_splits, part_o,
+                                      part_ml, status))
+            return rc;
+    } else {
+        if (int rc = launch_decode<2>(grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token,
+                                      positions, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, n_splits, part_o,
+                                      part_ml, status))
+            return rc;
+    }
+#undef DEC_ARGS
     if (n_splits > 1) {
         imp_launch(attn_merge_kernel, dim3(n_tokens * Hq), dim3(128), 0, s, (__nv_bfloat16*)out, out_stride,
                    (const float*)part_o, (const float*)part_ml, Hq, n_splits);

@@ -60,11 +60,28 @@ def _check(lib, rc: int, what: str) -> None:
         raise L.KernelError(f"{what} failed ({rc}): {lib.imp_last_error().decode(errors='replace')}")
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, group: int) -> int:
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16) -> int:
     """Key splits of the decode kernel: a function of the batch size alone (a captured graph must not
-    depend on the context length); short contexts simply leave the later splits empty."""
+    depend on the context length); short contexts simply leave the later splits empty.
+
+    The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with
+    fewer (token, kv head) pairs than such slots the keys are split until the slots are full; with
+    more, the smallest split count whose CTAs fill whole waves of slots to 95% is taken."""
     base = n_tokens * n_kv_heads * ((group + 15) // 16)
-    return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_CTAS // max(base, 1)))
+    if page_size % 16:
+        return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_CTAS // max(base, 1)))
+    slots = 2 * 148
+    if base <= slots:
+        return max(1, min(DECODE_MAX_SPLITS, slots // base))
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        ctas = base * s
+        eff = ctas / (-(-ctas // slots) * slots)
+        if eff >= 0.95:
+            return s
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best
 
 
 def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,
@@ -76,7 +93,7 @@ def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, 
     assert hk == n_kv_heads and dh == head_dim and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     if n_splits is None:
-        n_splits = decode_splits(T, n_kv_heads, n_q_heads // n_kv_heads)
+        n_splits = decode_splits(T, n_kv_heads, n_q_heads // n_kv_heads, page_size)
     scratch = None
     n_floats = lib.imp_attn_decode_scratch_floats(T, n_q_heads, n_splits)
     if n_floats:

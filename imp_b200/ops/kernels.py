@@ -16,6 +16,15 @@ from . import library as L
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
+# Matrix products with more rows than SMALL_M_MAX: "tcgen05" = this library's TMA + tcgen05 kernel
+# (csrc/gemm_tc.cu), "cublas" = the library GEMM through torch.mm (what the reference's engine calls
+# for its T>1 products).  IMP_B200_GEMM overrides the default.
+import os as _os
+
+LARGE_M_BACKEND = _os.environ.get("IMP_B200_GEMM", "tcgen05")
+if LARGE_M_BACKEND not in ("tcgen05", "cublas"):
+    raise ValueError(f"IMP_B200_GEMM must be 'tcgen05' or 'cublas', got {LARGE_M_BACKEND!r}")
+
 # Rows up to which the weight-streaming kernel is used for bfloat16 products; above it the
 # library GEMM (cuBLAS through torch.mm) runs, as the reference does for its T>1 products
 # (src/compute/gemm.cu:303-445).
@@ -106,6 +115,12 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tenso
                                                   x.shape[1], _stream())
         if rc != -2:
             L.check(rc, "gemm_bf16_stream_swiglu")
+            return out
+    if (LARGE_M_BACKEND == "tcgen05" and x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16
+            and out.dtype == torch.bfloat16):
+        if M <= TC_SWAP_MAX_M and gemm_bf16_tc_swap(out, x, w_interleaved, TC_OUT_SWIGLU):
+            return out
+        if gemm_bf16_tc(out, x, w_interleaved, TC_OUT_SWIGLU):
             return out
     gu = torch.empty((M, 2 * F), dtype=x.dtype, device=x.device)
     linear(gu, x, w_interleaved)
@@ -278,6 +293,32 @@ def gemm_bf16_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: 
     return True
 
 
+TC_SWAP_MAX_M = 128   # rows up to which the weights take the M side of the tcgen05 product
+
+
+def gemm_bf16_tc_swap(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = None,
+                      status: Optional[torch.Tensor] = None) -> bool:
+    """out = a[M,K] @ w[N,K]^T for M <= 128 with the weight rows on the M side of the tcgen05 MMA and the
+    K range split over CTAs when there are few weight-row tiles.  Returns False if alignment rules it out."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    if epilogue is None:
+        epilogue = TC_OUT_F32 if out.dtype == torch.float32 else TC_OUT_BF16
+    assert w.shape[1] == K and a.dtype == w.dtype == torch.bfloat16 and M <= TC_SWAP_MAX_M
+    assert out.shape == (M, N // 2 if epilogue == TC_OUT_SWIGLU else N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    lib = L.load()
+    n_scratch = lib.imp_gemm_bf16_tc_swap_scratch_floats(M, N, K, epilogue)
+    scratch = torch.empty(n_scratch, dtype=torch.float32, device=a.device) if n_scratch else None
+    rc = lib.imp_gemm_bf16_tc_swap(out.data_ptr(), out.stride(0), epilogue, a.data_ptr(), a.stride(0), w.data_ptr(),
+                                   w.stride(0), M, N, K, _ptr(scratch), _ptr(status), _stream())
+    if rc == -2:
+        return False
+    L.check(rc, "gemm_bf16_tc_swap")
+    return True
+
+
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
 
@@ -303,6 +344,11 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
     if M <= SMALL_M_MAX:
         return gemm_bf16_stream(out, x, w)
+    if LARGE_M_BACKEND == "tcgen05":
+        if M <= TC_SWAP_MAX_M and gemm_bf16_tc_swap(out, x, w):
+            return out
+        if gemm_bf16_tc(out, x, w):
+            return out
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:

@@ -211,6 +211,39 @@ def test_gemm_bf16_tcgen05(K, M, N, K_, odtype):
     assert not K.gemm_bf16_tc(out, odd[:, :K_], w, None, status)
 
 
+@pytest.mark.parametrize("M", [17, 33, 64, 65, 100, 128])
+@pytest.mark.parametrize("N,K_", [(128, 64), (130, 72), (1000, 4104), (4096, 1024), (200, 12288)])
+@pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_tcgen05_few_rows(K, M, N, K_, odtype):
+    """Weights on the M side of the MMA, K split over CTAs: every edge case of rows, columns and K."""
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=50).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=51).to(DEV)
+    status = K.new_status(DEV)
+    out = torch.full((M, N), float("nan"), dtype=odtype, device=DEV)
+    assert K.gemm_bf16_tc_swap(out, a, w, None, status)
+    K.check_status(status)
+    want = a.double().cpu() @ w.double().cpu().T
+    if odtype == torch.float32:
+        close(out, want, torch.float32, scale=float(want.abs().max()) * 8)
+    else:
+        close(out, want, torch.bfloat16)
+    again = torch.empty_like(out)
+    assert K.gemm_bf16_tc_swap(again, a, w, None, status) and torch.equal(again, out)   # split sums have a fixed order
+
+
+@pytest.mark.parametrize("M,F,K_", [(20, 136, 96), (64, 3072, 1024), (128, 8, 64)])
+def test_gemm_bf16_tcgen05_few_rows_fused_swiglu(K, M, F, K_):
+    x = rnd(M, K_, dtype=torch.bfloat16, seed=52).to(DEV)
+    wg = rnd(F, K_, dtype=torch.bfloat16, seed=53, scale=0.3).to(DEV)
+    wu = rnd(F, K_, dtype=torch.bfloat16, seed=54, scale=0.3).to(DEV)
+    status = K.new_status(DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert K.gemm_bf16_tc_swap(out, x, K.interleave_gate_up(wg, wu), K.TC_OUT_SWIGLU, status)
+    K.check_status(status)
+    g = x.double().cpu() @ wg.double().cpu().T
+    u = x.double().cpu() @ wu.double().cpu().T
+    close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
+
+
 @pytest.mark.parametrize("M,F,K_", [(200, 136, 96), (2048, 3072, 1024), (33, 8, 64)])
 def test_gemm_bf16_tcgen05_fused_swiglu(K, M, F, K_):
     x = rnd(M, K_, dtype=torch.bfloat16, seed=42).to(DEV)
