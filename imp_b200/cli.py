@@ -2,7 +2,9 @@
 
 Option names and meanings are the reference's where it has them (--model,
 --prompt, --max-tokens, --temperature, --top-p, --top-k, --seed, --min-p,
---repeat-penalty, --frequency-penalty, --presence-penalty, --device,
+--repeat-penalty, --frequency-penalty, --presence-penalty, --typical-p,
+--dry-multiplier, --dry-base, --dry-allowed-length, --dry-penalty-last-n,
+--mirostat, --mirostat-tau, --mirostat-eta, --device,
 --no-cuda-graphs, --prefill-chunk-size, --bench, --bench-pp, --bench-reps);
 --random-weights, --weights-seed, --weights-std, --dtype, --kv-pages,
 --page-size, --max-batch, --max-seq-len, --bench-batch are this engine's.
@@ -34,6 +36,15 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--frequency-penalty", type=float, default=0.0)
     p.add_argument("--presence-penalty", type=float, default=0.0)
     p.add_argument("--repeat-last-n", type=int, default=0, help="penalty window, 0 = all tokens")
+    p.add_argument("--typical-p", type=float, default=1.0, help="locally typical sampling (default: 1.0 = disabled)")
+    p.add_argument("--dry-multiplier", type=float, default=0.0, help="DRY n-gram penalty scale (default: 0.0 = disabled)")
+    p.add_argument("--dry-base", type=float, default=1.75, help="DRY exponential base (default: 1.75)")
+    p.add_argument("--dry-allowed-length", type=int, default=2,
+                   help="DRY: n-grams at or below this not penalized (default: 2)")
+    p.add_argument("--dry-penalty-last-n", type=int, default=0, help="DRY: how far back to scan (default: 0 = all)")
+    p.add_argument("--mirostat", type=int, default=0, help="Mirostat sampling (0=off, 2=v2) (default: 0)")
+    p.add_argument("--mirostat-tau", type=float, default=5.0, help="Mirostat target entropy (default: 5.0)")
+    p.add_argument("--mirostat-eta", type=float, default=0.1, help="Mirostat learning rate (default: 0.1)")
     p.add_argument("--device", type=int, default=0, help="CUDA device id (default: 0)")
     p.add_argument("--no-cuda-graphs", action="store_true", help="disable CUDA graph capture for decode")
     p.add_argument("--prefill-chunk-size", type=int, default=0, help="max tokens per prefill portion (0 = no cut)")
@@ -106,6 +117,9 @@ def main(argv: Optional[List[str]] = None) -> int:
                         max_tokens=args.max_tokens, seed=args.seed, min_p=args.min_p,
                         repetition_penalty=args.repeat_penalty, frequency_penalty=args.frequency_penalty,
                         presence_penalty=args.presence_penalty, repeat_last_n=args.repeat_last_n,
+                        typical_p=args.typical_p, dry_multiplier=args.dry_multiplier, dry_base=args.dry_base,
+                        dry_allowed_length=args.dry_allowed_length, dry_penalty_last_n=args.dry_penalty_last_n,
+                        mirostat=args.mirostat, mirostat_tau=args.mirostat_tau, mirostat_eta=args.mirostat_eta,
                         ignore_eos=args.ignore_eos)
     req = eng.submit(prompt, gp)
     if req.done:

@@ -212,6 +212,54 @@ IMP_API int imp_apply_penalties(float* logits, int64_t ld, int n_rows, int V, co
     IMP_RETURN_LAUNCH();
 }
 
+// ------------------------------------------------------------------- the draw
+// One token among those that `keep` accepts, with weights `weight`, from the
+// uniform number u: the first kept index, in index order, whose running weight
+// exceeds u * total.  Thread t owns the contiguous range [t*chunk, (t+1)*chunk);
+// thread 0 turns the per-thread sums into exclusive prefixes in a fixed order.
+// Returns -1 when nothing is kept.  All threads of the block must call it.
+template <class Keep, class Weight>
+__device__ __forceinline__ int draw_in_index_order(int V, float u, Keep keep, Weight weight, float* part,
+                                                   float* scratch, int* s_pick) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int chunk = (V + nthr - 1) / nthr;
+    const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
+    float mine = 0.f;
+    for (int i = lo; i < hi; ++i)
+        if (keep(i)) mine += weight(i);
+    __syncthreads();
+    part[tid] = mine;
+    if (tid == 0) *s_pick = -1;
+    __syncthreads();
+    if (tid == 0) {
+        float run = 0.f;
+        for (int t = 0; t < nthr; ++t) {
+            const float v = part[t];
+            part[t] = run;  // exclusive prefix
+            run += v;
+        }
+        scratch[0] = run;
+    }
+    __syncthreads();
+    const float total = scratch[0];
+    const float target = u * total;
+    const float before = part[tid];
+    if (mine > 0.f && before <= target && target < before + mine) {
+        float run = before;
+        int pick = -1, last = -1;
+        for (int i = lo; i < hi; ++i) {
+            if (keep(i)) {
+                run += weight(i);
+                last = i;
+                if (run > target) { pick = i; break; }
+            }
+        }
+        *s_pick = pick >= 0 ? pick : last;
+    }
+    __syncthreads();
+    return *s_pick;
+}
+
 // ------------------------------------------------------------------- sample
 // Per row r: temperature[r] <= 0 or top_k[r] == 1 -> argmax.  Otherwise:
 //   keep i with logit_i >= max + log(min_p)           (min_p > 0)
@@ -281,42 +329,9 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK) sample_kernel(
         if (tau_p > tau) tau = tau_p;
     }
 
-    // Draw in index order: thread t owns the contiguous range [t*chunk, (t+1)*chunk).
-    const int chunk = (V + SAMPLE_BLOCK - 1) / SAMPLE_BLOCK;
-    const int lo = tid * chunk, hi = min(V, lo + chunk);
-    float mine = 0.f;
-    for (int i = lo; i < hi; ++i)
-        if (KEPT0(i) && ordered_key(x[i]) >= tau) mine += EVAL(i);
-    part[tid] = mine;
-    if (tid == 0) s_pick = -1;
-    __syncthreads();
-    if (tid == 0) {
-        float run = 0.f;
-        for (int t = 0; t < SAMPLE_BLOCK; ++t) {
-            const float v = part[t];
-            part[t] = run;  // exclusive prefix
-            run += v;
-        }
-        scratch[0] = run;
-    }
-    __syncthreads();
-    const float total = scratch[0];
-    const float target = uniform[r] * total;
-    const float before = part[tid];
-    if (mine > 0.f && before <= target && target < before + mine) {
-        float run = before;
-        int pick = -1, last = -1;
-        for (int i = lo; i < hi; ++i) {
-            if (KEPT0(i) && ordered_key(x[i]) >= tau) {
-                run += EVAL(i);
-                last = i;
-                if (run > target) { pick = i; break; }
-            }
-        }
-        s_pick = pick >= 0 ? pick : last;
-    }
-    __syncthreads();
-    if (tid == 0) out[r] = s_pick >= 0 ? s_pick : arg;  // rounding left no owner: the most probable token
+    const int pick = draw_in_index_order(V, uniform[r], [&](int i) { return KEPT0(i) && ordered_key(x[i]) >= tau; },
+                                         [&](int i) { return EVAL(i); }, part, scratch, &s_pick);
+    if (tid == 0) out[r] = pick >= 0 ? pick : arg;  // rounding left no owner: the most probable token
 #undef KEPT0
 #undef EVAL
 }
@@ -329,5 +344,155 @@ IMP_API int imp_sample(const float* logits, int64_t ld, int n_rows, int V, const
                   "imp_sample: bad argument");
     sample_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature, top_k, top_p, min_p,
                                                                     uniform, out);
+    IMP_RETURN_LAUNCH();
+}
+
+// ------------------------------------------------------------------- DRY
+// logits[rows[i]][tokens[i]] -= values[i]: the sparse form of the "don't repeat
+// yourself" penalty, whose (token, value) pairs the host finds by matching the
+// end of the request's tokens against their earlier occurrences
+// (src/compute/sampling.cu:811-915 does the same split between host and device).
+__global__ void sparse_subtract_kernel(float* __restrict__ logits, int64_t ld, int V, const int* __restrict__ rows,
+                                       const int* __restrict__ tokens, const float* __restrict__ values, int n,
+                                       int n_rows) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = rows[i], t = tokens[i];
+    if (r < 0 || r >= n_rows || t < 0 || t >= V) return;
+    logits[(int64_t)r * ld + t] -= values[i];  // the host lists a (row, token) pair once
+}
+
+IMP_API int imp_sparse_subtract(float* logits, int64_t ld, int n_rows, int V, const int* rows, const int* tokens,
+                                const float* values, int n, void* stream) {
+    if (n == 0 || n_rows == 0) return 0;
+    IMP_CHECK_ARG(logits && rows && tokens && values && n > 0 && V > 0 && ld >= V, "imp_sparse_subtract: bad argument");
+    sparse_subtract_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(logits, ld, V, rows, tokens, values, n,
+                                                                           n_rows);
+    IMP_RETURN_LAUNCH();
+}
+
+// ------------------------------------------------------------------- typical-p
+// Locally typical filtering on the raw logits (src/compute/sampling.cu:917-1064;
+// order after min-p as in src/graph/executor.cu:92-97).  Over the tokens that
+// min-p keeps: p = softmax(logits), H = -sum p log2 p, dev_i = |-log2 p_i - H|;
+// the tokens of smallest deviation are kept until their mass reaches typical_p
+// (ties at the cut kept), every other logit becomes -inf.  The reference finds
+// the cut with a 256-bucket histogram of deviations and so keeps up to one bucket
+// more; here the cut is exact (a bitwise search over the deviation's bits).
+// Rows with typical_p outside (0, 1) are left untouched.
+__global__ void __launch_bounds__(SAMPLE_BLOCK) typical_filter_kernel(float* __restrict__ logits, int64_t ld, int V,
+                                                                      const float* __restrict__ typical_p,
+                                                                      const float* __restrict__ min_p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float tp = typical_p[r];
+    if (!(tp > 0.f && tp < 1.f)) return;
+    float* x = logits + (int64_t)r * ld;
+    float max_logit;
+    int arg;
+    argmax_row(x, V, s_val, s_idx, max_logit, arg);
+    if (arg == 0x7fffffff) return;
+    const float mp = min_p[r];
+    const float floor_logit = mp > 0.f ? max_logit + logf(mp) : -INFINITY;
+#define TYP_KEPT(i) (x[i] >= floor_logit && x[i] > -INFINITY)
+    float z = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_BLOCK)
+        if (TYP_KEPT(i)) z += expf(x[i] - max_logit);
+    z = block_sum(z, scratch);
+    const float lse = max_logit + logf(z);
+    const float inv_z = 1.f / z;
+    constexpr float LOG2E = 1.4426950408889634f;
+    float h = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_BLOCK)
+        if (TYP_KEPT(i)) h += expf(x[i] - max_logit) * inv_z * ((lse - x[i]) * LOG2E);
+    h = block_sum(h, scratch);
+#define DEV_KEY(i) __float_as_uint(fabsf((lse - x[i]) * LOG2E - h))
+    // The largest T with mass{key < T} < typical_p is the smallest key whose closed set reaches it.
+    unsigned cut = 0u;
+    for (int bit = 31; bit >= 0; --bit) {
+        const unsigned cand = cut | (1u << bit);
+        float mass = 0.f;
+        for (int i = tid; i < V; i += SAMPLE_BLOCK)
+            if (TYP_KEPT(i) && DEV_KEY(i) < cand) mass += expf(x[i] - max_logit) * inv_z;
+        mass = block_sum(mass, scratch);
+        if (mass < tp) cut = cand;
+    }
+    for (int i = tid; i < V; i += SAMPLE_BLOCK)
+        if (!(TYP_KEPT(i) && DEV_KEY(i) <= cut)) x[i] = -INFINITY;
+#undef DEV_KEY
+#undef TYP_KEPT
+}
+
+IMP_API int imp_typical_filter(float* logits, int64_t ld, int n_rows, int V, const float* typical_p,
+                               const float* min_p, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(logits && typical_p && min_p && V > 0 && ld >= V, "imp_typical_filter: bad argument");
+    typical_filter_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, typical_p, min_p);
+    IMP_RETURN_LAUNCH();
+}
+
+// ------------------------------------------------------------------- Mirostat v2
+// src/compute/sampling.cu:1067-1236: with p = softmax(logits / T), keep the
+// tokens whose surprise -log2 p_i is at most mu (all of them if none passes),
+// draw one, and report its surprise under the unfiltered distribution; the host
+// then moves mu by -eta * (surprise - tau).  Rows with active[r] == 0 are left
+// alone.  The draw uses the given uniform number and walks in index order.
+__global__ void __launch_bounds__(SAMPLE_BLOCK) mirostat_kernel(
+    const float* __restrict__ logits, int64_t ld, int V, const int* __restrict__ active,
+    const float* __restrict__ temperature, const float* __restrict__ mu, const float* __restrict__ uniform,
+    int* __restrict__ out, float* __restrict__ surprise) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float s_val[33];
+    __shared__ int s_idx[33];
+    __shared__ float scratch[33];
+    __shared__ float part[SAMPLE_BLOCK];
+    __shared__ int s_pick;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    if (!active[r]) return;
+    const float* x = logits + (int64_t)r * ld;
+    float max_logit;
+    int arg;
+    argmax_row(x, V, s_val, s_idx, max_logit, arg);
+    if (arg == 0x7fffffff) {
+        if (tid == 0) { out[r] = 0; surprise[r] = 0.f; }
+        return;
+    }
+    const float T = temperature[r] > 0.f ? temperature[r] : 1.f;
+    const float inv_T = 1.f / T;
+    float z = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_BLOCK) z += expf((x[i] - max_logit) * inv_T);
+    z = block_sum(z, scratch);
+    float threshold = max_logit + T * (logf(z) - mu[r] * 0.6931471805599453f);
+    float zf = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_BLOCK)
+        if (x[i] >= threshold) zf += expf((x[i] - max_logit) * inv_T);
+    zf = block_sum(zf, scratch);
+    if (!(zf > 0.f)) threshold = -INFINITY;
+    const int pick = draw_in_index_order(V, uniform[r], [&](int i) { return x[i] >= threshold; },
+                                         [&](int i) { return expf((x[i] - max_logit) * inv_T); }, part, scratch,
+                                         &s_pick);
+    if (tid == 0) {
+        const int chosen = pick >= 0 ? pick : arg;
+        const float p = expf((x[chosen] - max_logit) * inv_T) / z;
+        out[r] = chosen;
+        surprise[r] = -log2f(fmaxf(p, 1e-30f));
+    }
+}
+
+IMP_API int imp_sample_mirostat(const float* logits, int64_t ld, int n_rows, int V, const int* active,
+                                const float* temperature, const float* mu, const float* uniform, int* out,
+                                float* surprise, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(logits && active && temperature && mu && uniform && out && surprise && V > 0 && ld >= V,
+                  "imp_sample_mirostat: bad argument");
+    mirostat_kernel<<<n_rows, SAMPLE_BLOCK, 0, (cudaStream_t)stream>>>(logits, ld, V, active, temperature, mu, uniform,
+                                                                      out, surprise);
     IMP_RETURN_LAUNCH();
 }

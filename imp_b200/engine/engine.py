@@ -42,13 +42,24 @@ class GenerateParams:
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0
     repeat_last_n: int = 0
+    typical_p: float = 1.0
+    dry_multiplier: float = 0.0
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_penalty_last_n: int = 0
+    mirostat: int = 0
+    mirostat_tau: float = 5.0
+    mirostat_eta: float = 0.1
     ignore_eos: bool = False
 
     def sampling(self) -> SamplingParams:
         return SamplingParams(temperature=self.temperature, top_p=self.top_p, top_k=self.top_k, min_p=self.min_p,
                               repetition_penalty=self.repetition_penalty, frequency_penalty=self.frequency_penalty,
                               presence_penalty=self.presence_penalty, repeat_last_n=self.repeat_last_n,
-                              seed=self.seed)
+                              typical_p=self.typical_p, dry_multiplier=self.dry_multiplier, dry_base=self.dry_base,
+                              dry_allowed_length=self.dry_allowed_length,
+                              dry_penalty_last_n=self.dry_penalty_last_n, mirostat=self.mirostat,
+                              mirostat_tau=self.mirostat_tau, mirostat_eta=self.mirostat_eta, seed=self.seed)
 
 
 @dataclass
@@ -151,7 +162,8 @@ class Engine:
         if rows:
             toks = self.sampler.sample(logits, [r.params for r in rows], [r.seed for r in rows],
                                        [len(r.output) for r in rows], [r.all_tokens() for r in rows]
-                                       if any(r.params.has_penalties() for r in rows) else None)
+                                       if any(r.params.needs_history() for r in rows) else None,
+                                       [r.sampler_state for r in rows])
             sampled = {r.rid: t for r, t in zip(rows, toks)}
         self.stepper.check_device_status()
         finished = set(id(r) for r in self.scheduler.complete_step(plan, sampled))

@@ -31,7 +31,7 @@ from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional, Sequence
 
 from ..cache.manager import CacheManager
-from ..sampling.sampler import SamplingParams, resolve_seed
+from ..sampling.sampler import SamplerState, SamplingParams, resolve_seed
 
 
 class RequestStatus(enum.Enum):
@@ -65,6 +65,7 @@ class Request:
     n_computed: int = 0            # tokens of prompt+output whose keys/state are in the cache
     seed: int = 0                  # resolved sampling seed
     n_preempted: int = 0
+    sampler_state: SamplerState = field(default_factory=SamplerState)
 
     def all_tokens(self) -> List[int]:
         return self.prompt + self.output

@@ -383,6 +383,44 @@ def apply_penalties(logits: torch.Tensor, history: torch.Tensor, hist_start: tor
                                          pres.data_ptr(), counts.data_ptr(), _stream()), "apply_penalties")
 
 
+def sparse_subtract(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor) -> None:
+    """logits[rows[i], tokens[i]] -= values[i]; every (row, token) pair listed once."""
+    _need_cuda(logits, rows, tokens, values)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert rows.dtype == torch.int32 and tokens.dtype == torch.int32 and values.dtype == torch.float32
+    n = rows.numel()
+    assert tokens.numel() == n and values.numel() == n
+    L.check(L.load().imp_sparse_subtract(logits.data_ptr(), logits.stride(0), R, V, rows.data_ptr(),
+                                         tokens.data_ptr(), values.data_ptr(), n, _stream()), "sparse_subtract")
+
+
+def typical_filter(logits: torch.Tensor, typical_p: torch.Tensor, min_p: torch.Tensor) -> None:
+    """Locally typical filtering in place; rows whose typical_p is outside (0, 1) stay as they are."""
+    _need_cuda(logits, typical_p, min_p)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    for t in (typical_p, min_p):
+        assert t.dtype == torch.float32 and t.numel() == R
+    L.check(L.load().imp_typical_filter(logits.data_ptr(), logits.stride(0), R, V, typical_p.data_ptr(),
+                                        min_p.data_ptr(), _stream()), "typical_filter")
+
+
+def sample_mirostat(logits: torch.Tensor, active: torch.Tensor, temperature: torch.Tensor, mu: torch.Tensor,
+                    uniform: torch.Tensor, out: torch.Tensor, surprise: torch.Tensor) -> None:
+    """Mirostat v2 draw for the rows with active != 0: token into `out`, its surprise (bits) into `surprise`."""
+    _need_cuda(logits, active, temperature, mu, uniform, out, surprise)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert active.dtype == torch.int32 and out.dtype == torch.int32
+    for t in (temperature, mu, uniform, surprise):
+        assert t.dtype == torch.float32 and t.numel() == R
+    assert active.numel() == R and out.numel() == R
+    L.check(L.load().imp_sample_mirostat(logits.data_ptr(), logits.stride(0), R, V, active.data_ptr(),
+                                         temperature.data_ptr(), mu.data_ptr(), uniform.data_ptr(), out.data_ptr(),
+                                         surprise.data_ptr(), _stream()), "sample_mirostat")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            min_p: torch.Tensor, uniform: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need_cuda(logits, temperature, top_k, top_p, min_p, uniform, out)

@@ -60,6 +60,10 @@ _SIGNATURES = {
                                     c_void_p, c_void_p, c_void_p]),
     "imp_sample": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_void_p]),
+    "imp_sparse_subtract": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "imp_typical_filter": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "imp_sample_mirostat": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p]),
 }
 
 # Entry points that newer sources add; declared when present so an older build still loads in tools

@@ -2,7 +2,8 @@
 
 Order and formulas from kekzl/imp (src/graph/executor.cu:43-115 for the order;
 src/compute/sampling.cu:700-736 penalties, :767-810 min-p, :253-557 softmax of
-logits/T, top-k, nucleus cut, renormalise, draw).  Conventions of this engine
+logits/T, top-k, nucleus cut, renormalise, draw; :811-915 DRY; :917-1064
+typical-p; :1067-1236 Mirostat v2).  Conventions of this engine
 where the reference leaves room: ties at a cut are kept, and the draw walks the
 kept tokens in index order.
 """
@@ -69,3 +70,59 @@ def sample(logits, temperature, u, **filters):
     mass = np.where(keep, e, 0.0)
     cum = np.cumsum(mass)
     return int(np.searchsorted(cum, u * cum[-1], side="right"))
+
+
+def dry(tokens, multiplier, base, allowed_length, last_n=0):
+    """token -> penalty, by the reference's scan (src/compute/sampling.cu:826-880): for every
+    position of the window, how many tokens before it equal the sequence's end, walking back."""
+    n = len(tokens)
+    if multiplier <= 0 or n < 2:
+        return {}
+    start = max(0, n - last_n) if last_n > 0 else 0
+    longest = {}
+    for pos in range(start, n):
+        m, a, b = 0, pos - 1, n - 1
+        while a >= start and b >= 0 and tokens[a] == tokens[b]:
+            m, a, b = m + 1, a - 1, b - 1
+        if m > allowed_length:
+            longest[tokens[pos]] = max(longest.get(tokens[pos], 0), m)
+    return {t: multiplier * base ** (m - allowed_length) for t, m in longest.items()}
+
+
+def typical_keep(logits, typical_p, min_p=0.0):
+    """Mask of the tokens locally typical filtering keeps (src/compute/sampling.cu:917-1064, with an
+    exact cut instead of the reference's 256-bucket histogram): smallest |surprise - entropy| first,
+    until the kept mass reaches typical_p; ties at the cut kept."""
+    x = np.array(logits, dtype=np.float64)
+    alive = np.isfinite(x)
+    if min_p > 0:
+        alive &= x >= x.max() + math.log(min_p)
+    e = np.where(alive, np.exp(x - x.max()), 0.0)
+    p = e / e.sum()
+    with np.errstate(divide="ignore"):
+        surprise = np.where(alive, -np.log2(np.where(p > 0, p, 1.0)), np.inf)
+    H = float((p[alive] * surprise[alive]).sum())
+    dev = np.abs(surprise - H)
+    order = np.argsort(dev, kind="stable")
+    order = order[alive[order]]
+    cum = np.cumsum(p[order])
+    n = min(int(np.searchsorted(cum, typical_p, side="left")) + 1, order.size)
+    cut = dev[order[n - 1]]
+    return alive & (dev <= cut), dev, cut
+
+
+def mirostat_v2(logits, temperature, mu, u):
+    """(token, surprise in bits) of one Mirostat v2 draw (src/compute/sampling.cu:1072-1200): keep
+    surprise <= mu under softmax(logits / T) (everything if nothing passes), draw in index order."""
+    x = np.array(logits, dtype=np.float64)
+    T = temperature if temperature > 0 else 1.0
+    e = np.exp((x - x.max()) / T)
+    z = e.sum()
+    threshold = x.max() + T * (math.log(z) - mu * math.log(2.0))
+    keep = x >= threshold
+    if not keep.any():
+        keep[:] = True
+    mass = np.where(keep, e, 0.0)
+    cum = np.cumsum(mass)
+    tok = int(np.searchsorted(cum, u * cum[-1], side="right"))
+    return tok, -math.log2(max(e[tok] / z, 1e-30)), keep

@@ -610,3 +610,128 @@ def test_penalties(K):
     for r in range(3):
         want = S.penalize(logits[r].numpy(), hist[r], float(rep[r]), float(freq[r]), float(pres[r]))
         assert np.allclose(x[r].cpu().numpy(), want, atol=1e-5)
+
+
+def test_dry_penalty_matches_the_plain_scan(K):
+    from imp_b200.sampling.sampler import dry_penalties
+    rng = np.random.default_rng(5)
+    for trial in range(20):
+        n = int(rng.integers(2, 80))
+        toks = rng.integers(0, 4, n).tolist()            # tiny alphabet: long repeats are common
+        last_n = int(rng.choice([0, 5, 17]))
+        allowed = int(rng.integers(0, 4))
+        want = S.dry(toks, 0.8, 1.75, allowed, last_n)
+        got = dry_penalties(toks, 0.8, 1.75, allowed, last_n)
+        assert got.keys() == want.keys() and all(abs(got[t] - want[t]) < 1e-9 for t in want), (toks, last_n, allowed)
+    # "a b c d a b c" -> after c came d: a 3-token repeat would become 4 long
+    assert S.dry([1, 2, 3, 4, 1, 2, 3], 1.0, 2.0, 2) == {4: 2.0}
+    V = 50
+    logits = rnd(3, V, seed=31)
+    x = logits.clone().to(DEV)
+    rows = torch.tensor([0, 2, 2], dtype=torch.int32, device=DEV)
+    toks = torch.tensor([4, 49, 0], dtype=torch.int32, device=DEV)
+    vals = torch.tensor([2.0, 0.5, 1.25], dtype=torch.float32, device=DEV)
+    K.sparse_subtract(x, rows, toks, vals)
+    want = logits.clone()
+    want[0, 4] -= 2.0
+    want[2, 49] -= 0.5
+    want[2, 0] -= 1.25
+    assert torch.equal(x.cpu(), want)
+
+
+@pytest.mark.parametrize("typical_p,min_p", [(0.2, 0.0), (0.5, 0.0), (0.9, 0.0), (0.6, 0.05)])
+def test_typical_filter_matches_the_plain_twin(K, typical_p, min_p):
+    V = 1003
+    logits = rnd(3, V, seed=33, scale=2.5)
+    logits[2, ::7] = -float("inf")                       # tokens an earlier mask removed
+    x = logits.clone().to(DEV)
+    tp = torch.tensor([typical_p, 1.0, typical_p], dtype=torch.float32, device=DEV)
+    mp = torch.full((3,), min_p, dtype=torch.float32, device=DEV)
+    K.typical_filter(x, tp, mp)
+    got = x.cpu()
+    assert torch.equal(got[1], logits[1]), "a row with typical_p = 1 is left alone"
+    for r in (0, 2):
+        keep, dev, cut = S.typical_keep(logits[r].numpy(), typical_p, min_p)
+        kept = torch.isfinite(got[r]).numpy()
+        edge = np.abs(dev - cut) < 1e-3                  # float32 vs float64 at the cut
+        assert ((kept == keep) | edge).all(), f"row {r}: kept set differs away from the cut"
+        assert torch.equal(got[r][torch.from_numpy(kept)], logits[r][torch.from_numpy(kept)])
+        assert 0 < kept.sum() < np.isfinite(logits[r].numpy()).sum()
+    # the most probable token can be atypical: a peaked head over a flat tail
+    peaked = torch.zeros(1, 400)
+    peaked[0, 0] = 4.0
+    y = peaked.clone().to(DEV)
+    K.typical_filter(y, torch.tensor([0.3], device=DEV), torch.zeros(1, device=DEV))
+    keep, _, _ = S.typical_keep(peaked[0].numpy(), 0.3)
+    assert (torch.isfinite(y[0]).cpu().numpy() == keep).all()
+
+
+def test_mirostat_draw_and_surprise(K):
+    V, R = 777, 48
+    logits = rnd(1, V, seed=34, scale=2.0).repeat(R, 1)
+    rng = np.random.default_rng(6)
+    us = rng.random(R).astype(np.float32)
+    mus = rng.uniform(1.0, 12.0, R).astype(np.float32)
+    mus[0] = -5.0                                        # nothing passes: falls back to every token
+    active = torch.ones(R, dtype=torch.int32, device=DEV)
+    active[5] = 0
+    out = torch.full((R,), -7, dtype=torch.int32, device=DEV)
+    sur = torch.full((R,), -1.0, dtype=torch.float32, device=DEV)
+    K.sample_mirostat(logits.to(DEV), active, torch.full((R,), 0.9, device=DEV), torch.from_numpy(mus).to(DEV),
+                      torch.from_numpy(us).to(DEV), out, sur)
+    out, sur = out.tolist(), sur.tolist()
+    assert out[5] == -7 and sur[5] == -1.0, "inactive rows are not written"
+    x = logits[0].numpy()
+    for r in range(R):
+        if r == 5:
+            continue
+        tok, s, keep = S.mirostat_v2(x, 0.9, float(mus[r]), float(us[r]))
+        assert keep[out[r]], f"row {r}: token {out[r]} has surprise above mu={mus[r]}"
+        mass = np.where(keep, np.exp((x - x.max()) / 0.9), 0.0)
+        cum = np.cumsum(mass) / mass.sum()
+        lo, hi = cum[out[r]] - mass[out[r]] / mass.sum(), cum[out[r]]
+        assert lo - 1e-5 <= us[r] <= hi + 1e-5
+        e = np.exp((x - x.max()) / 0.9)
+        s_want = -math.log2(e[out[r]] / e.sum())         # surprise under the unfiltered distribution
+        assert abs(sur[r] - s_want) < 1e-3
+
+
+def test_sampler_mirostat_state_typical_and_dry_through_the_class(K):
+    from imp_b200.sampling.sampler import Sampler, SamplerState, SamplingParams, uniform_for
+    V = 300
+    sampler = Sampler(V, 4, DEV)
+    base = rnd(1, V, seed=35, scale=2.0)
+    # Mirostat: mu starts at 2 * tau and moves by -eta * (surprise - tau) after every draw
+    p = SamplingParams(temperature=1.0, mirostat=2, mirostat_tau=3.0, mirostat_eta=0.2, seed=11)
+    st = SamplerState()
+    mu = 6.0
+    for step in range(5):
+        tok = sampler.sample(base.clone().to(DEV), [p], [11], [step], None, [st])[0]
+        want_tok, s, _ = S.mirostat_v2(base[0].numpy(), 1.0, mu, uniform_for(11, step))
+        assert tok == want_tok
+        mu -= 0.2 * (s - 3.0)
+        assert abs(st.mirostat_mu - mu) < 1e-3
+    # typical-p before greedy: the argmax is taken among the typical tokens
+    peaked = torch.zeros(1, V)
+    peaked[0, 0] = 4.0
+    peaked[0, 17] = 0.01
+    g = SamplingParams(temperature=0.0, top_k=0, top_p=1.0, typical_p=0.3)
+    keep, _, _ = S.typical_keep(peaked[0].numpy(), 0.3)
+    assert not keep[0]
+    assert sampler.sample(peaked.clone().to(DEV), [g], [1], [0])[0] == 17
+    # DRY: the token that would extend a repeat loses multiplier * base ** (match - allowed)
+    hist = [9, 8, 7, 6, 9, 8, 7]
+    d = SamplingParams(temperature=0.0, dry_multiplier=50.0, dry_base=1.75, dry_allowed_length=2)
+    x = torch.zeros(1, V)
+    x[0, 6] = 5.0
+    x[0, 3] = 1.0
+    assert sampler.sample(x.clone().to(DEV), [SamplingParams.greedy()], [1], [0], [hist])[0] == 6
+    assert sampler.sample(x.clone().to(DEV), [d], [1], [0], [hist])[0] == 3
+    # a mixed batch: each row as it would be alone
+    rows = [p, g, d, SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=4)]
+    logits = torch.cat([base, peaked, x, base]).to(DEV)
+    st2 = [SamplerState() for _ in rows]
+    got = sampler.sample(logits.clone(), rows, [11, 1, 1, 4], [0, 0, 0, 3], [[], [], hist, []], st2)
+    alone = [sampler.sample(logits[i:i + 1].clone(), [rows[i]], [[11, 1, 1, 4][i]], [[0, 0, 0, 3][i]],
+                            [[[], [], hist, []][i]], [SamplerState()])[0] for i in range(4)]
+    assert got == alone
