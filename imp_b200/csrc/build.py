@@ -217,6 +217,7 @@ def build_variant(source: str, defines: dict, force: bool = False, verbose: bool
 
 
 ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))
+ATTENTION_TC_HEAD_DIMS = (64, 128)     # head sizes of the tensor-memory prefill kernel
 
 
 def build_all(force: bool = False) -> List[str]:
@@ -224,6 +225,7 @@ def build_all(force: bool = False) -> List[str]:
     paths = [build(force)]
     with ThreadPoolExecutor(max_workers=8) as ex:
         futs = [ex.submit(build_variant, "attention_mma.cu", {"IMP_ATTN_DH": dh}, force) for dh in ATTENTION_HEAD_DIMS]
+        futs += [ex.submit(build_variant, "attention_tc.cu", {"IMP_ATTN_DH": dh}, force) for dh in ATTENTION_TC_HEAD_DIMS]
         paths += [f.result() for f in futs]
     return paths
 

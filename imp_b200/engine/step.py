@@ -29,6 +29,8 @@ from .model import DecoderModel
 
 
 ATTENTION_TILE = 32   # query tokens per attention tile (two 16-row tensor-core tiles share staged keys)
+ATTENTION_WIDE_TILE = 128   # query tokens per tile of the tensor-memory prefill kernel
+ATTENTION_WIDE_MIN = 64     # portions at least this long are cut into wide tiles as well
 
 
 @dataclass
@@ -45,7 +47,8 @@ class StepContext:
 
     __slots__ = ("n_tokens", "n_seqs", "n_rows", "token_ids", "positions", "seq_of_token", "logit_rows",
                  "q_start", "kv_len", "state_slots", "block_tables", "max_q_len", "max_kv_len", "decode_only",
-                 "q_lens", "starts", "rids", "fresh", "slots", "tile_tok0", "tile_rows")
+                 "q_lens", "starts", "rids", "fresh", "slots", "tile_tok0", "tile_rows",
+                 "wide_tile_tok0", "wide_tile_rows", "rest_tile_tok0", "rest_tile_rows")
 
 
 class BatchBuffers:
@@ -63,7 +66,7 @@ class BatchBuffers:
         o = 0
         self.off = {}
         for name, n in (("tok", max_tokens), ("pos", max_tokens), ("seq", max_tokens), ("rows", max_tokens),
-                        ("tile0", max_tokens), ("tilen", max_tokens),
+                        ("tile0", max_tokens), ("tilen", max_tokens), ("wtile0", max_tokens), ("wtilen", max_tokens),
                         ("q_start", max_seqs + 1), ("kv_len", max_seqs), ("slots", max_seqs)):
             self.off[name] = o
             o += n
@@ -199,17 +202,29 @@ class Stepper:
         R = len(rows)
         if R:
             host[off["rows"]: off["rows"] + R] = rows
-        n_tiles = 0
+        n_tiles = n_wide = n_rest = 0
         if not decode_only:
-            tiles0, tilesn = [], []
+            # Every portion in tiles of ATTENTION_TILE tokens; and, for kernels with wide tiles, the same
+            # tokens again as wide tiles of the long portions followed by narrow tiles of the short ones.
+            tiles0, tilesn, wide0, widen, rest0, restn = [], [], [], [], [], []
             for s, n in enumerate(q_lens):
                 t0 = int(q_start[s])
                 for a in range(0, n, ATTENTION_TILE):
                     tiles0.append(t0 + a)
                     tilesn.append(min(ATTENTION_TILE, n - a))
-            n_tiles = len(tiles0)
+                if n >= ATTENTION_WIDE_MIN:
+                    for a in range(0, n, ATTENTION_WIDE_TILE):
+                        wide0.append(t0 + a)
+                        widen.append(min(ATTENTION_WIDE_TILE, n - a))
+                else:
+                    k = (n + ATTENTION_TILE - 1) // ATTENTION_TILE
+                    rest0.extend(tiles0[-k:])
+                    restn.extend(tilesn[-k:])
+            n_tiles, n_wide, n_rest = len(tiles0), len(wide0), len(rest0)
             host[off["tile0"]: off["tile0"] + n_tiles] = tiles0
             host[off["tilen"]: off["tilen"] + n_tiles] = tilesn
+            host[off["wtile0"]: off["wtile0"] + n_wide + n_rest] = wide0 + rest0
+            host[off["wtilen"]: off["wtilen"] + n_wide + n_rest] = widen + restn
         buf.upload(i, B)
 
         d = buf.dev
@@ -221,6 +236,10 @@ class Stepper:
         ctx.logit_rows = d[off["rows"]: off["rows"] + R]
         ctx.tile_tok0 = d[off["tile0"]: off["tile0"] + n_tiles]
         ctx.tile_rows = d[off["tilen"]: off["tilen"] + n_tiles]
+        ctx.wide_tile_tok0 = d[off["wtile0"]: off["wtile0"] + n_wide]
+        ctx.wide_tile_rows = d[off["wtilen"]: off["wtilen"] + n_wide]
+        ctx.rest_tile_tok0 = d[off["wtile0"] + n_wide: off["wtile0"] + n_wide + n_rest]
+        ctx.rest_tile_rows = d[off["wtilen"] + n_wide: off["wtilen"] + n_wide + n_rest]
         ctx.q_start = d[off["q_start"]: off["q_start"] + B + 1]
         ctx.kv_len = d[off["kv_len"]: off["kv_len"] + B]
         ctx.state_slots = d[off["slots"]: off["slots"] + B]

@@ -5,12 +5,17 @@ bfloat16: the MMA kernels of csrc/variants/attention_mma.cu, compiled on first u
 head size: the split-key decode kernel when every sequence brings one token, else the tiled
 prefill kernel (a decode token beside prompt portions is a tile of one row).  The step function
 cuts every sequence's new tokens into tiles of `engine.step.ATTENTION_TILE` = 32 tokens.
+For head sizes 64 and 128 and page sizes 8..128 (powers of two) the portions of at least
+`ATTENTION_WIDE_MIN` tokens go to the tensor-memory kernel of csrc/variants/attention_tc.cu in
+tiles of 128 tokens instead, and only the short ones to the 32-token kernel
+(`IMP_B200_ATTN_PREFILL=mma` keeps everything on the latter).
 """
 from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_int64, c_void_p
-from typing import Dict
+import os
+from typing import Dict, Optional
 
 import torch
 
@@ -52,6 +57,62 @@ def variant(head_dim: int) -> ctypes.CDLL:
                                          c_int, c_float, c_int, c_void_p, c_void_p]
         _variants[head_dim] = lib
     return lib
+
+
+TC_HEAD_DIMS = (64, 128)
+PREFILL_BACKEND = os.environ.get("IMP_B200_ATTN_PREFILL", "tcgen05")   # "tcgen05" | "mma"
+_tc_variants: Dict[int, ctypes.CDLL] = {}
+
+
+def tc_variant(head_dim: int) -> ctypes.CDLL:
+    """The tensor-memory prefill kernel for this head size (64 or 128), built on first use."""
+    lib = _tc_variants.get(head_dim)
+    if lib is None:
+        from ..csrc.build import build_variant
+        if head_dim not in TC_HEAD_DIMS:
+            raise L.KernelError(f"the tensor-memory prefill kernel exists for head sizes {TC_HEAD_DIMS}, not {head_dim}")
+        path = build_variant("attention_tc.cu", {"IMP_ATTN_DH": head_dim})
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise L.KernelError(f"cannot load {path}: {e}") from None
+        lib.imp_last_error.restype = ctypes.c_char_p
+        lib.imp_attn_tc_head_dim.restype = c_int
+        assert lib.imp_attn_tc_head_dim() == head_dim
+        lib.imp_attn_prefill_tc_supported.restype = c_int
+        lib.imp_attn_prefill_tc_supported.argtypes = [c_int64, c_int64, c_int]
+        lib.imp_attn_prefill_tc.restype = c_int
+        lib.imp_attn_prefill_tc.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+        _tc_variants[head_dim] = lib
+    return lib
+
+
+def prefill_tc_supported(head_dim: int, q, out, k_cache) -> bool:
+    """Whether the tensor-memory prefill kernel takes this geometry (else the 32-token kernel runs)."""
+    if PREFILL_BACKEND != "tcgen05" or head_dim not in TC_HEAD_DIMS or q.dtype != torch.bfloat16:
+        return False
+    if q.data_ptr() % 16 or out.data_ptr() % 16 or k_cache.data_ptr() % 16:
+        return False
+    return bool(tc_variant(head_dim).imp_attn_prefill_tc_supported(q.stride(0), out.stride(0), k_cache.shape[2]))
+
+
+def prefill_attention_tc(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token,
+                         positions, tile_tok0, tile_rows, scale, window, status):
+    """Tiles of up to 128 consecutive query tokens of one sequence over the cached keys, on tcgen05 (bfloat16)."""
+    lib = tc_variant(head_dim)
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert tile_tok0.dtype == torch.int32 and tile_rows.dtype == torch.int32 and tile_tok0.numel() == tile_rows.numel()
+    _check(lib, lib.imp_attn_prefill_tc(
+        out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), q.shape[0], k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(),
+        tile_tok0.data_ptr(), tile_rows.data_ptr(), tile_tok0.numel(), block_table.shape[0], n_q_heads, n_kv_heads,
+        page_size, num_pages, float(scale), int(window), None if status is None else status.data_ptr(),
+        torch.cuda.current_stream().cuda_stream), "attention prefill (tcgen05)")
+    return out
 
 
 def _check(lib, rc: int, what: str) -> None:
@@ -131,5 +192,13 @@ def paged_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, b
     if ctx.decode_only:
         return decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
                                 ctx.seq_of_token, ctx.positions, scale, window, rt.status)
+    wide = getattr(ctx, "wide_tile_tok0", None)
+    if wide is not None and wide.numel() and prefill_tc_supported(head_dim, q, out, k_cache):
+        prefill_attention_tc(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx.seq_of_token,
+                             ctx.positions, ctx.wide_tile_tok0, ctx.wide_tile_rows, scale, window, rt.status)
+        if ctx.rest_tile_tok0.numel():
+            prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx.seq_of_token,
+                              ctx.positions, ctx.rest_tile_tok0, ctx.rest_tile_rows, scale, window, rt.status)
+        return out
     return prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
                              ctx.seq_of_token, ctx.positions, ctx.tile_tok0, ctx.tile_rows, scale, window, rt.status)

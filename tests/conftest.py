@@ -39,7 +39,16 @@ TINY_C = {
     "sliding_window": 9, "layer_types": ["sliding_attention", "full_attention", "sliding_attention",
                                          "full_attention"], "max_position_embeddings": 768,
 }
-TINY = {"A": (TINY_A, 0.05, 4), "B": (TINY_B, 0.08, 16), "C": (TINY_C, 0.06, 8)}  # config, weight std, page size
+# D: head size 64 with two query heads per kv head, so that prompt portions of 64 tokens and more run on
+#    the tensor-memory attention kernel (128-token tiles); a 100-token window on the first layer.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "vocab_size": 211, "hidden_size": 112, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 152,
+    "rms_norm_eps": 2e-6, "rope_theta": 300000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+    "sliding_window": 100, "layer_types": ["sliding_attention", "full_attention"], "max_position_embeddings": 1024,
+}
+# config, weight std, page size
+TINY = {"A": (TINY_A, 0.05, 4), "B": (TINY_B, 0.08, 16), "C": (TINY_C, 0.06, 8), "D": (TINY_D, 0.06, 16)}
 
 
 @pytest.fixture(scope="session")

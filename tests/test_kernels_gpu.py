@@ -522,6 +522,104 @@ def test_attention_finds_one_far_key_among_hundreds(K, where):
         close(out.view(T, Hq, Dh), want, dtype)
 
 
+def run_prefill_tc(K, lengths, counts, Hq, Hkv, Dh, page, window, seed=11, spike=None, holes=True):
+    """The tensor-memory prefill kernel on the last `counts` tokens of each sequence, in tiles of 128."""
+    from imp_b200.ops import attention as A
+    status = K.new_status(DEV)
+    bt, num_pages, kc, vc, dense, toks, q = attention_case(lengths, counts, Hq, Hkv, Dh, page, torch.bfloat16, seed=seed,
+                                                           spike=spike)
+    T = len(toks)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    btd = bt.clone()
+    if window and holes:
+        for s, n in enumerate(lengths):
+            first = max(0, (n - counts[s]) - window + 1)
+            btd[s, :first // page] = -1
+    tiles0, tilesn, t = [], [], 0
+    for n in counts:
+        for a in range(0, n, 128):
+            tiles0.append(t + a); tilesn.append(min(128, n - a))
+        t += n
+    qd = q.reshape(T, Hq * Dh).to(DEV)
+    assert A.prefill_tc_supported(Dh, qd, qd, kc.to(DEV))
+    out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    A.prefill_attention_tc(out, qd, Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), btd.to(DEV), seq, pos,
+                           torch.tensor(tiles0, dtype=torch.int32, device=DEV),
+                           torch.tensor(tilesn, dtype=torch.int32, device=DEV), 1 / math.sqrt(Dh), window, status)
+    K.check_status(status)
+    want = attention_reference(dense, toks, window)
+    close(out.view(T, Hq, Dh), want, torch.bfloat16)
+    return out, want
+
+
+@pytest.mark.parametrize("Dh,Hq,Hkv,page,window", [
+    (128, 8, 2, 16, 0),      # the common shape: groups of 4, two heads per CTA
+    (128, 3, 3, 16, 0),      # no grouping: one head per CTA
+    (128, 6, 2, 8, 0),       # odd group: one head per CTA
+    (64, 4, 1, 32, 0), (64, 2, 2, 128, 0), (64, 4, 2, 64, 0),
+    (128, 4, 2, 16, 100), (64, 4, 4, 8, 300), (128, 2, 1, 32, 128), (64, 6, 3, 16, 37),
+])
+def test_attention_tc_prefill_shapes_pages_windows(K, Dh, Hq, Hkv, page, window):
+    # whole prompts, portions that start inside a page and a tile, single rows, a ragged last tile
+    run_prefill_tc(K, [300, 517, 129, 700], [300, 200, 1, 131], Hq, Hkv, Dh, page, window)
+    run_prefill_tc(K, [1000], [128], Hq, Hkv, Dh, page, window, seed=12)
+    run_prefill_tc(K, [257, 64], [257, 64], Hq, Hkv, Dh, page, window, seed=13)
+
+
+@pytest.mark.parametrize("where", ["first", "page_edge", "tile_edge", "far"])
+def test_attention_tc_prefill_finds_one_far_key(K, where):
+    """One key's score stands out in every sequence; its value (5.0 everywhere) must dominate head 0 of each group."""
+    spike = {"first": lambda n: 0, "page_edge": lambda n: 16 * (n // 32) - 1, "tile_edge": lambda n: 128 * (n // 256),
+             "far": lambda n: n // 7}[where]
+    out, want = run_prefill_tc(K, [900, 400], [1, 130], 4, 2, 128, 16, 0, seed=3, spike=spike)
+    assert (want[0].view(2, 2, 128)[:, 0, :] > 4.5).all()
+
+
+def test_attention_tc_prefill_rescales_when_the_maximum_grows(K):
+    """Scores that grow along the keys force the accumulator in tensor memory through its rescale path; scores
+    that fall never rescale after the first tile.  Both must agree with the plain reference."""
+    from imp_b200.ops import attention as A
+    Hq, Hkv, Dh, page, n = 2, 1, 128, 16, 640
+    for direction in (1.0, -1.0):
+        status = K.new_status(DEV)
+        bt, num_pages, kc, vc, dense, toks, q = attention_case([n], [n], Hq, Hkv, Dh, page, torch.bfloat16, seed=5)
+        # key j gets a component along dimension 0 that grows (or falls) with j; queries look along dimension 0
+        ramp = (direction * torch.arange(n, dtype=torch.float32) * 0.25).to(torch.bfloat16)
+        qd_, kd_, vd_ = dense[0]
+        kd_[:, :, 0] = ramp[:, None]
+        qd_[:, :, 0] = 8.0
+        q[:, :, 0] = 8.0
+        for j in range(n):
+            kc[int(bt[0, j // page]), :, j % page, 0] = ramp[j]
+        T = n
+        seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+        pos = torch.arange(T, dtype=torch.int32, device=DEV)
+        tiles0 = list(range(0, n, 128))
+        out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        A.prefill_attention_tc(out, q.reshape(T, Hq * Dh).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
+                               torch.tensor(tiles0, dtype=torch.int32, device=DEV),
+                               torch.full((len(tiles0),), 128, dtype=torch.int32, device=DEV), 1 / math.sqrt(Dh), 0, status)
+        K.check_status(status)
+        close(out.view(T, Hq, Dh), attention_reference(dense, toks, 0), torch.bfloat16)
+
+
+def test_attention_tc_prefill_reports_a_bad_page(K):
+    from imp_b200.ops import attention as A
+    Hq, Hkv, Dh, page = 2, 1, 64, 16
+    bt, num_pages, kc, vc, dense, toks, q = attention_case([200], [200], Hq, Hkv, Dh, page, torch.bfloat16)
+    bt[0, 3] = num_pages + 5
+    seq = torch.zeros(200, dtype=torch.int32, device=DEV)
+    pos = torch.arange(200, dtype=torch.int32, device=DEV)
+    status = K.new_status(DEV)
+    out = torch.empty(200, Hq * Dh, dtype=torch.bfloat16, device=DEV)
+    A.prefill_attention_tc(out, q.reshape(200, -1).to(DEV), Hq, Hkv, Dh, kc.to(DEV), vc.to(DEV), bt.to(DEV), seq, pos,
+                           torch.tensor([0, 128], dtype=torch.int32, device=DEV),
+                           torch.tensor([128, 72], dtype=torch.int32, device=DEV), 0.1, 0, status)
+    with pytest.raises(Exception, match="page"):
+        K.check_status(status)
+
+
 def test_attention_reports_a_bad_page(K):
     from imp_b200.ops import attention as A
     Hq, Hkv, Dh, page = 2, 1, 32, 16

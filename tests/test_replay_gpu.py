@@ -10,11 +10,12 @@ from replay_helpers import collect, mixed, portions, round64, run_trace, tail_de
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (5, 9, 1, 70, 33, 47), "B": (1, 17, 33, 40, 96, 64), "C": (3, 50, 81, 26, 2, 65)}
+LENGTHS = {"A": (5, 9, 1, 70, 33, 47), "B": (1, 17, 33, 40, 96, 64), "C": (3, 50, 81, 26, 2, 65),
+           "D": (200, 70, 3, 333, 129, 64)}
 
 
 def make_requests(name, vocab):
-    g = torch.Generator().manual_seed({"A": 0, "B": 1, "C": 2}[name])
+    g = torch.Generator().manual_seed({"A": 0, "B": 1, "C": 2, "D": 3}[name])
     return {f"r{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[name])}
 
 
@@ -52,7 +53,7 @@ def check_rows(rows, reqs, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_all_ways_of_cutting(name, dtype, model_folders, expected, tmp_path):
     folder, cd, page = model_folders[name]
     V = cd["vocab_size"]
@@ -60,11 +61,11 @@ def test_replay_all_ways_of_cutting(name, dtype, model_folders, expected, tmp_pa
     longest = round64(max(len(v) for v in reqs.values()))
 
     results = {}
-    for label, steps, pool in (
-        ("whole", whole(reqs), longest),
-        ("tail", tail_decode(reqs), longest),
-        ("portions", portions(reqs), longest),
-    ):
+    cuts = [("whole", whole(reqs), longest), ("tail", tail_decode(reqs), longest), ("portions", portions(reqs), longest)]
+    if name == "D":
+        # portions long enough for the 128-token attention tiles, starting inside pages and tiles
+        cuts.append(("wide_portions", portions(reqs, sizes=(70, 130, 2, 64, 100, 67)), longest))
+    for label, steps, pool in cuts:
         out = run_trace(folder, dtype, steps, pool, str(tmp_path / label), V, page_size=page)
         rows = collect(steps, out)
         check_rows(rows, reqs, ref, dtype)
@@ -82,6 +83,6 @@ def test_replay_all_ways_of_cutting(name, dtype, model_folders, expected, tmp_pa
     if dtype == "float32":
         # The float32 kernels reduce every row in an order that depends on that row alone, so the
         # logits of a position are the same bits however the work was cut and batched.
-        for label in ("tail", "portions", "mixed"):
+        for label in [c[0] for c in cuts[1:]] + ["mixed"]:
             for key, row in results["whole"].items():
                 assert np.array_equal(row, results[label][key]), f"{label}: {key} differs from the whole run"
