@@ -5,7 +5,7 @@
 // heads that share a kv head, and walks the cached keys of the sequence in tiles of 128 from the
 // window's start to the last token's position (keys come from the pages only; the new tokens'
 // keys are already there).  Roles:
-//   warp 0, lane 0   producer.  Q tiles once, then per key tile the K pages and the V pages of the
+//   warp 0           producer.  Q tiles once, then per key tile the K pages and the V pages of the
 //                    kv head with TMA (cp.async.bulk.tensor, 128-byte swizzle), one box per page
 //                    and 64 head dimensions, into shared-memory rings; page ids come from the block
 //                    table, pages that do not exist are fetched from beyond the tensor (zeros).
@@ -14,7 +14,7 @@
 //                    MN-major operand straight from its [key, dim] layout.  After P_w V of tile i
 //                    it issues Q_w K^T of tile i+1, so while one head's softmax runs the tensor
 //                    cores work on the other head.
-//   warps 2..5 (head 0), 6..9 (head 1)   softmax.  A thread owns one query row: it reads its row of
+//   warps 4..7 (head 0), 8..11 (head 1)   softmax.  A thread owns one query row: it reads its row of
 //                    S from tensor memory, applies the causal / window mask on tiles that need it,
 //                    keeps the running maximum and sum in 32-bit, writes P = exp2(s - m) as bfloat16
 //                    into shared memory in the K-major swizzled layout the MMA reads, and at the
@@ -51,7 +51,7 @@ constexpr float FA_RESCALE_STEP = 8.f;           // log2 of the growth of a row 
 template <int NQ> struct FaCfg {
     static constexpr int K_STAGES = (DH == 128 && NQ == 2) ? 1 : 2;
     static constexpr int V_STAGES = 2;
-    static constexpr int THREADS = 64 + 128 * NQ;
+    static constexpr int THREADS = 128 + 128 * NQ;        // warps 0-3: producer, MMA issuer, two idle; then 4 per head
     static constexpr int TMEM_COLS = 256 * NQ;
     static constexpr int TILE_BYTES = NQ * (FA_Q_BYTES + FA_P_BYTES) + (K_STAGES + V_STAGES) * FA_KV_BYTES;
     static constexpr int N_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 3 * NQ;
@@ -150,48 +150,62 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // With two heads the 384 threads start with 168 registers each; the softmax threads hold a whole row of S
+    // (128 values) and take registers over from the first warpgroup, which needs few.
+    if (warp < 4) {
+    if (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == 0) {
-        if (lane == 0 && n_kt > 0) {
-            // ------------------------------------------------------------------ producer
-            mbar_expect_tx(q_full, NQ * FA_Q_BYTES);
-            for (int w = 0; w < NQ; ++w)
-                for (int kb = 0; kb < FA_KB; ++kb)
-                    tma_load_2d(smem_u32(q_s + w * FA_Q_BYTES + kb * FA_BLOCK_BYTES), &map_q, (head0 + w) * DH + kb * 64, tok0,
-                                q_full);
+        if (n_kt > 0) {
+            // ------------------------------------------------------------------ producer (whole warp)
+            // Lane 0 waits for a free stage and announces the bytes; then every lane fetches boxes: box b of a tile is
+            // page b / FA_KB, head-dimension block b % FA_KB.  Page ids are read before the wait, so the table lookup
+            // overlaps it.
+            if (lane == 0) {
+                mbar_expect_tx(q_full, NQ * FA_Q_BYTES);
+                for (int w = 0; w < NQ; ++w)
+                    for (int kb = 0; kb < FA_KB; ++kb)
+                        tma_load_2d(smem_u32(q_s + w * FA_Q_BYTES + kb * FA_BLOCK_BYTES), &map_q, (head0 + w) * DH + kb * 64,
+                                    tok0, q_full);
+            }
             const int* bt = block_table + (int64_t)seq * bt_stride;
             const int pages_per_tile = FA_BN / P;
+            const int boxes = pages_per_tile * FA_KB;         // at most 32: page sizes start at 8
             const int oob_row = num_pages * Hkv * P;          // a box that starts here is all zeros
+            const int my_pg = lane / FA_KB, my_kb = lane % FA_KB;
             bool ok = true;
             int k_issued = 0, v_issued = 0;
             for (int i = 0; i < n_kt && ok; ++i) {
-                const int page0 = (kt_lo + i) * pages_per_tile;
+                int y = oob_row;
+                if (lane < boxes) {
+                    const int idx = (kt_lo + i) * pages_per_tile + my_pg;
+                    const int page = idx < bt_stride ? bt[idx] : -1;
+                    if (page >= 0 && page < num_pages) {
+                        y = (page * Hkv + hk) * P;
+                    } else if (idx * P <= pos_last && idx * P + P - 1 >= first_key) {
+                        // some row of this tile reads the page: it starts at or before the last position and ends inside
+                        // the first row's window
+                        imp_report(status, IMP_BAD_PAGE);
+                    }
+                }
                 for (int kv = 0; kv < 2 && ok; ++kv) {
                     const int stages = kv == 0 ? KS : VS;
                     const int s = i % stages;
                     const uint32_t full = (kv == 0 ? k_full0 : v_full0) + 8 * s;
                     const uint32_t empty = (kv == 0 ? k_empty0 : v_empty0) + 8 * s;
-                    ok = mbar_wait(empty, ((uint32_t)(i / stages) & 1u) ^ 1u, status);
-                    if (!ok) break;
-                    mbar_expect_tx(full, FA_KV_BYTES);
-                    unsigned char* dst = (kv == 0 ? k_s : v_s) + s * FA_KV_BYTES;
-                    for (int pg = 0; pg < pages_per_tile; ++pg) {
-                        const int idx = page0 + pg;
-                        int page = idx < bt_stride ? bt[idx] : -1;
-                        if (page < 0 || page >= num_pages) {
-                            // needed by some row of this tile only when it starts at or before the last position
-                            // and inside the window of the first row
-                            if (idx * P <= pos_last && idx * P + P - 1 >= first_key) imp_report(status, IMP_BAD_PAGE);
-                            page = -1;
-                        }
-                        const int y = page < 0 ? oob_row : (page * Hkv + hk) * P;
-                        for (int kb = 0; kb < FA_KB; ++kb)
-                            tma_load_2d(smem_u32(dst + kb * FA_BLOCK_BYTES + pg * P * 128), kv == 0 ? &map_k : &map_v, kb * 64,
-                                        y, full);
+                    if (lane == 0) {
+                        ok = mbar_wait(empty, ((uint32_t)(i / stages) & 1u) ^ 1u, status);
+                        if (ok) mbar_expect_tx(full, FA_KV_BYTES);
                     }
+                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                    if (!ok) break;
+                    unsigned char* dst = (kv == 0 ? k_s : v_s) + s * FA_KV_BYTES;
+                    if (lane < boxes)
+                        tma_load_2d(smem_u32(dst + my_kb * FA_BLOCK_BYTES + my_pg * P * 128), kv == 0 ? &map_k : &map_v,
+                                    my_kb * 64, y, full);
                     if (kv == 0) k_issued = i + 1; else v_issued = i + 1;
                 }
             }
-            if (!ok) {   // let the copies in flight land before the CTA's shared memory is released
+            if (!ok && lane == 0) {   // let the copies in flight land before the CTA's shared memory is released
                 mbar_wait(q_full, 0, nullptr);
                 for (int i = k_issued > KS ? k_issued - KS : 0; i < k_issued; ++i)
                     mbar_wait(k_full0 + 8 * (i % KS), (uint32_t)(i / KS) & 1u, nullptr);
@@ -247,9 +261,11 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 }
             }
         }
+    }
     } else {
         // -------------------------------------------------------------------- softmax
-        const int w = (warp - 2) >> 2;                       // which head of the CTA
+        if (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        const int w = (warp - 4) >> 2;                       // which head of the CTA
         const int row = (warp & 3) * 32 + lane;              // tensor-memory lane = query row of the tile
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_tmem = lane_base + (uint32_t)(w * 256), o_tmem = s_tmem + 128u;
@@ -266,21 +282,28 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             const bool masked = (k0 + FA_BN - 1 > pos0) || (window > 0 && pos0 + FA_BM - 1 - k0 >= window);
             const int hi = p - k0;                                        // columns <= hi are not in the future
             const int lo = window > 0 ? p - window + 1 - k0 : -(1 << 30); // columns >= lo are inside the window
+            // the whole row of S: four loads in flight, one wait
+            uint32_t sr[FA_BN / 32][32];
+#pragma unroll
+            for (int c = 0; c < FA_BN / 32; ++c) tc_ld32_issue(s_tmem + (uint32_t)(c * 32), sr[c]);
+            tc_wait_ld_pin<true>(sr[0]);
+#pragma unroll
+            for (int c = 1; c < FA_BN / 32; ++c) tc_wait_ld_pin<false>(sr[c]);
             float tmax = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FA_BN / 32; ++c) {
-                float v[32];
-                tc_ld32(s_tmem + (uint32_t)(c * 32), v);
-                if (masked) {
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < FA_BN / 32; ++c)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int col = c * 32 + j;
-                        if (col <= hi && col >= lo) tmax = fmaxf(tmax, v[j]);
+                        if (!(col <= hi && col >= lo)) sr[c][j] = 0xff800000u;   // -inf
+                        tmax = fmaxf(tmax, __uint_as_float(sr[c][j]));
                     }
-                } else {
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, v[j]);
-                }
+                for (int c = 0; c < FA_BN / 32; ++c)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(sr[c][j]));
             }
             tmax *= scale_log2;                                           // scale > 0: the order is kept
             const bool grow = tmax > m_used + FA_RESCALE_STEP;            // also true for the first finite maximum
@@ -303,17 +326,13 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 m_used = m_new;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;    // a row with nothing visible yet
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < FA_BN / 32; ++c) {
                 float v[32];
-                tc_ld32(s_tmem + (uint32_t)(c * 32), v);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const int col = c * 32 + j;
-                    float e = fa_exp2(fmaf(v[j], scale_log2, -m_sub));
-                    if (masked && !(col <= hi && col >= lo)) e = 0.f;
-                    v[j] = e;
-                    l += e;
+                    v[j] = fa_exp2(fmaf(__uint_as_float(sr[c][j]), scale_log2, -m_sub));   // exp2(-inf) = 0 for masked keys
+                    l += v[j];
                 }
                 // 32 keys = four 16-byte chunks of this row in key block c / 2
                 unsigned char* blk = p_row + (c >> 1) * FA_BLOCK_BYTES;
