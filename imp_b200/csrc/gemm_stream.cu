@@ -18,15 +18,16 @@
 // 496-649, CUDA cores, one warp per output row) and cuBLASLt for 2 <= M <= 64 (:148-156).
 #include "common.cuh"
 
+#include <cstdlib>
+
 constexpr int GS_WARPS = 4;
 constexpr int GS_KB = 64;                          // elements of K per warp and stage
 constexpr int GS_STAGE_K = GS_KB * GS_WARPS;       // 256 elements of K per stage
-constexpr int gs_stages(int nt) { return 6; }
 constexpr int GS_RED_BYTES = 4 * 8 * 32 * 4;      // reduction buffer: 4 warps x (up to 8 slots) x 32 lanes
 constexpr int GS_ROW_BYTES = GS_STAGE_K * 2 + 16;  // 528: rows 16 bytes apart modulo 128 -> conflict-free 16-byte reads
 constexpr int GS_W_BYTES = 16 * GS_ROW_BYTES;      // weight part of a stage; 8*NT activation rows follow
 constexpr int gs_stage_bytes(int nt) { return (16 + 8 * nt) * GS_ROW_BYTES; }
-constexpr int gs_smem_bytes(int nt) { return gs_stages(nt) * gs_stage_bytes(nt) + GS_RED_BYTES; }
+constexpr int gs_smem_bytes(int nt, int stages) { return stages * gs_stage_bytes(nt) + GS_RED_BYTES; }
 
 __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -47,13 +48,12 @@ template <int N> __device__ __forceinline__ void gs_wait_group() {
 // SWIGLU: the 16 rows of a CTA are 8 gate rows followed by their 8 up rows (the caller interleaves
 // the two matrices in blocks of 8 rows), so accumulator slots c and c+2 of a lane hold gate and up
 // of the same output column and token; the epilogue writes silu(gate) * up into C[M, N/2].
-template <int NT, typename TO, bool SWIGLU>
+template <int NT, typename TO, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restrict__ C, int64_t ldc,
                                                                     const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                     const __nv_bfloat16* __restrict__ W, int64_t ldw,
                                                                     int M, int N, int K) {
     extern __shared__ __align__(128) unsigned char gs_smem[];
-    constexpr int STAGES = gs_stages(NT);
     constexpr int STAGE_BYTES = gs_stage_bytes(NT);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -189,13 +189,13 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
     gs_wait_group<0>();
 }
 
-template <int NT, typename TO, bool SWIGLU>
-static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+template <int NT, typename TO, bool SWIGLU, int STAGES>
+static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
     static bool attr_set = false;   // once per instantiation (one device per process)
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gs_smem_bytes(NT));
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gs_smem_bytes(NT, STAGES));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
@@ -203,8 +203,27 @@ static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, 
     // One tile per CTA measured faster than two persistent CTAs per SM on every shape of the 8B model
     // (the kernel itself takes any grid size: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...).
     const int grid = n_tiles;
-    return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU>, dim3(grid), dim3(GS_WARPS * 32), gs_smem_bytes(NT), s, C, ldc,
+    return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU, STAGES>, dim3(grid), dim3(GS_WARPS * 32), gs_smem_bytes(NT, STAGES), s, C, ldc,
                       A, lda, W, ldw, M, N, K);
+}
+
+static int gs_env_stages() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("IMP_B200_GS_STAGES");
+        v = e ? atoi(e) : 5;
+    }
+    return v;
+}
+
+template <int NT, typename TO, bool SWIGLU>
+static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+                                    int64_t ldw, int M, int N, int K, cudaStream_t s) {
+    switch (gs_env_stages()) {
+        case 4: return launch_stream_st<NT, TO, SWIGLU, 4>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 5: return launch_stream_st<NT, TO, SWIGLU, 5>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        default: return launch_stream_st<NT, TO, SWIGLU, 6>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    }
 }
 
 template <typename TO, bool SWIGLU>

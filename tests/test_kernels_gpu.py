@@ -288,7 +288,8 @@ def paged_layout(lengths, page_size, n_extra_pages=3, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,Dh,rot,page", [(4, 2, 16, 16, 4), (6, 3, 32, 32, 16), (5, 5, 48, 24, 3), (8, 1, 128, 128, 16)])
+@pytest.mark.parametrize("Hq,Hkv,Dh,rot,page", [(4, 2, 16, 16, 4), (6, 3, 32, 32, 16), (5, 5, 48, 24, 3), (8, 1, 128, 128, 16),
+                                                (2, 1, 256, 256, 16), (3, 1, 80, 40, 5), (2, 2, 16, 6, 4)])
 def test_qk_norm_rope_kv_write(K, dtype, Hq, Hkv, Dh, rot, page):
     lengths = [11, 1, 30]
     starts = [4, 0, 17]                                    # tokens of this step continue sequences at these positions
