@@ -30,6 +30,8 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 LINK_FLAGS = ["-shared", "-Xcompiler", "-fPIC"]
+# Extra compiler flags for experiments (e.g. "-DIMP_PDL_EARLY=0"); part of the build's hash.
+NVCC_FLAGS += os.environ.get("IMP_B200_NVCC_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):

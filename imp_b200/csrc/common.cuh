@@ -50,8 +50,25 @@ void imp_set_error(const char* fmt, ...);
 // of the stream may have written, and calls pdl_launch_dependents() so that the next kernel's
 // blocks may become resident while this one still runs (they stop at their own pdl_wait()).
 // Launched without the attribute (or after a kernel of another library) both are no-ops.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Kernels call the two in the order wait, launch_dependents.  With IMP_PDL_EARLY (the default) the
+// trigger is issued by pdl_wait() itself, before the wait: the next kernel's blocks may then become
+// resident (and fetch what does not depend on earlier kernels, e.g. weights) while the kernel before
+// this one still runs.  That is safe because every kernel waits for its own predecessor before it
+// touches anything an earlier kernel wrote, and completion is transitive along the stream.
+#ifndef IMP_PDL_EARLY
+#define IMP_PDL_EARLY 1
+#endif
+__device__ __forceinline__ void pdl_wait() {
+#if IMP_PDL_EARLY
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+#if !IMP_PDL_EARLY
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
 
 // 1 unless the environment variable IMP_B200_NO_PDL is set (read once).
 int imp_pdl_enabled();
