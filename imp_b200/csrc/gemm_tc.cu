@@ -326,11 +326,12 @@ __global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(cons
 // Epilogue: lane r of the accumulator is output column n0 + r, column t is token t, so consecutive
 // lanes write consecutive addresses of C[t, :].  With interleaved gate/up weight rows (SwiGLU,
 // splits == 1) lanes r and r + 8 of every 16 hold gate and up of one output column.
-constexpr int TCS_STAGES = 6;
 constexpr int TCS_W_BYTES = 128 * TC_BK * 2;   // 16 KiB
 
+// Up to 64 tokens: four stages of 24 KiB, so that two CTAs share an SM (and its memory pipes); more: six of 32 KiB.
+template <int BN> constexpr int tcs_stages() { return BN <= 64 ? 4 : 6; }
 template <int BN> constexpr int tcs_stage_bytes() { return TCS_W_BYTES + BN * TC_BK * 2; }
-template <int BN> constexpr int tcs_smem_bytes() { return TCS_STAGES * tcs_stage_bytes<BN>() + 1024 + 256; }
+template <int BN> constexpr int tcs_smem_bytes() { return tcs_stages<BN>() * tcs_stage_bytes<BN>() + 1024 + 256; }
 
 // EPI: 0 = bfloat16 C[M,N], 1 = float32 C[M,N] (also the split partials), 2 = SwiGLU bfloat16 C[M,N/2]
 template <int BN, int EPI>
@@ -338,8 +339,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
                                                               const __grid_constant__ CUtensorMap map_x, void* __restrict__ Cv,
                                                               int64_t ldc, int64_t split_stride, int M, int N, int K,
                                                               int kb_per_split, int* status) {
-    pdl_wait();
-    pdl_launch_dependents();
+    constexpr int TCS_STAGES = tcs_stages<BN>();
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = tcs_stage_bytes<BN>();
@@ -353,6 +353,8 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     const int k_blocks = max(kb_hi - kb_lo, 0);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TCS_STAGES), accum_bar = smem_u32(bars + 2 * TCS_STAGES);
 
+    // Nothing before pdl_wait() reads or writes what an earlier kernel of the stream may still be
+    // working on: barriers, tensor memory and the weight tiles of the first stages only.
     if (threadIdx.x == 0) {
         for (int s = 0; s < TCS_STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
@@ -375,7 +377,17 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     if (warp == 0 && lane == 0) {
         int issued = 0;
         bool ok = true;
-        for (int i = 0; i < k_blocks; ++i) {
+        // the weights of the first stages do not depend on the kernel before this one
+        const int early = k_blocks < TCS_STAGES ? k_blocks : TCS_STAGES;
+        for (int i = 0; i < early; ++i) {
+            mbar_expect_tx(full0 + 8 * i, STAGE);
+            tma_load_2d(smem_u32(tiles + i * STAGE), &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * i);
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i)
+            tma_load_2d(smem_u32(tiles + i * STAGE) + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, 0, full0 + 8 * i);
+        issued = early;
+        for (int i = early; i < k_blocks; ++i) {
             const int s = i % TCS_STAGES;
             ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status);
             if (!ok) break;
@@ -388,7 +400,10 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         if (!ok)
             for (int i = issued > TCS_STAGES ? issued - TCS_STAGES : 0; i < issued; ++i)
                 mbar_wait(full0 + 8 * (i % TCS_STAGES), (uint32_t)(i / TCS_STAGES) & 1u, nullptr);
-    } else if (warp == 1 && lane == 0) {
+    } else {
+        pdl_wait();
+    }
+    if (warp == 1 && lane == 0) {
         const uint32_t idesc = tc_instr_desc(128, BN);
         bool ok = true;
         for (int i = 0; i < k_blocks && ok; ++i) {
@@ -550,14 +565,15 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
 
 // ---- few rows (16 < M <= 128) -----------------------------------------------------------------------
 // Number of K splits imp_gemm_bf16_tc_swap will use, and the floats of scratch it then needs.
-static int tcs_splits(int N, int K, int epilogue) {
+static int tcs_splits(int M, int N, int K, int epilogue) {
     if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         sms = 148;
+    const int slots = M <= 64 ? 2 * sms : sms;          // resident CTAs: two per SM with 64-column tiles
     const int tiles = (N + 127) / 128;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
-    int splits = (sms + tiles - 1) / tiles;              // enough CTAs for every SM
+    int splits = slots / tiles;                          // as many CTAs as fit in one wave
     const int max_splits = total_kb / 8 > 0 ? total_kb / 8 : 1;   // at least 8 blocks of K per split
     if (splits > max_splits) splits = max_splits;
     if (splits > 16) splits = 16;
@@ -565,7 +581,7 @@ static int tcs_splits(int N, int K, int epilogue) {
 }
 
 IMP_API int64_t imp_gemm_bf16_tc_swap_scratch_floats(int M, int N, int K, int epilogue) {
-    const int splits = tcs_splits(N, K, epilogue);
+    const int splits = tcs_splits(M, N, K, epilogue);
     return splits > 1 ? (int64_t)splits * M * N : 0;
 }
 
@@ -580,8 +596,9 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
         attr_set = true;
     }
     dim3 grid((N + 127) / 128, 1, splits);
-    gemm_tc_swap_kernel<BN, EPI><<<grid, 128, tcs_smem_bytes<BN>(), s>>>(mw, mx, C, ldc, split_stride, M, N, K, kb_per_split,
-                                                                         status);
+    cudaError_t e = imp_launch(gemm_tc_swap_kernel<BN, EPI>, grid, dim3(128), (size_t)tcs_smem_bytes<BN>(), s, mw, mx, C, ldc,
+                               split_stride, M, N, K, kb_per_split, status);
+    if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
 
@@ -596,7 +613,7 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
     if (epilogue == 2) IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_tc_swap: %d interleaved rows are not a multiple of 16", N);
     IMP_CHECK_ARG(lda >= K && ldw >= K && ldc >= (epilogue == 2 ? N / 2 : N), "imp_gemm_bf16_tc_swap: leading dimension too small");
     if (K % 8 || lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16) return IMP_ERR_UNSUPPORTED;
-    const int splits = tcs_splits(N, K, epilogue);
+    const int splits = tcs_splits(M, N, K, epilogue);
     IMP_CHECK_ARG(splits == 1 || scratch, "imp_gemm_bf16_tc_swap: %d splits of K need scratch memory", splits);
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_per_split = (total_kb + splits - 1) / splits;
@@ -613,10 +630,14 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
         if (rc) return rc;
         const int64_t total = (int64_t)M * N;
         const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        cudaError_t e;
         if (epilogue == TC_OUT_F32)
-            gemm_tc_reduce_kernel<float><<<grid, 256, 0, s>>>((float*)C, ldc, scratch, split_stride, M, N, splits);
+            e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, (const float*)scratch,
+                           split_stride, M, N, splits);
         else
-            gemm_tc_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)C, ldc, scratch, split_stride, M, N, splits);
+            e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc,
+                           (const float*)scratch, split_stride, M, N, splits);
+        if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     } else if (epilogue == TC_OUT_BF16) {
         rc = BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
