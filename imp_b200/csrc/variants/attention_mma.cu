@@ -830,8 +830,8 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
     int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
     float* __restrict__ part_ml, int* status) {
-    pdl_wait();
-    pdl_launch_dependents();
+    // pdl_wait() comes later: the batch arrays and the keys before this step's position do not depend on the
+    // kernel before this one, so the first stages are requested while it still runs.
     extern __shared__ __align__(128) unsigned char dt_smem[];
     __shared__ __align__(8) uint64_t dt_bars[2 * DT_STAGES];     // [0,S) full, [S,2S) empty
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -875,39 +875,51 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     for (int r = 0; r < NR; ++r) { st.m[r] = -INFINITY; st.l[r] = 0.f; }
 
     if (warp == DT_CONSUMERS) {
+        // ---------------------------------------------------------------------- producer
+        bool ok = true;
+        int issued = 0;
+        auto issue_stage = [&](int s) {
+            const int it = s - stage_lo, slot = it % DT_STAGES;
+            const int j_stage = first_al + DT_KEYS * s;
+            uint32_t bytes = 0;
+            int64_t off[DT_CONSUMERS];
+#pragma unroll
+            for (int w = 0; w < DT_CONSUMERS; ++w) {
+                const int j0 = j_stage + 16 * w;
+                off[w] = -1;
+                if (j0 > pos || j0 + 15 < first) continue;          // every key of the step is masked: not fetched
+                const int lp = j0 / P;
+                const int page = bt[lp];
+                if (page < 0 || page >= num_pages) { imp_report(status, IMP_BAD_PAGE); continue; }
+                off[w] = (((int64_t)page * Hkv + hk) * P + (j0 - lp * P)) * DH;
+                bytes += 2 * DT_RUN_BYTES;
+            }
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * slot), "r"(bytes) : "memory");
+            const uint32_t sbase = ring + slot * DT_STAGE_BYTES;
+#pragma unroll
+            for (int w = 0; w < DT_CONSUMERS; ++w) {
+                if (off[w] < 0) continue;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(sbase + w * DT_RUN_BYTES), "l"(kc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(sbase + (DT_CONSUMERS + w) * DT_RUN_BYTES), "l"(vc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
+            }
+            issued = it + 1;
+        };
         if (lane == 0) {
-            // ------------------------------------------------------------------ producer
-            bool ok = true;
-            int issued = 0;
-            for (int s = stage_lo; s < stage_hi && ok; ++s) {
+            // stages that end before this step's own position hold keys of earlier steps only
+            for (int s = stage_lo; s < stage_hi && s - stage_lo < DT_STAGES; ++s) {
+                if (first_al + DT_KEYS * s + DT_KEYS - 1 >= pos) break;
+                issue_stage(s);
+            }
+        }
+        pdl_wait();
+        if (lane == 0) {
+            for (int s = stage_lo + issued; s < stage_hi && ok; ++s) {
                 const int it = s - stage_lo, slot = it % DT_STAGES;
                 ok = dt_wait(empty0 + 8 * slot, ((uint32_t)(it / DT_STAGES) & 1u) ^ 1u, status);
                 if (!ok) break;
-                const int j_stage = first_al + DT_KEYS * s;
-                uint32_t bytes = 0;
-                int64_t off[DT_CONSUMERS];
-#pragma unroll
-                for (int w = 0; w < DT_CONSUMERS; ++w) {
-                    const int j0 = j_stage + 16 * w;
-                    off[w] = -1;
-                    if (j0 > pos || j0 + 15 < first) continue;          // every key of the step is masked: not fetched
-                    const int lp = j0 / P;
-                    const int page = bt[lp];
-                    if (page < 0 || page >= num_pages) { imp_report(status, IMP_BAD_PAGE); continue; }
-                    off[w] = (((int64_t)page * Hkv + hk) * P + (j0 - lp * P)) * DH;
-                    bytes += 2 * DT_RUN_BYTES;
-                }
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * slot), "r"(bytes) : "memory");
-                const uint32_t sbase = ring + slot * DT_STAGE_BYTES;
-#pragma unroll
-                for (int w = 0; w < DT_CONSUMERS; ++w) {
-                    if (off[w] < 0) continue;
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(sbase + w * DT_RUN_BYTES), "l"(kc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(sbase + (DT_CONSUMERS + w) * DT_RUN_BYTES), "l"(vc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
-                }
-                issued = it + 1;
+                issue_stage(s);
             }
             if (!ok) {   // a bounded chance for the copies in flight to land before the memory is released
                 for (int it = issued > DT_STAGES ? issued - DT_STAGES : 0; it < issued; ++it)
@@ -916,6 +928,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         }
     } else {
         // -------------------------------------------------------------------- consumers
+        pdl_wait();
         RowInfo rows[2];
         const __nv_bfloat16* qrow[2];
 #pragma unroll
