@@ -207,11 +207,15 @@ static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, 
                       A, lda, W, ldw, M, N, K);
 }
 
+// Ring depth.  Five stages let three CTAs share an SM (444 resident CTAs on 148 SMs).  A product with
+// so few tiles that two CTAs per SM hold them all runs eight stages instead: every CTA then keeps
+// 56 KiB of weight reads in flight, which the memory needs when only a few hundred CTAs pull on it.
+// IMP_B200_GS_STAGES=4|5|6|8 forces one depth (for measurements).
 static int gs_env_stages() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("IMP_B200_GS_STAGES");
-        v = e ? atoi(e) : 5;
+        v = e ? atoi(e) : 0;
     }
     return v;
 }
@@ -219,10 +223,13 @@ static int gs_env_stages() {
 template <int NT, typename TO, bool SWIGLU>
 static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
-    switch (gs_env_stages()) {
+    int stages = gs_env_stages();
+    if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * 148) ? 8 : 5;
+    switch (stages) {
         case 4: return launch_stream_st<NT, TO, SWIGLU, 4>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        case 5: return launch_stream_st<NT, TO, SWIGLU, 5>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        default: return launch_stream_st<NT, TO, SWIGLU, 6>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 6: return launch_stream_st<NT, TO, SWIGLU, 6>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 8: return launch_stream_st<NT, TO, SWIGLU, 8>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        default: return launch_stream_st<NT, TO, SWIGLU, 5>(C, ldc, A, lda, W, ldw, M, N, K, s);
     }
 }
 
