@@ -23,11 +23,13 @@
 constexpr int GS_WARPS = 4;
 constexpr int GS_KB = 64;                          // elements of K per warp and stage
 constexpr int GS_STAGE_K = GS_KB * GS_WARPS;       // 256 elements of K per stage
-constexpr int GS_RED_BYTES = 4 * 8 * 32 * 4;      // reduction buffer: 4 warps x (up to 8 slots) x 32 lanes
+constexpr int GS_RED_BYTES = 4 * 8 * 32 * 4;      // reduction buffer per row group: 4 warps x (up to 8 slots) x 32 lanes
 constexpr int GS_ROW_BYTES = GS_STAGE_K * 2 + 16;  // 528: rows 16 bytes apart modulo 128 -> conflict-free 16-byte reads
-constexpr int GS_W_BYTES = 16 * GS_ROW_BYTES;      // weight part of a stage; 8*NT activation rows follow
-constexpr int gs_stage_bytes(int nt) { return (16 + 8 * nt) * GS_ROW_BYTES; }
-constexpr int gs_smem_bytes(int nt, int stages) { return stages * gs_stage_bytes(nt) + GS_RED_BYTES; }
+// A CTA owns RG groups of 16 weight rows (RG = 1 or 2; 4 warps per group); the groups share the staged
+// activation rows, so with RG = 2 the activations cross from the L2 half as often per weight byte.
+constexpr int gs_w_bytes(int rg) { return 16 * rg * GS_ROW_BYTES; }   // weight part of a stage; 8*NT activation rows follow
+constexpr int gs_stage_bytes(int nt, int rg) { return (16 * rg + 8 * nt) * GS_ROW_BYTES; }
+constexpr int gs_smem_bytes(int nt, int stages, int rg) { return stages * gs_stage_bytes(nt, rg) + rg * GS_RED_BYTES; }
 
 __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -48,35 +50,37 @@ template <int N> __device__ __forceinline__ void gs_wait_group() {
 // SWIGLU: the 16 rows of a CTA are 8 gate rows followed by their 8 up rows (the caller interleaves
 // the two matrices in blocks of 8 rows), so accumulator slots c and c+2 of a lane hold gate and up
 // of the same output column and token; the epilogue writes silu(gate) * up into C[M, N/2].
-template <int NT, typename TO, bool SWIGLU, int STAGES>
-__global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restrict__ C, int64_t ldc,
+template <int NT, typename TO, bool SWIGLU, int STAGES, int RG>
+__global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __restrict__ C, int64_t ldc,
                                                                     const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                     const __nv_bfloat16* __restrict__ W, int64_t ldw,
                                                                     int M, int N, int K) {
     extern __shared__ __align__(128) unsigned char gs_smem[];
-    constexpr int STAGE_BYTES = gs_stage_bytes(NT);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int STAGE_BYTES = gs_stage_bytes(NT, RG);
+    constexpr int THREADS = GS_WARPS * 32 * RG, ROWS = 16 * RG, W_BYTES = gs_w_bytes(RG);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int rg = (tid >> 5) / GS_WARPS, warp = (tid >> 5) % GS_WARPS;   // row group, and K block within a stage
     const int g = lane >> 2, t = lane & 3;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(gs_smem);
-    float(*red)[NT * 4][32] = reinterpret_cast<float(*)[NT * 4][32]>(gs_smem + STAGES * STAGE_BYTES);
+    float(*red)[NT * 4][32] = reinterpret_cast<float(*)[NT * 4][32]>(gs_smem + STAGES * STAGE_BYTES) + rg * GS_WARPS;
     const int n_stages = (K + GS_STAGE_K - 1) / GS_STAGE_K;
-    const int n_tiles = (N + 15) / 16;
+    const int n_tiles = (N + ROWS - 1) / ROWS;
     const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total = my_tiles * n_stages;       // steps of this CTA: (tile, stage) pairs in order
 
     // Producer side: step q_issue is (tile i_tile, stage i_stage).
     int q_issue = 0, i_tile = blockIdx.x, i_stage = 0;
-    // Weight copies of a step: 16 rows x 32 chunks of 16 bytes = 512 chunks, 4 per thread; chunk c ->
+    // Weight copies of a step: ROWS rows x 32 chunks of 16 bytes, 4 per thread; chunk c ->
     // row c / 32, column chunk c % 32, so a warp copies one row's 512 contiguous bytes.
     auto issue_w = [&]() {
         if (q_issue < total) {
             const uint32_t sbase = smem_base + (q_issue % STAGES) * STAGE_BYTES;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int c = tid + i * (GS_WARPS * 32);
+                const int c = tid + i * THREADS;
                 const int row = c >> 5, col = c & 31;
                 const int k = i_stage * GS_STAGE_K + col * 8;
-                const __nv_bfloat16* src = W + (int64_t)min(i_tile * 16 + row, N - 1) * ldw + min(k, K - 8);
+                const __nv_bfloat16* src = W + (int64_t)min(i_tile * ROWS + row, N - 1) * ldw + min(k, K - 8);
                 gs_cp_async(sbase + row * GS_ROW_BYTES + col * 16, src, k + 8 <= K ? 16 : 0);
             }
         }
@@ -84,10 +88,10 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
     // Activation copies: 8*NT rows x 32 chunks, 2*NT per thread; rows past M and columns past K are zeros.
     auto issue_a = [&]() {
         if (q_issue < total) {
-            const uint32_t sbase = smem_base + (q_issue % STAGES) * STAGE_BYTES + GS_W_BYTES;
+            const uint32_t sbase = smem_base + (q_issue % STAGES) * STAGE_BYTES + W_BYTES;
 #pragma unroll
-            for (int i = 0; i < 2 * NT; ++i) {
-                const int c = tid + i * (GS_WARPS * 32);
+            for (int i = 0; i < 2 * NT / RG; ++i) {
+                const int c = tid + i * THREADS;
                 const int row = c >> 5, col = c & 31;
                 const int k = i_stage * GS_STAGE_K + col * 8;
                 const __nv_bfloat16* src = A + (int64_t)min(row, M - 1) * lda + min(k, K - 8);
@@ -129,14 +133,15 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
         gs_commit();                   // an empty group keeps the group count in step with the step count
         advance();
         const unsigned char* sp = gs_smem + (q % STAGES) * STAGE_BYTES + warp * (GS_KB * 2) + 32 * t;
-        const uint4 wa0 = *reinterpret_cast<const uint4*>(sp + g * GS_ROW_BYTES);
-        const uint4 wa1 = *reinterpret_cast<const uint4*>(sp + g * GS_ROW_BYTES + 16);
-        const uint4 wb0 = *reinterpret_cast<const uint4*>(sp + (g + 8) * GS_ROW_BYTES);
-        const uint4 wb1 = *reinterpret_cast<const uint4*>(sp + (g + 8) * GS_ROW_BYTES + 16);
+        const unsigned char* wp = sp + rg * 16 * GS_ROW_BYTES;     // this row group's 16 weight rows
+        const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + g * GS_ROW_BYTES);
+        const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + g * GS_ROW_BYTES + 16);
+        const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + (g + 8) * GS_ROW_BYTES);
+        const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + (g + 8) * GS_ROW_BYTES + 16);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4 c0 = *reinterpret_cast<const uint4*>(sp + GS_W_BYTES + (8 * nt + g) * GS_ROW_BYTES);
-            const uint4 c1 = *reinterpret_cast<const uint4*>(sp + GS_W_BYTES + (8 * nt + g) * GS_ROW_BYTES + 16);
+            const uint4 c0 = *reinterpret_cast<const uint4*>(sp + W_BYTES + (8 * nt + g) * GS_ROW_BYTES);
+            const uint4 c1 = *reinterpret_cast<const uint4*>(sp + W_BYTES + (8 * nt + g) * GS_ROW_BYTES + 16);
             gs_mma(acc[nt], wa0.x, wb0.x, wa0.y, wb0.y, c0.x, c0.y);
             gs_mma(acc[nt], wa0.z, wb0.z, wa0.w, wb0.w, c0.z, c0.w);
             gs_mma(acc[nt], wa1.x, wb1.x, wa1.y, wb1.y, c1.x, c1.y);
@@ -144,7 +149,8 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
         }
         if (++c_stage < n_stages) continue;
         // ---- the tile is complete: add the four warps' sums in a fixed order and write ------------------
-        const int n0 = c_tile * 16;
+        const int n0 = c_tile * ROWS + rg * 16;
+        const int tid_g = tid & (GS_WARPS * 32 - 1);     // thread within the row group
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -155,7 +161,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
         __syncthreads();
         if (SWIGLU) {
             // 8 columns x 8*NT tokens; thread i takes (tile nt, slot c in {0,1}) = i / 32 and lane i % 32.
-            for (int i = tid; i < NT * 64; i += GS_WARPS * 32) {
+            for (int i = tid_g; i < NT * 64; i += GS_WARPS * 32) {
                 const int r = i >> 5, l = i & 31;
                 const int nt = r >> 1, c = r & 1;
                 float gate = 0.f, up = 0.f;
@@ -164,14 +170,14 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
                     gate += red[w][nt * 4 + c][l];
                     up += red[w][nt * 4 + c + 2][l];
                 }
-                const int col = c_tile * 8 + (l >> 2);
+                const int col = (c_tile * RG + rg) * 8 + (l >> 2);
                 const int tok = 8 * nt + 2 * (l & 3) + c;
                 if (n0 + (l >> 2) + 8 < N && tok < M)
                     C[(int64_t)tok * ldc + col] = from_float<TO>(gate / (1.f + expf(-gate)) * up);
             }
         } else {
             // 16 rows x 8*NT tokens = NT*128 sums; thread i takes register slot i / 32 of lane i % 32.
-            for (int i = tid; i < NT * 128; i += GS_WARPS * 32) {
+            for (int i = tid_g; i < NT * 128; i += GS_WARPS * 32) {
                 const int r = i >> 5, l = i & 31;
                 float s = 0.f;
 #pragma unroll
@@ -189,21 +195,21 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_stream_kernel(TO* __restri
     gs_wait_group<0>();
 }
 
-template <int NT, typename TO, bool SWIGLU, int STAGES>
+template <int NT, typename TO, bool SWIGLU, int STAGES, int RG>
 static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
     static bool attr_set = false;   // once per instantiation (one device per process)
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU, STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gs_smem_bytes(NT, STAGES));
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU, STAGES, RG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gs_smem_bytes(NT, STAGES, RG));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const int n_tiles = (N + 15) / 16;
+    const int n_tiles = (N + 16 * RG - 1) / (16 * RG);
     // One tile per CTA measured faster than two persistent CTAs per SM on every shape of the 8B model
     // (the kernel itself takes any grid size: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...).
     const int grid = n_tiles;
-    return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU, STAGES>, dim3(grid), dim3(GS_WARPS * 32), gs_smem_bytes(NT, STAGES), s, C, ldc,
+    return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU, STAGES, RG>, dim3(grid), dim3(GS_WARPS * 32 * RG), gs_smem_bytes(NT, STAGES, RG), s, C, ldc,
                       A, lda, W, ldw, M, N, K);
 }
 
@@ -224,12 +230,23 @@ template <int NT, typename TO, bool SWIGLU>
 static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
     int stages = gs_env_stages();
+    // Up to 8 tokens: two row groups per CTA where 32-row tiles still give about one CTA per SM or more.
+    // With at least 148 such tiles, four stages of 21 KiB (two CTAs per SM); with 96..147 tiles, six stages
+    // (one CTA per SM, 80 KiB of weight reads in flight each).  IMP_B200_GS_RG=1 keeps 16-row tiles
+    // everywhere, =2 uses 32-row tiles only in the first case.
+    static int rg_env = -1;
+    if (rg_env < 0) { const char* e = getenv("IMP_B200_GS_RG"); rg_env = e ? atoi(e) : 3; }
+    // (With one or two tokens the activations are a small share of the traffic and more, smaller CTAs win.)
+    if (NT == 1 && M >= 3 && rg_env >= 2 && stages == 0 && (N + 31) / 32 >= 148)
+        return launch_stream_st<1, TO, SWIGLU, 4, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= 96 && (N + 31) / 32 < 148)
+        return launch_stream_st<1, TO, SWIGLU, 6, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
     if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * 148) ? 8 : 5;
     switch (stages) {
-        case 4: return launch_stream_st<NT, TO, SWIGLU, 4>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        case 6: return launch_stream_st<NT, TO, SWIGLU, 6>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        case 8: return launch_stream_st<NT, TO, SWIGLU, 8>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        default: return launch_stream_st<NT, TO, SWIGLU, 5>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 4: return launch_stream_st<NT, TO, SWIGLU, 4, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 6: return launch_stream_st<NT, TO, SWIGLU, 6, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 8: return launch_stream_st<NT, TO, SWIGLU, 8, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        default: return launch_stream_st<NT, TO, SWIGLU, 5, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
     }
 }
 
