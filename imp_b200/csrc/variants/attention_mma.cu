@@ -519,9 +519,9 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first16 = first & ~15;
     const int total_steps = (pos - first16) / 16 + 1;
-    const int per_split = (total_steps + n_splits - 1) / n_splits;
-    const int step_lo = split * per_split;
-    const int step_hi = min(total_steps, step_lo + per_split);
+    // balanced ranges: every split gets floor or ceil of total / n_splits steps, none is left empty while others hold two
+    const int step_lo = (int)((int64_t)split * total_steps / n_splits);
+    const int step_hi = (int)((int64_t)(split + 1) * total_steps / n_splits);
 
     RowInfo rows[2];
     const __nv_bfloat16* qrow[2];
@@ -852,9 +852,9 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first_al = first & ~(DT_KEYS - 1);
     const int total_stages = (pos - first_al) / DT_KEYS + 1;
-    const int per_split = (total_stages + n_splits - 1) / n_splits;
-    const int stage_lo = split * per_split;
-    const int stage_hi = min(total_stages, stage_lo + per_split);
+    // balanced ranges: every split gets floor or ceil of total / n_splits stages
+    const int stage_lo = (int)((int64_t)split * total_stages / n_splits);
+    const int stage_hi = (int)((int64_t)(split + 1) * total_stages / n_splits);
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dt_smem);
     const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(dt_bars), empty0 = full0 + 8 * DT_STAGES;
     if (tid == 0) {
