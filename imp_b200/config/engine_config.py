@@ -4,7 +4,7 @@
 `compute_dtype`, `prefill_chunk_size`, `enable_cuda_graphs` come from
 include/imp/config.h:11-81 (defaults: src/api/imp_api.cpp:35-72);
 `kv_block_size` from src/runtime/engine.h:59.  `max_batch_tokens` (the token
-budget of one step) and `max_live_requests` are this engine's own.
+budget of one step) and `lookahead` are this engine's own.
 """
 from __future__ import annotations
 
@@ -25,6 +25,7 @@ class EngineConfig:
     enable_cuda_graphs: bool = True   # capture decode-only steps
     gpu_memory_fraction: float = 0.8  # of free memory to the cache when nothing else sizes it
     state_slots: int = 0              # fixed-size state slots; 0 = max_batch_size
+    lookahead: bool = True            # launch the next decode step before reading the last one's tokens
 
     def validate(self) -> None:
         if self.compute_dtype not in ("bfloat16", "float32"):

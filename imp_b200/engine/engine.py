@@ -23,7 +23,7 @@ from ..config.model_config import ModelConfig
 from ..sampling.sampler import Sampler, SamplingParams
 from .loading import load_model, make_cache, random_model
 from .model import DecoderModel
-from .scheduler import Request, RequestStatus, Scheduler, StepPlan
+from .scheduler import Request, RequestStatus, ScheduledEntry, Scheduler, StepPlan
 from .step import StepEntry, Stepper
 
 
@@ -70,6 +70,19 @@ class StepOutput:
     status: RequestStatus
 
 
+@dataclass
+class _InFlight:
+    """A step that has been queued on the device and whose tokens have not been read yet."""
+
+    plan: StepPlan
+    rows: List[Request]              # the requests that get a token, in the order of the sampled tokens
+    tokens_dev: Optional[torch.Tensor]   # int32 [len(rows)] on the device
+    tokens_host: Optional[torch.Tensor]  # pinned copy of the same, valid once `event` has passed
+    status_host: torch.Tensor            # pinned copy of the device status word
+    event: torch.cuda.Event
+    early: List[StepOutput]          # outputs known at launch (requests the scheduler gave up on)
+
+
 class Engine:
     """Model + cache + step function + scheduler + sampler on one GPU."""
 
@@ -92,6 +105,11 @@ class Engine:
         self.scheduler = Scheduler(self.cache, cfg.max_batch_size, cfg.max_batch_tokens, cfg.prefill_chunk_size,
                                    self.max_seq_len)
         self.sampler = Sampler(model.vocab_size, cfg.max_batch_size, rt.device)
+        self._inflight: Optional[_InFlight] = None
+        # two pinned landing places for (tokens, status): a step in flight and the one launched ahead of it
+        self._landing = [(torch.zeros(cfg.max_batch_size, dtype=torch.int32).pin_memory(),
+                          torch.zeros(1, dtype=torch.int32).pin_memory()) for _ in range(2)]
+        self._landing_turn = 0
         self._ids = itertools.count()
         eos = model_config.eos_token_id
         self.eos_token_ids: Tuple[int, ...] = () if eos is None else (int(eos),)
@@ -143,33 +161,99 @@ class Engine:
         return self.scheduler.add(req)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
-    def step(self) -> List[StepOutput]:
-        """One engine step: schedule, run the batch, sample, finish.  Returns the new tokens."""
-        plan = self.scheduler.schedule()
-        outs = [StepOutput(r.rid, -1, True, r.status) for r in plan.failed]
-        if not plan.entries:
-            return outs
+    # ------------------------------------------------------------------- steps
+    def _launch(self, plan: StepPlan, device_tokens: Optional[torch.Tensor] = None,
+                early: Optional[List[StepOutput]] = None) -> _InFlight:
+        """Queue the plan's batch, its sampling and the copy of the results to pinned memory."""
         entries, rows = [], []
         for e in plan.entries:
-            toks = e.request.tokens_slice(e.start, e.n_tokens)
+            toks = [0] * e.n_tokens if device_tokens is not None else e.request.tokens_slice(e.start, e.n_tokens)
             entries.append(StepEntry(e.request.rid, toks, [e.n_tokens - 1] if e.samples else []))
             if e.samples:
                 rows.append(e.request)
-        logits = self.stepper.step(entries)
-        sampled: Dict[Hashable, int] = {}
+        logits = self.stepper.step(entries, device_tokens)
+        tokens_dev = tokens_host = None
+        land_tokens, land_status = self._landing[self._landing_turn]
+        self._landing_turn ^= 1
         if rows:
-            toks = self.sampler.sample(logits, [r.params for r in rows], [r.seed for r in rows],
-                                       [len(r.output) for r in rows], [r.all_tokens() for r in rows]
-                                       if any(r.params.needs_history() for r in rows) else None,
-                                       [r.sampler_state for r in rows])
-            sampled = {r.rid: t for r, t in zip(rows, toks)}
-        self.stepper.check_device_status()
-        finished = set(id(r) for r in self.scheduler.complete_step(plan, sampled))
-        for r in rows:
+            # a token launched ahead of the last one's arrival counts as one more output
+            ahead = 1 if device_tokens is not None else 0
+            tokens_dev = self.sampler.sample_device(
+                logits, [r.params for r in rows], [r.seed for r in rows], [len(r.output) + ahead for r in rows],
+                [r.all_tokens() for r in rows] if any(r.params.needs_history() for r in rows) else None,
+                [r.sampler_state for r in rows])
+            tokens_host = land_tokens[:len(rows)]
+            tokens_host.copy_(tokens_dev, non_blocking=True)
+        land_status.copy_(self.stepper.rt.status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return _InFlight(plan, rows, tokens_dev, tokens_host, land_status, ev, early or [])
+
+    def _finish(self, fl: _InFlight) -> List[StepOutput]:
+        """Wait for a queued step, hand its tokens to the scheduler, and report them."""
+        fl.event.synchronize()
+        code = int(fl.status_host[0])
+        if code != 0:
+            self.stepper.check_device_status()      # raises with the device's message and clears the word
+        outs = list(fl.early)
+        live = [r for r in fl.rows if not r.done]   # a request may have finished while this step was under way
+        toks = fl.tokens_host.tolist() if fl.rows else []
+        sampled = {r.rid: t for r, t in zip(fl.rows, toks)}
+        finished = set(id(r) for r in self.scheduler.complete_step(fl.plan, sampled))
+        for r in live:
             outs.append(StepOutput(r.rid, sampled[r.rid], id(r) in finished, r.status))
         return outs
+
+    def _plan_ahead(self, fl: _InFlight) -> Optional[StepPlan]:
+        """The step after `fl` if it can be decided before `fl`'s tokens are known: every running request
+        gets a token from `fl`, none of them ends with it for a reason known in advance (length, context),
+        none needs its token on the host to sample the next one, nothing waits for admission, and the pages
+        are there.  A request that ends on its end-of-sequence token takes part in one step too many; its
+        result is dropped."""
+        sch = self.scheduler
+        if not self.config.lookahead or not fl.rows or sch.waiting or len(fl.rows) != len(sch.running):
+            return None
+        if len(fl.plan.entries) != len(fl.rows) or fl.plan.preempted or fl.plan.failed:
+            return None
+        entries = []
+        for e in fl.plan.entries:
+            r = e.request
+            if r.done or r.params.needs_history() or r.params.mirostat:
+                return None
+            start = e.start + e.n_tokens
+            if len(r.output) + 1 >= r.max_tokens or start + 1 >= self.max_seq_len:
+                return None
+            entries.append(ScheduledEntry(r, start, 1, True))
+        probe = [StepEntry(e.request.rid, [0], [0]) for e in entries]
+        if self.stepper.pages_short(probe) > 0:
+            return None
+        return StepPlan(entries=entries)
+
+    def step(self) -> List[StepOutput]:
+        """One engine step: schedule, run the batch, sample, finish.  Returns the new tokens.
+
+        With `lookahead` the step after this one is queued on the device before this one's tokens are
+        read (its token ids stay on the device), when `_plan_ahead` allows it; the host's work then
+        overlaps the device's.  Every call still returns the tokens of exactly one step."""
+        fl = self._inflight
+        self._inflight = None
+        if fl is None:
+            plan = self.scheduler.schedule()
+            early = [StepOutput(r.rid, -1, True, r.status) for r in plan.failed]
+            if not plan.entries:
+                return early
+            fl = self._launch(plan, early=early)
+        ahead = self._plan_ahead(fl)
+        if ahead is not None:
+            self._inflight = self._launch(ahead, device_tokens=fl.tokens_dev)
+        return self._finish(fl)
+
+    def drain(self) -> List[StepOutput]:
+        """Finish a step that was launched ahead, if any (its requests may all have ended already)."""
+        fl, self._inflight = self._inflight, None
+        return self._finish(fl) if fl is not None else []
 
     def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
         """Generate for every prompt (continuous batching inside); returns the new tokens per prompt.
@@ -186,6 +270,8 @@ class Engine:
                                   f"pool of {self.cache.num_pages} holds")
         while any(not r.done for r in reqs):
             self.step()
+        if not self.scheduler.has_work():
+            self.drain()
         failed = [r for r in reqs if r.status != RequestStatus.FINISHED]
         if failed:
             raise MemoryError(f"{len(failed)} request(s) ran out of cache pages: "

@@ -285,6 +285,8 @@ class Scheduler:
         finished = []
         for e in plan.entries:
             req = e.request
+            if req.done:
+                continue    # finished or cancelled while this step was already under way
             req.n_computed = e.start + e.n_tokens
             if not e.samples:
                 continue

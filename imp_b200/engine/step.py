@@ -256,10 +256,18 @@ class Stepper:
         for rid, start, n in zip(ctx.rids, ctx.starts, ctx.q_lens):
             self.cache.commit(rid, start + n)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch.  Returns float32 logits [wanted rows, vocab] on the device, in the
-        order of the entries and of each entry's `want`."""
+        order of the entries and of each entry's `want`.
+
+        `device_tokens` (int32, one per token of the batch, on the device) replaces the entries'
+        token ids: the ids of a step whose tokens were sampled on the device and have not come
+        back to the host yet.  The entries then carry placeholders."""
         ctx = self.prepare(entries)
+        if device_tokens is not None:
+            if device_tokens.numel() != ctx.n_tokens or device_tokens.dtype != torch.int32:
+                raise ValueError("device_tokens must hold one int32 id per token of the batch")
+            ctx.token_ids.copy_(device_tokens)
         if self.use_cuda_graphs and ctx.decode_only and ctx.n_rows == ctx.n_seqs:
             logits = self._forward_decode_graph(ctx)
         else:

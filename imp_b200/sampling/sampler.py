@@ -150,9 +150,18 @@ class Sampler:
         tokens so far (prompt and output), used by the penalties and DRY; `states[r]` carries
         Mirostat's mu between calls (needed only for rows that use Mirostat).
         """
+        if logits.shape[0] == 0:
+            return []
+        return self.sample_device(logits, params, seeds, steps, histories, states).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                      steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None,
+                      states: Optional[Sequence[SamplerState]] = None) -> torch.Tensor:
+        """`sample` with the token ids left on the device (int32 [R]).  Without Mirostat rows nothing
+        here waits for the device, so the caller can queue more work before it reads the tokens."""
         R = logits.shape[0]
         if R == 0:
-            return []
+            return torch.empty(0, dtype=torch.int32, device=self.device)
         assert len(params) == R and len(seeds) == R and len(steps) == R
         histories = histories or [[] for _ in range(R)]
         if any(p.has_penalties() for p in params):
@@ -164,7 +173,7 @@ class Sampler:
                                [p.min_p for p in params]], dtype=torch.float32, device=self.device)
             K.typical_filter(logits, tp[0], tp[1])
         if all(p.is_greedy() for p in params):
-            return K.argmax(logits).tolist()
+            return K.argmax(logits)
         f = np.empty((5, R), dtype=np.float32)
         k = np.empty((2, R), dtype=np.int32)
         miro = [r for r, p in enumerate(params) if p.mirostat == 2]
@@ -191,11 +200,11 @@ class Sampler:
             temp = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=self.device)
             surprise = torch.zeros(R, dtype=torch.float32, device=self.device)
             K.sample_mirostat(logits, kd[1], temp, fd[4], fd[3], out, surprise)
-            sur = surprise.tolist()
+            sur = surprise.tolist()          # waits for the device: mu is host state
             for r in miro:
                 p = params[r]
                 states[r].mirostat_mu -= p.mirostat_eta * (sur[r] - p.mirostat_tau)
-        return out.tolist()
+        return out
 
     def _dry(self, logits, params, histories) -> None:
         rows: List[int] = []

@@ -156,3 +156,71 @@ def test_entry_point_refuses_bad_input(model_folders):
     with pytest.raises(TypeError):
         eng.generate([1, 2, 3], GenerateParams(max_tokens=2))
     assert eng.cache.free_pages() == eng.cache.num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_changes_nothing(dtype, model_folders):
+    """With `lookahead` the engine queues the next decode step before it has read the last one's tokens.
+    Tokens, finish reasons and the cache's bookkeeping must be what they are without it: greedy and
+    sampled requests, different lengths, an end-of-sequence token in the middle, a late arrival."""
+    from imp_b200 import GenerateParams
+    from imp_b200.engine.scheduler import FinishReason
+    folder, cd, page = model_folders["B"]
+    V = cd["vocab_size"]
+    prompts = prompts_for(V, [3, 20, 9, 14], seed=21)
+    params = [GenerateParams(max_tokens=25, temperature=0.0), GenerateParams(max_tokens=40, temperature=0.9, seed=5),
+              GenerateParams(max_tokens=7, temperature=0.0), GenerateParams(max_tokens=33, temperature=0.7, top_k=20, seed=8)]
+    runs = {}
+    for la in (False, True):
+        eng = engine(folder, dtype, page, lookahead=la)
+        # make the greedy continuation of the first prompt end early: its 6th token becomes the end-of-sequence id
+        probe = engine(folder, dtype, page, lookahead=False).generate([prompts[0]], params[0])[0]
+        eng.eos_token_ids = (probe[5],)
+        reqs = [eng.submit(p, q) for p, q in zip(prompts[:3], params[:3])]
+        n_calls = 0
+        while any(not r.done for r in reqs):
+            outs = eng.step()
+            n_calls += 1
+            if n_calls == 6:                      # a request arrives while the others decode
+                reqs.append(eng.submit(prompts[3], params[3]))
+            for o in outs:
+                assert o.token >= 0 or o.finished
+        eng.drain()
+        assert not eng.has_work() and eng.cache.free_pages() == eng.cache.num_pages
+        eng.cache.check_invariants()
+        runs[la] = [(list(r.output), r.finish_reason) for r in reqs]
+    if dtype == "float32":
+        assert runs[True] == runs[False]
+    else:
+        # bfloat16 results depend on the batch's size through rounding (another kernel, another order of
+        # additions), and a request that ends on its end-of-sequence token rides along for one step more
+        # with the step ahead: a sampled token may then differ.  What must agree is what was decided.
+        assert [(len(o), why) for o, why in runs[True]] == [(len(o), why) for o, why in runs[False]]
+        assert [o[:3] for o, _ in runs[True]] == [o[:3] for o, _ in runs[False]]
+    first = runs[True][0]
+    assert first[1] == FinishReason.EOS and len(first[0]) <= 6
+    assert runs[True][2][1] == FinishReason.LENGTH and len(runs[True][2][0]) == 7
+
+
+def test_lookahead_overlaps_only_when_it_may(model_folders):
+    """The step ahead is launched for plain decoding only: not while a prompt is still being read in
+    portions, not for requests whose sampling needs their tokens on the host, not into a token that ends
+    a request by its length."""
+    from imp_b200 import GenerateParams
+    folder, cd, page = model_folders["A"]
+    eng = engine(folder, "bfloat16", page, prefill_chunk_size=8)
+    r = eng.submit(prompts_for(cd["vocab_size"], [20])[0], GenerateParams(max_tokens=4, temperature=0.0))
+    eng.step()
+    assert eng._inflight is None                  # first portion of the prompt: nothing sampled yet
+    eng.step(); eng.step()
+    assert len(r.output) == 1 and eng._inflight is not None      # decoding: one step is under way
+    eng.step()
+    assert len(r.output) == 2 and eng._inflight is not None
+    eng.step()
+    assert len(r.output) == 3 and eng._inflight is not None      # the step under way brings the fourth, last token
+    eng.step()
+    assert r.done and len(r.output) == 4 and eng._inflight is None and not eng.has_work()   # nothing was launched beyond it
+    pen = eng.submit([1, 2, 3], GenerateParams(max_tokens=5, temperature=0.0, repetition_penalty=1.3))
+    while not pen.done:
+        eng.step()
+        assert eng._inflight is None              # the penalty reads the tokens on the host
