@@ -316,6 +316,193 @@ __global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(cons
     }
 }
 
+// ------------------------------------------------------------ pairs of CTAs (cta_group::2)
+// Two CTAs of a cluster, on neighbouring SMs, compute one 256 x 256 tile together.  Each of them loads
+// its own 128 rows of A and its own half (128 rows) of the W tile, so a k-block costs an SM 32 KiB of
+// shared-memory fill instead of 48; the MMA (M = 256, N = 256, issued by the even CTA for both) reads
+// W from both CTAs' shared memory, and each CTA's tensor memory receives the accumulator of its own 128
+// rows.  Protocol, per stage s of the six-deep ring (barriers live at the same offsets in both CTAs):
+//   full[s]   in the even CTA only: its producer announces the bytes of both CTAs' copies, all four TMA
+//             loads (cta_group::2) complete on it;
+//   empty[s]  in both: the MMA's commit arrives on both at once (multicast), each producer waits its own;
+//   accumulator full: the commit after a tile's last MMA, again on both; accumulator empty: in the even
+//   CTA, eight arrivals (four epilogue warps of each CTA, the odd CTA's through the cluster's shared
+//   window).
+// Both CTAs pass a cluster barrier after initialising their barriers and before they leave.
+constexpr int TC2_STAGES = 6;
+constexpr int TC2_HALF_BYTES = 128 * TC_BK * 2;                 // 16 KiB: 128 rows of A, or of W
+constexpr int TC2_STAGE_BYTES = 2 * TC2_HALF_BYTES;
+constexpr int TC2_SMEM_BYTES = TC2_STAGES * TC2_STAGE_BYTES + 1024 + 256;
+constexpr int TC2_BM = 256, TC2_BN = 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of `addr` (an address in this CTA's shared memory) in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: the copy lands in this CTA's shared memory, its bytes count on `bar`,
+// which may be the partner's barrier (an address in the cluster's shared window).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The barrier at this offset in both CTAs of the pair gets an arrival when the MMAs issued so far are done.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
+    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                        void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * TC2_STAGE_BYTES);
+    // bars: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC2_STAGES + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    const int num_m = (M + TC2_BM - 1) / TC2_BM, num_n = (N + TC2_BN - 1) / TC2_BN;
+    const int total = num_m * num_n;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC2_STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * TC2_STAGES), acce0 = smem_u32(bars + 2 * TC2_STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC2_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 8);     // four epilogue warps of each CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs, the same slot offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)TCP_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();        // the partner's barriers are initialised before anything can arrive on them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------ producer (one per CTA, for its own halves)
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += n_pairs) {
+                const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC2_STAGES;
+                    ok = mbar_wait(empty0 + 8 * s, ((it / TC2_STAGES) & 1u) ^ 1u, status);
+                    if (!ok) break;
+                    const uint32_t a_dst = smem_u32(tiles + s * TC2_STAGE_BYTES), b_dst = a_dst + TC2_HALF_BYTES;
+                    const uint32_t full_even = cluster_map(full0 + 8 * s, 0);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * TC2_STAGE_BYTES);   // both CTAs' copies
+                    tma_load_2d_pair(a_dst, &map_a, kb * TC_BK, m0, full_even);
+                    tma_load_2d_pair(b_dst, &map_w, kb * TC_BK, n0, full_even);
+                }
+            }
+            if (!ok && rank == 0) {   // a bounded chance for the copies still in flight to land
+                for (uint32_t j = it > TC2_STAGES ? it - TC2_STAGES : 0; j < it; ++j)
+                    mbar_wait(full0 + 8 * (j % TC2_STAGES), (j / TC2_STAGES) & 1u, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------ MMA issuer (even CTA)
+            const uint32_t idesc = tc_instr_desc(TC2_BM, TC2_BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += n_pairs, ++local) {
+                const uint32_t buf = local & 1u;
+                ok = mbar_wait(acce0 + 8 * buf, ((local >> 1) & 1u) ^ 1u, status);   // both epilogues have drained it
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * TC2_BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC2_STAGES;
+                    ok = mbar_wait(full0 + 8 * s, (it / TC2_STAGES) & 1u, status);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + s * TC2_STAGE_BYTES), b_addr = a_addr + TC2_HALF_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                        tc_mma_pair(d_tmem, tc_smem_desc(a_addr + k * TC_UMMA_K * 2), tc_smem_desc(b_addr + k * TC_UMMA_K * 2),
+                                    idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty0 + 8 * s);
+                }
+                if (ok) tc_commit_pair(accf0 + 8 * buf);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int quarter = warp & 3;
+        const uint32_t acce_even0 = cluster_map(acce0, 0);
+        uint32_t local = 0;
+        for (int t = pair; t < total; t += n_pairs, ++local) {
+            const uint32_t buf = local & 1u;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN;
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
+#pragma unroll 1
+            for (int c = 0; c < TC2_BN / 32; ++c) {
+                float v[32];
+                tc_ld32(taddr + (uint32_t)(c * 32), v);
+                tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acce_even0 + 8 * buf);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();        // neither CTA leaves while the other may still read its memory or signal its barriers
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TCP_TMEM_COLS)
+                     : "memory");
+    }
+}
+
 // ------------------------------------------------------- few rows: weights on the M side
 // For 16 < M <= 128 activation rows the product is turned round, as in the decode kernel of
 // gemm_stream.cu: 128 weight rows are the M side of the MMA (one accumulator lane per weight row),
@@ -515,8 +702,8 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t
 }
 
 template <int EPI>
-static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, int* status,
-                     cudaStream_t s) {
+static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw128, int M,
+                     int N, int K, int* status, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
@@ -531,6 +718,22 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
             sms = 148;
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); mode = -1; return (int)e; }
+    }
+    // IMP_B200_TC_PAIR=0 keeps single CTAs; by default products of 256 rows and more run on CTA pairs.
+    static int pair_mode = -1;
+    if (pair_mode < 0) {
+        const char* e = getenv("IMP_B200_TC_PAIR");
+        pair_mode = e ? atoi(e) : 1;
+        if (pair_mode) {
+            cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM_BYTES);
+            if (e2 != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e2)); pair_mode = -1; return (int)e2; }
+        }
+    }
+    if (mode == 0 && pair_mode == 1 && M >= 256) {
+        const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
+        const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+        gemm_tc_pair_kernel<EPI><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, s>>>(ma, mw128, C, ldc, M, N, K, status);
+        IMP_RETURN_LAUNCH();
     }
     const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
     if (mode == 1) {
@@ -558,9 +761,11 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
     if (int rc = make_map(&ma, A, M, K, lda, TC_BM)) return rc;
     if (int rc = make_map(&mw, W, N, K, ldw, TC_BN)) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (epilogue == TC_OUT_BF16) return launch_tc<TC_OUT_BF16>(C, ldc, ma, mw, M, N, K, status, s);
-    if (epilogue == TC_OUT_F32) return launch_tc<TC_OUT_F32>(C, ldc, ma, mw, M, N, K, status, s);
-    return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, M, N, K, status, s);
+    CUtensorMap mw128;   // the W tile in halves of 128 rows, for CTA pairs
+    if (int rc = make_map(&mw128, W, N, K, ldw, 128)) return rc;
+    if (epilogue == TC_OUT_BF16) return launch_tc<TC_OUT_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
+    if (epilogue == TC_OUT_F32) return launch_tc<TC_OUT_F32>(C, ldc, ma, mw, mw128, M, N, K, status, s);
+    return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
 }
 
 // ---- few rows (16 < M <= 128) -----------------------------------------------------------------------
