@@ -1,0 +1,111 @@
+"""The engine at the layer widths of the benchmark model (hidden 4096, 32 query / 8 kv heads of 128,
+inner 12288), two layers and a reduced, odd vocabulary, against the plain implementation: the shapes
+at which the tensor-memory GEMMs (single CTAs, CTA pairs, swap-AB), the weight-streaming GEMM with
+32-row tiles and the tensor-memory attention run in the benchmark, here checked for their numbers.
+"""
+import numpy as np
+import pytest
+import torch
+
+from plain.qwen3_plain import PlainModel
+
+pytestmark = pytest.mark.gpu
+
+WIDE = {
+    "architectures": ["Qwen3ForCausalLM"], "vocab_size": 32003, "hidden_size": 4096, "num_hidden_layers": 2,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+    "max_position_embeddings": 1024,
+}
+
+
+@pytest.fixture(scope="module")
+def wide(tmp_path_factory):
+    from imp_b200.config.registry import config_from_dict
+    from imp_b200.weights.random_init import write_model_folder
+    folder = str(tmp_path_factory.mktemp("wide"))
+    write_model_folder(folder, config_from_dict(WIDE), seed=3, std=0.02)
+    g = torch.Generator().manual_seed(8)
+    ids = {name: torch.randint(0, WIDE["vocab_size"], (n,), generator=g).tolist()
+           for name, n in (("a", 300), ("b", 140), ("c", 33))}
+    plain = PlainModel(folder)
+    ref = {name: plain.logits(v) for name, v in ids.items()}
+    return folder, ids, ref
+
+
+def run(eng, ids, plan):
+    """plan: list of steps, each a list of (request, n tokens); returns {request: logits of all its rows}."""
+    from imp_b200 import StepEntry
+    done = {k: 0 for k in ids}
+    rows = {k: [] for k in ids}
+    for step in plan:
+        entries = [StepEntry(r, ids[r][done[r]:done[r] + n], list(range(n))) for r, n in step]
+        lg = eng.step_tokens(entries)
+        at = 0
+        for r, n in step:
+            rows[r].append(lg[at:at + n])
+            at += n
+            done[r] += n
+    for r in ids:
+        if done[r]:
+            assert done[r] == len(ids[r])
+            eng.end(r)
+    return {r: torch.cat(v) for r, v in rows.items() if v}
+
+
+def engine(folder, dtype):
+    from imp_b200 import Engine, EngineConfig
+    return Engine.from_folder(folder, EngineConfig(compute_dtype=dtype, kv_block_size=16, max_batch_size=24, max_seq_len=512,
+                                                   kv_cache_tokens=24 * 512, max_batch_tokens=640))
+
+
+def test_bfloat16_at_real_widths(wide):
+    folder, ids, ref = wide
+    eng = engine(folder, "bfloat16")
+
+    def check(got, what):
+        for r, lg in got.items():
+            want = ref[r]
+            scale = float(want.abs().max())
+            err = (lg - want).abs()
+            assert (err <= 0.03 * scale + 0.03 * want.abs()).all(), f"{what}, request {r}: max error {float(err.max()):.3g} of {scale:.3g}"
+            # the most likely token agrees wherever it is clearly ahead
+            top2 = torch.topk(want, 2, dim=-1).values
+            clear = (top2[:, 0] - top2[:, 1]) > 0.1 * scale
+            assert (lg.argmax(-1)[clear] == want.argmax(-1)[clear]).all(), f"{what}, request {r}: argmax differs"
+
+    # whole prompts: 300 rows on CTA pairs, 140 on single CTAs, 33 on the swap-AB kernel; attention in 128-token tiles
+    check(run(eng, ids, [[("a", 300)], [("b", 140)], [("c", 33)]]), "whole")
+    # portions beside decode tokens: 130 + 100 + the rest of a; b and c token by token for a while, then in portions
+    plan = [[("a", 130), ("b", 1), ("c", 1)], [("a", 100), ("b", 1), ("c", 1)], [("b", 70), ("c", 31), ("a", 1)]]
+    plan += [[("a", 1), ("b", 1)] for _ in range(20)]
+    plan += [[("a", 49), ("b", 48)]]
+    check(run(eng, ids, plan), "portions and decode")
+    # twenty sequences decoding together (the swap-AB kernel's shape in decode): twenty copies of c, last 3 tokens
+    many = {f"c{i}": ids["c"] for i in range(20)}
+    from imp_b200 import StepEntry
+    eng.step_tokens([StepEntry(r, v[:30], []) for r, v in list(many.items())[:10]])
+    eng.step_tokens([StepEntry(r, v[:30], []) for r, v in list(many.items())[10:]])
+    for t in range(30, 33):
+        lg = eng.step_tokens([StepEntry(r, [v[t]], [0]) for r, v in many.items()])
+        want = ref["c"][t]
+        scale = float(want.abs().max())
+        assert ((lg - want[None]).abs() <= 0.03 * scale + 0.03 * want.abs()[None]).all(), f"20-way decode at position {t}"
+        assert (lg - lg[0:1]).abs().max() <= 0.02 * scale        # the same sequence twenty times: the same logits
+    for r in many:
+        eng.end(r)
+    eng.cache.check_invariants()
+    assert eng.cache.free_pages() == eng.cache.num_pages
+
+
+def test_float32_at_real_widths_is_exact_under_cutting(wide):
+    folder, ids, ref = wide
+    eng = engine(folder, "float32")
+    small = {"b": ids["b"], "c": ids["c"]}
+    whole = run(eng, small, [[("b", 140)], [("c", 33)]])
+    for r, lg in whole.items():
+        err = (lg - ref[r]).abs()
+        assert (err <= 2e-3 + 2e-3 * ref[r].abs()).all(), f"request {r}: max error {float(err.max()):.3g}"
+    cut = run(eng, small, [[("b", 70), ("c", 2)], [("b", 69), ("c", 30)], [("b", 1), ("c", 1)]])
+    for r in small:
+        assert np.array_equal(whole[r].numpy(), cut[r].numpy()), f"request {r}: logits depend on the cut"
