@@ -32,7 +32,7 @@ constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int TC_TMEM_COLS = 256;
 
-enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU_BF16 = 2 };
+enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU_BF16 = 2, TC_OUT_QKV_ROPE = 3 };
 
 // Store 32 consecutive accumulator columns of one row (converted as the epilogue asks).
 template <int EPI>
@@ -316,6 +316,131 @@ __global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(cons
     }
 }
 
+// ------------------------------------------------ epilogue of the fused q,k,v projection
+// With TC_OUT_QKV_ROPE the product's columns are the heads of q, then k, then v (head size 64 or 128, so
+// a 256-column tile holds whole heads) and nothing is written as a [M, N] matrix: a thread, which owns a
+// token's row of the accumulator, normalises each q and k head (RMSNorm over the head with one weight
+// vector for q and one for k, 32-bit), rotates it by the token's position (pairs (i, i + Dh/2), cos / sin
+// from a table) and writes q to its own buffer and k to the token's slot of the cache pages; v heads go
+// to the pages as they are.  The values never round to bfloat16 in between.  Same math as
+// qk_norm_rope_kv_kernel (rope_kv.cu), which runs after an unfused product.
+struct QkvRopeArgs {
+    const int* positions;        // [M]
+    const int* seq_of_token;     // [M]
+    const int* block_table;      // [n_seqs, bt_stride]
+    const float* cos_tab;        // [max_pos, Dh / 2]
+    const float* sin_tab;
+    const float* q_norm_w;       // [Dh] or null (no norm)
+    const float* k_norm_w;
+    __nv_bfloat16* q_out;        // [M, q_stride], head h at column h * Dh
+    __nv_bfloat16* k_cache;      // [num_pages, Hkv, page_size, Dh]
+    __nv_bfloat16* v_cache;
+    int64_t q_stride;
+    float eps;
+    int bt_stride, n_seqs, max_pos, Hq, Hkv, Dh, page_size, num_pages;
+};
+
+__device__ __forceinline__ void store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 o;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+        o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+        o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+        reinterpret_cast<uint4*>(dst)[i] = o;
+    }
+}
+
+// One accumulator row (token `row`, tensor-memory address `taddr` of its first column) of the tile that
+// starts at column n0.  All 32 lanes of the warp call it together (the tensor-memory loads are collective);
+// `live` says whether this lane's row exists.
+__device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t taddr, int row, int n0, int N, bool live,
+                                             int* status) {
+    const int Dh = a.Dh, half = Dh >> 1, chunks = Dh >> 5;          // 32-column chunks per head: 2 or 4
+    int pos = 0;
+    int64_t page_row = -1;
+    if (live) {
+        pos = a.positions[row];
+        const int seq = a.seq_of_token[row];
+        if (seq < 0 || seq >= a.n_seqs) {
+            imp_report(status, IMP_BAD_SEQUENCE);
+            live = false;
+        } else if (pos < 0 || pos >= a.max_pos || pos / a.page_size >= a.bt_stride) {
+            imp_report(status, IMP_BAD_POSITION);
+            live = false;
+        } else {
+            const int slot_page = pos / a.page_size;
+            const int page = a.block_table[(int64_t)seq * a.bt_stride + slot_page];
+            if (page < 0 || page >= a.num_pages) imp_report(status, IMP_BAD_PAGE);
+            else page_row = (int64_t)page * a.Hkv * a.page_size + (pos - slot_page * a.page_size);
+        }
+    }
+    const float* cs = a.cos_tab + (int64_t)pos * half;
+    const float* sn = a.sin_tab + (int64_t)pos * half;
+    for (int h0 = 0; h0 < 256; h0 += Dh) {
+        const int col0 = n0 + h0;
+        if (col0 >= N) break;                                       // uniform over the warp
+        const int hh = col0 / Dh;
+        const uint32_t thead = taddr + (uint32_t)h0;
+        if (hh >= a.Hq + a.Hkv) {
+            // ---- v: to the pages as it is
+            __nv_bfloat16* dst = (live && page_row >= 0) ? a.v_cache + (page_row + (int64_t)(hh - a.Hq - a.Hkv) * a.page_size) * Dh
+                                                         : nullptr;
+            for (int c = 0; c < chunks; ++c) {
+                float v[32];
+                tc_ld32(thead + (uint32_t)(c * 32), v);
+                if (dst) store32_bf16(dst + c * 32, v);
+            }
+            continue;
+        }
+        const bool is_q = hh < a.Hq;
+        const float* nw = is_q ? a.q_norm_w : a.k_norm_w;
+        float inv = 1.f;
+        if (nw) {
+            float ss = 0.f;
+            for (int c = 0; c < chunks; ++c) {
+                float v[32];
+                tc_ld32(thead + (uint32_t)(c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ss = fmaf(v[i], v[i], ss);
+            }
+            inv = rsqrtf(ss / (float)Dh + a.eps);
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (live) {
+            if (is_q) dst = a.q_out + (int64_t)row * a.q_stride + (int64_t)hh * Dh;
+            else if (page_row >= 0) dst = a.k_cache + (page_row + (int64_t)(hh - a.Hq) * a.page_size) * Dh;
+        }
+        for (int c = 0; c < chunks / 2; ++c) {                      // dims [32c, 32c+32) pair with [half + 32c, ...)
+            float x[32], y[32];
+            tc_ld32(thead + (uint32_t)(c * 32), x);
+            tc_ld32(thead + (uint32_t)(half + c * 32), y);
+            if (dst == nullptr) continue;
+            // the table row of this token is read 16 bytes at a time: 32 rows touch 32 sectors per load either
+            // way, so fewer, wider loads keep the L1 out of the way
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+                const float4 co4 = *reinterpret_cast<const float4*>(cs + c * 32 + 4 * i4);
+                const float4 si4 = *reinterpret_cast<const float4*>(sn + c * 32 + 4 * i4);
+                const float co[4] = {co4.x, co4.y, co4.z, co4.w}, si[4] = {si4.x, si4.y, si4.z, si4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = 4 * i4 + j, d = c * 32 + i;
+                    float xa = x[i] * inv, yb = y[i] * inv;
+                    if (nw) { xa *= nw[d]; yb *= nw[d + half]; }
+                    x[i] = xa * co[j] - yb * si[j];
+                    y[i] = xa * si[j] + yb * co[j];
+                }
+            }
+            store32_bf16(dst + c * 32, x);
+            store32_bf16(dst + half + c * 32, y);
+        }
+    }
+}
+
 // ------------------------------------------------------------ pairs of CTAs (cta_group::2)
 // Two CTAs of a cluster, on neighbouring SMs, compute one 256 x 256 tile together.  Each of them loads
 // its own 128 rows of A and its own half (128 rows) of the W tile, so a k-block costs an SM 32 KiB of
@@ -379,7 +504,8 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status) {
+                        void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status,
+                        const __grid_constant__ QkvRopeArgs qkv) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ unsigned char tc_smem_raw[];
@@ -482,11 +608,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN;
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
+            if (EPI == TC_OUT_QKV_ROPE) {
+                qkv_rope_row(qkv, taddr, row, n0, N, row < M, status);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < TC2_BN / 32; ++c) {
-                float v[32];
-                tc_ld32(taddr + (uint32_t)(c * 32), v);
-                tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+                for (int c = 0; c < TC2_BN / 32; ++c) {
+                    float v[32];
+                    tc_ld32(taddr + (uint32_t)(c * 32), v);
+                    tc_store32<EPI == TC_OUT_QKV_ROPE ? TC_OUT_BF16 : EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -732,7 +862,7 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
     if (mode == 0 && pair_mode == 1 && M >= 256) {
         const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
         const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
-        gemm_tc_pair_kernel<EPI><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, s>>>(ma, mw128, C, ldc, M, N, K, status);
+        gemm_tc_pair_kernel<EPI><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, s>>>(ma, mw128, C, ldc, M, N, K, status, QkvRopeArgs{});
         IMP_RETURN_LAUNCH();
     }
     const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
@@ -854,5 +984,56 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
                       : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
     }
     if (rc) return rc;
+    IMP_RETURN_LAUNCH();
+}
+
+// q, k, v = A W^T with the per-head norm, the rotation and the cache write done in the product's epilogue
+// (see QkvRopeArgs): A [M, K], W [(Hq + 2 Hkv) * Dh, K] with q heads first, then k, then v.  Needs at least
+// 256 rows, head size 64 or 128 rotated over its whole width, CTA pairs enabled; returns IMP_ERR_UNSUPPORTED
+// otherwise (the caller then runs the product and the rotary kernel one after the other).
+IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int K, int Hq, int Hkv,
+                                      int Dh, const float* q_norm_w, const float* k_norm_w, float eps, const float* cos_tab,
+                                      const float* sin_tab, int max_pos, const int* positions, const int* seq_of_token,
+                                      const int* block_table, int bt_stride, int n_seqs, void* q_out, int64_t q_stride,
+                                      void* k_cache, void* v_cache, int page_size, int num_pages, int* status, void* stream) {
+    if (M == 0) return 0;
+    IMP_CHECK_ARG(A && W && M > 0 && K > 0 && Hq > 0 && Hkv > 0, "imp_gemm_bf16_tc_qkv_rope: bad argument");
+    IMP_CHECK_ARG(cos_tab && sin_tab && positions && seq_of_token && block_table && q_out && k_cache && v_cache,
+                  "imp_gemm_bf16_tc_qkv_rope: null pointer");
+    IMP_CHECK_ARG((q_norm_w == nullptr) == (k_norm_w == nullptr), "imp_gemm_bf16_tc_qkv_rope: q and k norm weights must both be set or both be null");
+    IMP_CHECK_ARG(lda >= K && ldw >= K && q_stride >= (int64_t)Hq * Dh && page_size > 0 && num_pages > 0 && max_pos > 0,
+                  "imp_gemm_bf16_tc_qkv_rope: bad geometry");
+    const int N = (Hq + 2 * Hkv) * Dh;
+    if (M < 256 || (Dh != 64 && Dh != 128)) return IMP_ERR_UNSUPPORTED;
+    if (K % 8 || lda % 8 || ldw % 8 || q_stride % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)q_out % 16 ||
+        (uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16)
+        return IMP_ERR_UNSUPPORTED;
+    static int ready = -1, sms = 148;
+    if (ready < 0) {
+        const char* e = getenv("IMP_B200_TC_PAIR");
+        ready = (e == nullptr || atoi(e) != 0) && getenv("IMP_B200_TC_SIMPLE") == nullptr ? 1 : 0;
+        if (ready) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 1)
+                sms = 148;
+            cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  TC2_SMEM_BYTES);
+            if (e2 != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e2)); ready = -1; return (int)e2; }
+        }
+    }
+    if (!ready) return IMP_ERR_UNSUPPORTED;
+    CUtensorMap ma, mw128;
+    if (int rc = make_map(&ma, A, M, K, lda, TC_BM)) return rc;
+    if (int rc = make_map(&mw128, W, N, K, ldw, 128)) return rc;
+    QkvRopeArgs a;
+    a.positions = positions; a.seq_of_token = seq_of_token; a.block_table = block_table;
+    a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w;
+    a.q_out = (__nv_bfloat16*)q_out; a.k_cache = (__nv_bfloat16*)k_cache; a.v_cache = (__nv_bfloat16*)v_cache;
+    a.q_stride = q_stride; a.eps = eps; a.bt_stride = bt_stride; a.n_seqs = n_seqs; a.max_pos = max_pos;
+    a.Hq = Hq; a.Hkv = Hkv; a.Dh = Dh; a.page_size = page_size; a.num_pages = num_pages;
+    const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
+    const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+    gemm_tc_pair_kernel<TC_OUT_QKV_ROPE><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, (cudaStream_t)stream>>>(
+        ma, mw128, nullptr, 0, M, N, K, status, a);
     IMP_RETURN_LAUNCH();
 }

@@ -207,6 +207,44 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, he
         "qk_norm_rope_kv_write")
 
 
+def linear_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int,
+                    head_dim: int, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                    cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                    block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    status: Optional[torch.Tensor] = None) -> bool:
+    """q, k, v = x w_qkv^T with the per-head norm, the rotation over the whole head and the cache write in
+    the product's epilogue: q goes to q_out [T, Hq*Dh], k and v to the pages.  Norm weights in float32.
+    Returns False, having done nothing, when the shape or the backend rules the fused kernel out
+    (fewer than 256 rows, a head size other than 64 / 128, alignment, IMP_B200_GEMM=cublas): the caller
+    then uses `linear` and `qk_norm_rope_kv_write`."""
+    if LARGE_M_BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16:
+        return False
+    T, Kd = x.shape
+    if T < 256 or head_dim not in (64, 128) or cos.shape[1] * 2 != head_dim:
+        return False
+    _need_cuda(q_out, x, w_qkv, q_norm_w, k_norm_w, cos, sin, positions, seq_of_token, block_table, k_cache, v_cache)
+    assert w_qkv.shape == ((n_q_heads + 2 * n_kv_heads) * head_dim, Kd) and x.stride(1) == 1 and w_qkv.stride(1) == 1
+    assert q_out.dtype == torch.bfloat16 and q_out.shape == (T, n_q_heads * head_dim) and q_out.stride(1) == 1
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    if q_norm_w is not None:
+        assert q_norm_w.dtype == torch.float32 and k_norm_w.dtype == torch.float32
+        assert q_norm_w.numel() == head_dim and k_norm_w.numel() == head_dim
+    assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and k_cache.shape == v_cache.shape
+    assert positions.dtype == torch.int32 and seq_of_token.dtype == torch.int32 and block_table.dtype == torch.int32
+    rc = L.load().imp_gemm_bf16_tc_qkv_rope(
+        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), T, Kd, n_q_heads, n_kv_heads, head_dim,
+        _ptr(q_norm_w), _ptr(k_norm_w), float(eps), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+        block_table.shape[0], q_out.data_ptr(), q_out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), page_size,
+        num_pages, _ptr(status), _stream())
+    if rc == -2:
+        return False
+    L.check(rc, "gemm_bf16_tc_qkv_rope")
+    return True
+
+
 def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                             k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                             seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0,

@@ -51,6 +51,10 @@ _SIGNATURES = {
                                             c_int, c_void_p]),
     "imp_gemm_bf16_tc": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
                                  c_void_p, c_void_p]),
+    "imp_gemm_bf16_tc_qkv_rope": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                                          c_void_p, c_void_p]),
     "imp_gemm_bf16_tc_swap": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
                                       c_void_p, c_void_p, c_void_p]),
     "imp_gemm_bf16_tc_swap_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),

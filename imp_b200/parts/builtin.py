@@ -134,15 +134,28 @@ class GQAAttention(Mixer):
         if self.q_norm is not None and self.q_norm.dtype != self.k_norm.dtype:
             self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
         self.norm_eps = float(params.get("qk_norm_eps", 1e-6))
+        # 32-bit copies of the two small weight vectors for the fused projection kernel
+        self.q_norm_f32 = self.q_norm.float().contiguous() if self.q_norm is not None else None
+        self.k_norm_f32 = self.k_norm.float().contiguous() if self.k_norm is not None else None
         pos = params.get("position")
         self.position = build_part("position", pos, {}, rt) if pos is not None else None
         tensors.clear()  # the separate q/k/v matrices are not kept
 
     def forward(self, x, ctx, cache: LayerCache):
         rt, T = self.rt, x.shape[0]
+        tables = self.position.rotary_tables() if self.position is not None else None
+        if tables is not None and cache.writes and not rt.is_float32 and tables[2] == self.dh:
+            # long portions: projection, norm, rotation and cache write in one kernel
+            q = rt.empty((T, self.hq * self.dh))
+            if K.linear_qkv_rope(q, x, self.w_qkv, self.hq, self.hkv, self.dh, self.q_norm_f32, self.k_norm_f32,
+                                 self.norm_eps, tables[0], tables[1], ctx.positions, ctx.seq_of_token, cache.block_table,
+                                 cache.kv[0], cache.kv[1], rt.status):
+                attn = rt.empty((T, self.hq * self.dh))
+                self.attend(attn, q, ctx, cache)
+                out = rt.empty((T, self.w_o.shape[0]))
+                return K.linear(out, attn, self.w_o)
         qkv = rt.empty((T, (self.hq + 2 * self.hkv) * self.dh))
         K.linear(qkv, x, self.w_qkv)
-        tables = self.position.rotary_tables() if self.position is not None else None
         k_cache = cache.kv[0] if cache.writes else None
         v_cache = cache.kv[1] if cache.writes else None
         if self.position is not None and tables is None:

@@ -834,3 +834,65 @@ def test_sampler_mirostat_state_typical_and_dry_through_the_class(K):
     alone = [sampler.sample(logits[i:i + 1].clone(), [rows[i]], [[11, 1, 1, 4][i]], [[0, 0, 0, 3][i]],
                             [[[], [], hist, []][i]], [SamplerState()])[0] for i in range(4)]
     assert got == alone
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,with_norm", [(32, 8, 128, 16, True), (3, 1, 64, 8, True), (5, 2, 128, 32, False),
+                                                      (8, 4, 64, 16, True)])
+def test_fused_qkv_projection_matches_projection_then_rotary_kernel(K, Hq, Hkv, Dh, page, with_norm):
+    """The q,k,v product with norm, rotation and cache write in its epilogue against the plain computation
+    (and, loosely, against the two-kernel path): q buffer, K pages and V pages; rows in two sequences that
+    start inside pages; a width that leaves the last 256-column tile of the product partly empty."""
+    T, Kd = 300, 192
+    lengths, starts = [210, 177], [40, 47]                 # 170 + 130 new tokens
+    bt, num_pages = paged_layout(lengths, page, seed=4)
+    toks = [(s, p) for s, (st, n) in enumerate(zip(starts, lengths)) for p in range(st, n)]
+    assert len(toks) == T
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32)
+    N = (Hq + 2 * Hkv) * Dh
+    x = rnd(T, Kd, dtype=torch.bfloat16, seed=41)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=42, scale=0.1)
+    qw = (1 + 0.2 * rnd(Dh, seed=43)) if with_norm else None
+    kw = (1 + 0.2 * rnd(Dh, seed=44)) if with_norm else None
+    max_pos = 256
+    i = torch.arange(Dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-2.0 * i / Dh))[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    kc = torch.zeros(num_pages, Hkv, page, Dh, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.full((T, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = K.new_status(DEV)
+    ran = K.linear_qkv_rope(q_out, x.to(DEV), w.to(DEV), Hq, Hkv, Dh, None if qw is None else qw.to(DEV),
+                            None if kw is None else kw.to(DEV), 1e-6, cos, sin, pos.to(DEV), seq.to(DEV), bt.to(DEV), kc, vc,
+                            status)
+    assert ran, "the fused kernel should take this shape"
+    K.check_status(status)
+    # plain computation in double precision
+    y = x.double() @ w.double().T
+    q = y[:, :Hq * Dh].view(T, Hq, Dh)
+    k = y[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+    v = y[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+    if with_norm:
+        q, k = P.rmsnorm(q, qw.double(), 1e-6), P.rmsnorm(k, kw.double(), 1e-6)
+    q, k = P.rope(q, pos.tolist(), 1e4), P.rope(k, pos.tolist(), 1e4)
+    close(q_out.view(T, Hq, Dh), q, torch.bfloat16)
+    kc_c, vc_c = kc.cpu(), vc.cpu()
+    touched = torch.zeros(num_pages, page, dtype=torch.bool)
+    for n, (s, p) in enumerate(toks):
+        pg, sl = int(bt[s, p // page]), p % page
+        close(kc_c[pg, :, sl, :], k[n], torch.bfloat16)
+        close(vc_c[pg, :, sl, :], v[n], torch.bfloat16)
+        touched[pg, sl] = True
+    assert (kc_c[~touched.unsqueeze(1).expand(-1, Hkv, -1)] == 0).all() and (vc_c[~touched.unsqueeze(1).expand(-1, Hkv, -1)] == 0).all()
+    # fewer than 256 rows, or another head size: declined, nothing written
+    q2 = torch.full((100, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert not K.linear_qkv_rope(q2, x[:100].to(DEV), w.to(DEV), Hq, Hkv, Dh, None, None, 1e-6, cos, sin, pos[:100].to(DEV),
+                                 seq[:100].to(DEV), bt.to(DEV), kc, vc, status)
+    assert torch.isnan(q2.float()).all()
+    # a page outside the pool is reported, its rows are not written
+    badbt = bt.clone()
+    badbt[1, starts[1] // page] = num_pages + 3
+    K.linear_qkv_rope(q_out, x.to(DEV), w.to(DEV), Hq, Hkv, Dh, None, None, 1e-6, cos, sin, pos.to(DEV), seq.to(DEV),
+                      badbt.to(DEV), kc, vc, status)
+    with pytest.raises(Exception, match="page"):
+        K.check_status(status)
