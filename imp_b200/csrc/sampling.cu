@@ -9,8 +9,9 @@
 // logits/T over the whole vocabulary, the k most probable, the shortest prefix
 // of them whose probability reaches top_p, renormalise, one uniform draw.
 // Differences: one block per row for any number of rows at once; k is not
-// capped at 128 (selection is a bitwise search over ordered keys instead of
-// per-thread heaps); ties at a cut are kept; the uniform number is an input
+// capped at 128 (the kept tokens are found by a radix selection over ordered
+// keys into a short list of up to 1024 candidates, where the cuts and the draw
+// are made; wider sets take a bitwise search over the keys, 32 passes per filter); ties at a cut are kept; the uniform number is an input
 // (the reference re-seeds an LCG with the same seed on every call, :541-543,
 // which draws the same number at every step); the draw walks the kept tokens in
 // index order.  Every reduction has a fixed order, so a row's result does not
@@ -18,6 +19,7 @@
 #include "common.cuh"
 
 constexpr int SAMPLE_BLOCK = 1024;
+constexpr int SAMPLE_CAND = 1024;    // tokens the sampler's short list holds (one per thread)
 
 __device__ __forceinline__ unsigned ordered_key(float f) {
     const unsigned b = __float_as_uint(f);
@@ -302,6 +304,147 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK) sample_kernel(
     for (int i = tid; i < V; i += SAMPLE_BLOCK)
         if (KEPT0(i)) z += EVAL(i);
     z = block_sum(z, scratch);
+
+    // ---- short list: when the filters leave at most SAMPLE_CAND tokens, find them with a radix selection
+    // (four passes over the row instead of 32 per filter), bring them into shared memory in index order and
+    // do the nucleus cut and the draw there.  Same kept set and same draw rule as the passes below, which
+    // remain for the cases the short list cannot hold (no top-k and a nucleus wider than SAMPLE_CAND tokens).
+    {
+        const float tp0 = top_p[r];
+        const bool k_on = k > 0 && k < V, p_on = tp0 > 0.f && tp0 < 1.f;
+        const int want_n = k_on ? k : SAMPLE_CAND;
+        if ((k_on || p_on) && want_n <= SAMPLE_CAND) {
+            __shared__ int hist[256];
+            __shared__ int s_sel[3];                  // chosen bin, tokens still wanted, candidates so far
+            __shared__ int c_idx[SAMPLE_CAND], c_tmp[SAMPLE_CAND];
+            __shared__ float c_e[SAMPLE_CAND], c_x[SAMPLE_CAND];
+            // the want_n-th largest ordered key among the tokens min-p keeps, 8 bits at a time
+            unsigned prefix = 0u;
+            int remaining = want_n;
+            bool all_kept = false;                    // fewer than want_n tokens in all: everything is a candidate
+            for (int shift = 24; shift >= 0; shift -= 8) {
+                for (int b = tid; b < 256; b += SAMPLE_BLOCK) hist[b] = 0;
+                __syncthreads();
+                const unsigned hi_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+                for (int i0 = 0; i0 < V; i0 += SAMPLE_BLOCK) {
+                    const int i = i0 + tid;
+                    int bin = -1;
+                    if (i < V && KEPT0(i)) {
+                        const unsigned key = ordered_key(x[i]);
+                        if ((key & hi_mask) == prefix) bin = (int)((key >> shift) & 255u);
+                    }
+                    // lanes of a warp that hit the same bin add up first: one atomic per bin and warp
+                    const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                    if (bin >= 0 && (int)(__ffs(peers) - 1) == (tid & 31)) atomicAdd(&hist[bin], __popc(peers));
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    int acc = 0, b = 255;
+                    for (; b >= 0; --b) {
+                        if (acc + hist[b] >= remaining) break;
+                        acc += hist[b];
+                    }
+                    s_sel[0] = b;                     // -1: not enough tokens under this prefix
+                    s_sel[1] = remaining - acc;
+                    // everything above the chosen bin plus the whole bin fits the list: no need to look closer,
+                    // the exact cut is made among the candidates
+                    if (b >= 0 && (want_n - remaining) + acc + hist[b] <= SAMPLE_CAND) s_sel[0] = b | 0x100;
+                }
+                __syncthreads();
+                if (s_sel[0] < 0) { all_kept = true; break; }
+                prefix |= (unsigned)(s_sel[0] & 0xff) << shift;
+                remaining = s_sel[1];
+                const bool stop = (s_sel[0] & 0x100) != 0;
+                __syncthreads();
+                if (stop) break;
+            }
+            const unsigned tau_k = all_kept ? 0u : prefix;   // lower edge of the last bin looked at
+            // candidates: min-p kept and key >= tau_k; more than the list holds (ties) -> the general passes
+            if (tid == 0) s_sel[2] = 0;
+            __syncthreads();
+            for (int i = tid; i < V; i += SAMPLE_BLOCK)
+                if (KEPT0(i) && ordered_key(x[i]) >= tau_k) {
+                    const int slot = atomicAdd(&s_sel[2], 1);
+                    if (slot < SAMPLE_CAND) c_tmp[slot] = i;
+                }
+            __syncthreads();
+            const int c = s_sel[2];
+            if (c >= 1 && c <= SAMPLE_CAND) {
+                // into index order (the order they arrived in varies from run to run; the sums below must not)
+                if (tid < c) {
+                    const int me = c_tmp[tid];
+                    int rank = 0;
+                    for (int j = 0; j < c; ++j) rank += c_tmp[j] < me;
+                    c_idx[rank] = me;
+                }
+                __syncthreads();
+                if (tid < c) {
+                    c_x[tid] = x[c_idx[tid]];
+                    c_e[tid] = EVAL(c_idx[tid]);
+                }
+                __syncthreads();
+                bool keep = tid < c;
+                if (k_on && tid < c) {                 // the list may hold more than k: keep those with fewer than k above them
+                    int greater = 0;
+                    const float mine = c_x[tid];
+                    for (int j = 0; j < c; ++j) greater += c_x[j] > mine;
+                    keep = greater < k;
+                }
+                bool usable = true;
+                if (p_on) {
+                    const float want = tp0 * z;
+                    if (!k_on) {
+                        // without top-k the list must contain the whole nucleus: its mass has to reach the target
+                        if (tid == 0) {
+                            float m = 0.f;
+                            for (int j = 0; j < c; ++j) m += c_e[j];
+                            scratch[0] = m;
+                        }
+                        __syncthreads();
+                        usable = scratch[0] >= want || all_kept;
+                        __syncthreads();
+                    }
+                    if (usable && tid < c) {
+                        float above = 0.f;            // mass of the strictly more probable candidates
+                        const float mine = c_x[tid];
+                        for (int j = 0; j < c; ++j)
+                            if (c_x[j] > mine) above += c_e[j];
+                        keep = keep && above < want;
+                    }
+                }
+                if (usable) {
+                    part[tid] = keep ? c_e[tid] : 0.f;
+                    if (tid < c) c_tmp[tid] = keep ? 1 : 0;
+                    if (tid == 0) s_pick = -1;
+                    __syncthreads();
+                    if (tid == 0) {
+                        float run = 0.f;
+                        for (int j = 0; j < c; ++j) {
+                            const float v = part[j];
+                            part[j] = run;            // exclusive prefix in index order
+                            run += v;
+                        }
+                        scratch[0] = run;
+                    }
+                    __syncthreads();
+                    const float target = uniform[r] * scratch[0];
+                    if (keep && c_e[tid] > 0.f && part[tid] <= target && target < part[tid] + c_e[tid]) s_pick = c_idx[tid];
+                    __syncthreads();
+                    if (tid == 0) {
+                        int pick = s_pick;
+                        if (pick < 0) {               // rounding left no owner: the last kept candidate, else the most probable
+                            for (int j = c - 1; j >= 0 && pick < 0; --j)
+                                if (c_tmp[j]) pick = c_idx[j];
+                            if (pick < 0) pick = arg;
+                        }
+                        out[r] = pick;
+                    }
+                    return;
+                }
+            }
+            __syncthreads();
+        }
+    }
 
     unsigned tau = 0u;  // keep keys >= tau
     if (k > 0 && k < V) {

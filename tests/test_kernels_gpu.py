@@ -896,3 +896,23 @@ def test_fused_qkv_projection_matches_projection_then_rotary_kernel(K, Hq, Hkv, 
                       badbt.to(DEV), kc, vc, status)
     with pytest.raises(Exception, match="page"):
         K.check_status(status)
+
+
+@pytest.mark.parametrize("scale,filters", [(4.0, {"top_k": 40, "top_p": 0.9}), (4.0, {"top_p": 0.95}), (0.3, {"top_p": 0.9}),
+                                           (2.0, {"top_k": 2000}), (2.0, {"top_k": 1000, "min_p": 0.001}),
+                                           (3.0, {"top_k": 5, "top_p": 0.3})])
+def test_sample_large_vocabulary_short_list_and_general_passes(K, scale, filters):
+    """At a real vocabulary the sampler finds the kept tokens by a radix selection into a short list of at
+    most 1024 candidates; a nucleus or a top-k wider than that takes the general passes.  Both must pick
+    what the plain twin picks."""
+    V, R = 50021, 24
+    logits = rnd(1, V, seed=51, scale=scale).repeat(R, 1)
+    logits[:, 123] = logits[:, 77]                       # a tie inside the distribution
+    us = np.random.default_rng(3).random(R).astype(np.float32)
+    got = run_sample(K, logits, 0.8, us, **filters)
+    x = logits[0].numpy()
+    keep, _ = S.kept_set(x, 0.8, **filters)
+    for tok, u in zip(got, us):
+        assert keep[tok], f"token {tok} is outside the kept set of {filters}"
+        lo, hi, _ = S.draw_interval(x, 0.8, tok, **filters)
+        assert lo - 2e-5 <= u <= hi + 2e-5, f"u={u} does not select token {tok} (interval [{lo}, {hi}))"
