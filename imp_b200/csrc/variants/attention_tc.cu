@@ -10,15 +10,15 @@
 //                    and 64 head dimensions, into shared-memory rings; page ids come from the block
 //                    table, pages that do not exist are fetched from beyond the tensor (zeros).
 //   warp 1, lane 0   MMA issuer.  S_w = Q_w K^T (M=128 tokens, N=128 keys, K=head size) into tensor
-//                    memory, and O_w += P_w V (M=128, N=head size, K=128 keys), V being read as an
+//                    memory, and O_w += P_w V (M=128, N=head size, K=128 keys; P from tensor memory), V being read as an
 //                    MN-major operand straight from its [key, dim] layout.  After P_w V of tile i
 //                    it issues Q_w K^T of tile i+1, so while one head's softmax runs the tensor
 //                    cores work on the other head.
 //   warps 4..7 (head 0), 8..11 (head 1)   softmax.  A thread owns one query row: it reads its row of
 //                    S from tensor memory, applies the causal / window mask on tiles that need it,
 //                    keeps the running maximum and sum in 32-bit, writes P = exp2(s - m) as bfloat16
-//                    into shared memory in the K-major swizzled layout the MMA reads, and at the
-//                    end divides its row of O by the sum and stores it.  O stays in tensor memory
+//                    pairs back into tensor memory over S, from where the MMA takes it as its A
+//                    operand, and at the end divides its row of O by the sum and stores it.  O stays in tensor memory
 //                    across key tiles; it is rescaled only when a row's maximum grew by more than
 //                    2^8 since the last rescale (P then stays below 2^8, exact enough in bfloat16
 //                    and 32-bit sums), the decision being taken per warp.
@@ -44,16 +44,15 @@ constexpr int FA_BN = 128;                       // keys per tile
 constexpr int FA_KB = DH / 64;                   // 64-wide blocks of the head dimension
 constexpr int FA_BLOCK_BYTES = 128 * 128;        // 128 rows of 128 bytes: one swizzled block
 constexpr int FA_Q_BYTES = FA_KB * FA_BLOCK_BYTES;          // one head's Q tile
-constexpr int FA_P_BYTES = 2 * FA_BLOCK_BYTES;              // one head's P tile (128 x 128 keys)
 constexpr int FA_KV_BYTES = FA_KB * FA_BLOCK_BYTES;         // one K or V tile
 constexpr float FA_RESCALE_STEP = 8.f;           // log2 of the growth of a row maximum that forces a rescale
 
 template <int NQ> struct FaCfg {
-    static constexpr int K_STAGES = (DH == 128 && NQ == 2) ? 1 : 2;
+    static constexpr int K_STAGES = 2;
     static constexpr int V_STAGES = 2;
     static constexpr int THREADS = 128 + 128 * NQ;        // warps 0-3: producer, MMA issuer, two idle; then 4 per head
     static constexpr int TMEM_COLS = 256 * NQ;
-    static constexpr int TILE_BYTES = NQ * (FA_Q_BYTES + FA_P_BYTES) + (K_STAGES + V_STAGES) * FA_KV_BYTES;
+    static constexpr int TILE_BYTES = NQ * FA_Q_BYTES + (K_STAGES + V_STAGES) * FA_KV_BYTES;
     static constexpr int N_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 3 * NQ;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
 };
@@ -69,6 +68,17 @@ __device__ __forceinline__ uint64_t fa_v_desc(uint32_t addr) {
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
+}
+
+// D += A B with A (bfloat16, two consecutive K elements per 32-bit column, one row per lane) in tensor memory.
+__device__ __forceinline__ void fa_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 __device__ __forceinline__ float fa_exp2(float x) {
@@ -96,8 +106,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     extern __shared__ unsigned char fa_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = tiles;                                   // [NQ][FA_Q_BYTES]
-    unsigned char* p_s = q_s + NQ * FA_Q_BYTES;                   // [NQ][FA_P_BYTES]
-    unsigned char* k_s = p_s + NQ * FA_P_BYTES;                   // [KS][FA_KV_BYTES]
+    unsigned char* k_s = q_s + NQ * FA_Q_BYTES;                   // [KS][FA_KV_BYTES]
     unsigned char* v_s = k_s + KS * FA_KV_BYTES;                  // [VS][FA_KV_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::TILE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BARS);
@@ -241,12 +250,12 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     if (ok && w == 0) ok = mbar_wait(v_full0 + 8 * (i % VS), (uint32_t)(i / VS) & 1u, status);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t p_addr = smem_u32(p_s + w * FA_P_BYTES), v_addr = smem_u32(v_s + (i % VS) * FA_KV_BYTES);
+                    const uint32_t v_addr = smem_u32(v_s + (i % VS) * FA_KV_BYTES);
+                    // P is the A operand straight from tensor memory: 16 keys = 8 columns of bfloat16 pairs per step
 #pragma unroll
                     for (int t = 0; t < FA_BN / 16; ++t)
-                        tc_mma(tmem_base + (uint32_t)(w * 256 + 128),
-                               tc_smem_desc(p_addr + (t >> 2) * FA_BLOCK_BYTES + (t & 3) * 32), fa_v_desc(v_addr + t * 2048),
-                               idesc_o, (i > 0 || t > 0) ? 1u : 0u);
+                        fa_mma_ts(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256 + t * 8),
+                                  fa_v_desc(v_addr + t * 2048), idesc_o, (i > 0 || t > 0) ? 1u : 0u);
                     tc_commit(o_done0 + 8 * w);
                     if (w == NQ - 1) tc_commit(v_empty0 + 8 * (i % VS));
                     if (i + 1 < n_kt) {
@@ -270,7 +279,6 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_tmem = lane_base + (uint32_t)(w * 256), o_tmem = s_tmem + 128u;
         const int p = pos0 + (row < rows ? row : rows - 1);  // padding rows repeat the last real row
-        unsigned char* p_row = p_s + w * FA_P_BYTES + (row >> 3) * 1024 + (row & 7) * 128;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_kt && ok; ++i) {
@@ -326,29 +334,26 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 m_used = m_new;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;    // a row with nothing visible yet
+            // P = exp2(s - m) as bfloat16 pairs, written over the first 64 columns of S (this thread's own row):
+            // keys 2j, 2j+1 share column j, the lower key in the lower half
 #pragma unroll
-            for (int c = 0; c < FA_BN / 32; ++c) {
-                float v[32];
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                float pk[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    v[j] = fa_exp2(fmaf(__uint_as_float(sr[c][j]), scale_log2, -m_sub));   // exp2(-inf) = 0 for masked keys
-                    l += v[j];
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int c = 2 * hlf + cc;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[c][j]), scale_log2, -m_sub));   // exp2(-inf) = 0: masked
+                        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[c][j + 1]), scale_log2, -m_sub));
+                        l += e0 + e1;
+                        pk[cc * 16 + (j >> 1)] = __uint_as_float(fa_pack(e0, e1));
+                    }
                 }
-                // 32 keys = four 16-byte chunks of this row in key block c / 2
-                unsigned char* blk = p_row + (c >> 1) * FA_BLOCK_BYTES;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int chunk = ((c & 1) * 4 + t) ^ (row & 7);
-                    uint4 u;
-                    u.x = fa_pack(v[8 * t], v[8 * t + 1]);
-                    u.y = fa_pack(v[8 * t + 2], v[8 * t + 3]);
-                    u.z = fa_pack(v[8 * t + 4], v[8 * t + 5]);
-                    u.w = fa_pack(v[8 * t + 6], v[8 * t + 7]);
-                    *reinterpret_cast<uint4*>(blk + chunk * 16) = u;
-                }
+                tc_st32(s_tmem + (uint32_t)(hlf * 32), pk);
             }
+            tc_wait_st();
             tc_fence_before_sync();                                       // this row's reads and writes of tensor memory
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores' proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready0 + 8 * w);
         }
