@@ -297,7 +297,8 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             tc_wait_ld_pin<true>(sr[0]);
 #pragma unroll
             for (int c = 1; c < FA_BN / 32; ++c) tc_wait_ld_pin<false>(sr[c]);
-            float tmax = -INFINITY;
+            // four independent maxima: one chain of 128 dependent comparisons would sit on the critical path
+            float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < FA_BN / 32; ++c)
@@ -305,14 +306,15 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     for (int j = 0; j < 32; ++j) {
                         const int col = c * 32 + j;
                         if (!(col <= hi && col >= lo)) sr[c][j] = 0xff800000u;   // -inf
-                        tmax = fmaxf(tmax, __uint_as_float(sr[c][j]));
+                        tm[j & 3] = fmaxf(tm[j & 3], __uint_as_float(sr[c][j]));
                     }
             } else {
 #pragma unroll
                 for (int c = 0; c < FA_BN / 32; ++c)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(sr[c][j]));
+                    for (int j = 0; j < 32; ++j) tm[j & 3] = fmaxf(tm[j & 3], __uint_as_float(sr[c][j]));
             }
+            float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
             tmax *= scale_log2;                                           // scale > 0: the order is kept
             const bool grow = tmax > m_used + FA_RESCALE_STEP;            // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
@@ -334,6 +336,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 m_used = m_new;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;    // a row with nothing visible yet
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};                             // four partial sums, added in a fixed order
             // P = exp2(s - m) as bfloat16 pairs, written over the first 64 columns of S (this thread's own row):
             // keys 2j, 2j+1 share column j, the lower key in the lower half
 #pragma unroll
@@ -346,12 +349,13 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     for (int j = 0; j < 32; j += 2) {
                         const float e0 = fa_exp2(fmaf(__uint_as_float(sr[c][j]), scale_log2, -m_sub));   // exp2(-inf) = 0: masked
                         const float e1 = fa_exp2(fmaf(__uint_as_float(sr[c][j + 1]), scale_log2, -m_sub));
-                        l += e0 + e1;
+                        ls[(j >> 1) & 3] += e0 + e1;
                         pk[cc * 16 + (j >> 1)] = __uint_as_float(fa_pack(e0, e1));
                     }
                 }
                 tc_st32(s_tmem + (uint32_t)(hlf * 32), pk);
             }
+            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             tc_wait_st();
             tc_fence_before_sync();                                       // this row's reads and writes of tensor memory
             __syncwarp();
