@@ -952,7 +952,9 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
     IMP_CHECK_ARG(splits == 1 || scratch, "imp_gemm_bf16_tc_swap: %d splits of K need scratch memory", splits);
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_per_split = (total_kb + splits - 1) / splits;
-    const int BN = M <= 64 ? 64 : 128;
+    static int bn32 = -1;                     // IMP_B200_TCS_BN32=0 keeps 64 columns for up to 32 rows (measurements)
+    if (bn32 < 0) { const char* e = getenv("IMP_B200_TCS_BN32"); bn32 = e ? atoi(e) : 1; }
+    const int BN = (M <= 32 && bn32) ? 32 : (M <= 64 ? 64 : 128);
     CUtensorMap mw, mx;
     if (int rc = make_map(&mw, W, N, K, ldw, 128)) return rc;
     if (int rc = make_map(&mx, A, M, K, lda, BN)) return rc;
@@ -960,7 +962,8 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
     int rc = 0;
     if (splits > 1) {
         const int64_t split_stride = (int64_t)M * N;
-        rc = BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s);
         if (rc) return rc;
         const int64_t total = (int64_t)M * N;
@@ -974,13 +977,16 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
                            (const float*)scratch, split_stride, M, N, splits);
         if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     } else if (epilogue == TC_OUT_BF16) {
-        rc = BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
     } else if (epilogue == TC_OUT_F32) {
-        rc = BN == 64 ? launch_tcs<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
     } else {
-        rc = BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
     }
     if (rc) return rc;

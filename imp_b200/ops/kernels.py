@@ -28,7 +28,8 @@ if LARGE_M_BACKEND not in ("tcgen05", "cublas"):
 # Rows up to which the weight-streaming kernel is used for bfloat16 products; above it the
 # library GEMM (cuBLAS through torch.mm) runs, as the reference does for its T>1 products
 # (src/compute/gemm.cu:303-445).
-SMALL_M_MAX = 16
+SMALL_M_MAX = 16        # most rows the weight-streaming kernel takes
+STREAM_M_MAX = 7         # rows up to which it is the first choice (measured: from 8 rows the tcgen05 swap-AB kernel wins)
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -108,7 +109,11 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tenso
     F = out.shape[1]
     if M == 0:
         return out
-    if x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and M <= SMALL_M_MAX and out.dtype == x.dtype:
+    bf16 = x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == x.dtype
+    if (bf16 and STREAM_M_MAX < M <= SMALL_M_MAX and LARGE_M_BACKEND == "tcgen05"
+            and gemm_bf16_tc_swap(out, x, w_interleaved, TC_OUT_SWIGLU)):
+        return out
+    if bf16 and M <= SMALL_M_MAX:
         assert x.stride(1) == 1 and w_interleaved.stride(1) == 1 and out.stride(1) == 1
         rc = L.load().imp_gemm_bf16_stream_swiglu(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0),
                                                   w_interleaved.data_ptr(), w_interleaved.stride(0), M, 2 * F,
@@ -381,6 +386,12 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.bfloat16:
         raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
     if M <= SMALL_M_MAX:
+        # The weight-streaming kernel, except where the swap-AB tcgen05 kernel measured faster: from 8 rows up,
+        # and at any row count for products with a long contraction and few output columns (K split over CTAs).
+        N, Kd = w.shape
+        if (LARGE_M_BACKEND == "tcgen05" and (M > STREAM_M_MAX or (Kd >= 2 * N and N >= 1024))
+                and gemm_bf16_tc_swap(out, x, w)):
+            return out
         return gemm_bf16_stream(out, x, w)
     if LARGE_M_BACKEND == "tcgen05":
         if M <= TC_SWAP_MAX_M and gemm_bf16_tc_swap(out, x, w):
