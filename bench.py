@@ -210,8 +210,9 @@ def run_ours(args):
 
     gen = torch.Generator().manual_seed(0)
     if args.only == "decode":
-        ms, calls = time_decode(eng, B, CONTEXT, args.steps, args.warmup, torch, K, StepEntry)
-        print(json.dumps({"only": "decode", "batch": B, "layers": n_layers, "ms_per_step": round(ms, 4),
+        ctx = min(max(args.context or CONTEXT, args.steps + args.warmup + 1), CONTEXT)
+        ms, calls = time_decode(eng, B, ctx, args.steps, args.warmup, torch, K, StepEntry)
+        print(json.dumps({"only": "decode", "batch": B, "layers": n_layers, "context": ctx, "ms_per_step": round(ms, 4),
                           "launcher_calls_per_step": calls}))
         return 0
     # ---- prefill: one prompt of 2,048 tokens in one step --------------------------------------------
@@ -334,6 +335,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one phase only and print its timing (for profiling small cases)")
+    ap.add_argument("--context", type=int, default=0,
+                    help="with --only decode: the contexts end here instead of at the configured length")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -939,10 +939,10 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
 
 // C = A[M,K] * W[N,K]^T for 1 <= M <= 128 with the weights on the M side of the MMA.
 // epilogue as for imp_gemm_bf16_tc.  `scratch` must hold imp_gemm_bf16_tc_swap_scratch_floats() floats.
-IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
-                                  int M, int N, int K, float* scratch, int* status, void* stream) {
+static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                  int M, int N, int K, float* scratch, int* status, void* stream, bool partials_only) {
     if (M == 0 || N == 0) return 0;
-    IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_tc_swap: bad argument");
+    IMP_CHECK_ARG((C || partials_only) && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_tc_swap: bad argument");
     IMP_CHECK_ARG(M <= 128, "imp_gemm_bf16_tc_swap: M %d exceeds 128", M);
     IMP_CHECK_ARG(epilogue >= 0 && epilogue <= 2, "imp_gemm_bf16_tc_swap: unknown epilogue %d", epilogue);
     if (epilogue == 2) IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_tc_swap: %d interleaved rows are not a multiple of 16", N);
@@ -966,6 +966,7 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
            : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
                       : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s);
         if (rc) return rc;
+        if (partials_only) IMP_RETURN_LAUNCH();
         const int64_t total = (int64_t)M * N;
         const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
         cudaError_t e;
@@ -991,6 +992,44 @@ IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void
     }
     if (rc) return rc;
     IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                  int M, int N, int K, float* scratch, int* status, void* stream) {
+    return gemm_bf16_tc_swap_impl(C, ldc, epilogue, A, lda, W, ldw, M, N, K, scratch, status, stream, false);
+}
+
+// How many partial results imp_gemm_bf16_tc_swap_partials leaves for this shape (1: it does not split, call the
+// plain entry point instead).
+IMP_API int imp_gemm_bf16_tc_swap_splits(int M, int N, int K) { return tcs_splits(M, N, K, TC_OUT_F32); }
+
+// The product left unsummed: scratch[s][M, N] (32-bit, M * N floats apart) for s < imp_gemm_bf16_tc_swap_splits()
+// holds the part of A W^T that split s of the contraction contributes.  Whoever reads the result next adds the
+// parts in split order (the norm and rotary kernels have entry points that do), which saves the summing kernel.
+IMP_API int imp_gemm_bf16_tc_swap_partials(float* scratch, const void* A, int64_t lda, const void* W, int64_t ldw, int M,
+                                           int N, int K, int* status, void* stream) {
+    IMP_CHECK_ARG(scratch, "imp_gemm_bf16_tc_swap_partials: no scratch memory");
+    if (tcs_splits(M, N, K, TC_OUT_F32) < 2) return IMP_ERR_UNSUPPORTED;
+    return gemm_bf16_tc_swap_impl(nullptr, N, TC_OUT_F32, A, lda, W, ldw, M, N, K, scratch, status, stream, true);
+}
+
+// C[M, N] (bfloat16 or float32, by `epilogue`) = the sum of the partial results, in split order.
+IMP_API int imp_gemm_bf16_tc_swap_sum(void* C, int64_t ldc, int epilogue, const float* scratch, int M, int N, int splits,
+                                      void* stream) {
+    if (M == 0 || N == 0) return 0;
+    IMP_CHECK_ARG(C && scratch && splits >= 1 && ldc >= N && (epilogue == TC_OUT_BF16 || epilogue == TC_OUT_F32),
+                  "imp_gemm_bf16_tc_swap_sum: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)M * N;
+    const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    cudaError_t e;
+    if (epilogue == TC_OUT_F32)
+        e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, scratch, total, M, N, splits);
+    else
+        e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc, scratch,
+                       total, M, N, splits);
+    if (e != cudaSuccess) { imp_set_error("gemm_tc_swap_sum: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
 }
 
 // q, k, v = A W^T with the per-head norm, the rotation and the cache write done in the product's epilogue

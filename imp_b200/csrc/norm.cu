@@ -72,18 +72,23 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
-template <typename TA, typename TW>
+// SPLIT: the branch has not been summed yet.  `part` holds n_splits 32-bit partial results [n_rows_total, d] of a
+// product whose contraction was cut over CTAs, split_stride floats apart; the branch value is their sum in split
+// order rounded to TA, bit for bit what the summing kernel would have stored.
+template <typename TA, typename TW, bool SPLIT>
 __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch,
                                                                      const TW* __restrict__ w, TA* __restrict__ out,
                                                                      const int* __restrict__ rows, int d, float eps,
-                                                                     float weight_offset, int write_h) {
+                                                                     float weight_offset, int write_h,
+                                                                     const float* __restrict__ part, int64_t split_stride,
+                                                                     int n_splits) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int64_t src = rows ? rows[r] : r;
     float* hrow = h + src * d;
-    const TA* brow = branch ? branch + src * d : nullptr;
+    const TA* brow = (SPLIT || branch) ? branch + src * d : nullptr;   // with SPLIT only its null-ness is used
     const int nv = d >> 2;
     float4 v[NORM_MAX_V4], wv[NORM_MAX_V4];
 #pragma unroll
@@ -94,7 +99,24 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
             wv[i] = Vec4<TW>::load(w + 4 * c);
         }
     }
-    if (brow) {
+    if (SPLIT) {
+        const float* prow = part + src * d;
+#pragma unroll
+        for (int i = 0; i < NORM_MAX_V4; ++i) {
+            const int c = threadIdx.x + i * NORM_BLOCK;
+            if (c < nv) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s = 0; s < n_splits; ++s) {
+                    const float4 b = Vec4<float>::load(prow + s * split_stride + 4 * c);
+                    acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+                }
+                v[i].x += to_float(from_float<TA>(acc.x));
+                v[i].y += to_float(from_float<TA>(acc.y));
+                v[i].z += to_float(from_float<TA>(acc.z));
+                v[i].w += to_float(from_float<TA>(acc.w));
+            }
+        }
+    } else if (brow) {
 #pragma unroll
         for (int i = 0; i < NORM_MAX_V4; ++i) {
             const int c = threadIdx.x + i * NORM_BLOCK;
@@ -145,12 +167,165 @@ IMP_API int imp_add_rmsnorm(float* h, const void* branch, const void* w, void* o
 #define LAUNCH(TA, TW)                                                                                     \
     do {                                                                                                   \
         if (vec)                                                                                           \
-            imp_launch(add_rmsnorm_vec_kernel<TA, TW>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,        \
-                       (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h);   \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW, false>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h, \
+                       (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h,    \
+                       (const float*)nullptr, (int64_t)0, 0);                                              \
         else                                                                                               \
             add_rmsnorm_kernel<TA, TW><<<n_out_rows, NORM_BLOCK, 0, s>>>(                                  \
                 h, (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h);       \
     } while (0)
+    if (act_dtype == IMP_F32 && w_dtype == IMP_F32) LAUNCH(float, float);
+    else if (act_dtype == IMP_F32) LAUNCH(float, __nv_bfloat16);
+    else if (w_dtype == IMP_F32) LAUNCH(__nv_bfloat16, float);
+    else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+    IMP_RETURN_LAUNCH();
+}
+
+// The unsummed branch for few rows: one row is shared by a cluster of CTAs, 512 columns each (a thread holds
+// one float4, or two for rows of more than 4096 columns), so that the n_splits partial rows are fetched by
+// enough threads at once.  Each CTA adds up its squares, stores the sum into every CTA of the cluster (shared
+// memory of the cluster), and after one cluster barrier all of them add the same numbers in rank order.
+constexpr int CN_THREADS = 128, CN_MAX_C = 8, CN_MAX_V = 2;
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(CN_THREADS) add_rmsnorm_split_cluster_kernel(
+    float* __restrict__ h, const TW* __restrict__ w, TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+    float weight_offset, int write_h, const float* __restrict__ part, int64_t split_stride, int n_splits) {
+    __shared__ float scratch[33];
+    __shared__ float slots[CN_MAX_C];
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int C = gridDim.x;
+    // first half of "every CTA of the cluster is running"; the wait stands before the first remote store
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.y;
+    const int64_t src = rows ? rows[r] : r;
+    float* hrow = h + src * d;
+    const float* prow = part + src * d;
+    const int nv = d >> 2;
+    float4 v[CN_MAX_V], wv[CN_MAX_V];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CN_MAX_V; ++i) {
+        const int c = (int)rank * CN_THREADS + threadIdx.x + i * C * CN_THREADS;
+        if (c < nv) {
+            v[i] = Vec4<float>::load(hrow + 4 * c);
+            wv[i] = Vec4<TW>::load(w + 4 * c);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* p = prow + 4 * c;
+            int sp = 0;
+            for (; sp + 4 <= n_splits; sp += 4) {      // four rows requested together, added in split order
+                const float4 b0 = Vec4<float>::load(p + (sp + 0) * split_stride), b1 = Vec4<float>::load(p + (sp + 1) * split_stride);
+                const float4 b2 = Vec4<float>::load(p + (sp + 2) * split_stride), b3 = Vec4<float>::load(p + (sp + 3) * split_stride);
+                acc.x += b0.x; acc.y += b0.y; acc.z += b0.z; acc.w += b0.w;
+                acc.x += b1.x; acc.y += b1.y; acc.z += b1.z; acc.w += b1.w;
+                acc.x += b2.x; acc.y += b2.y; acc.z += b2.z; acc.w += b2.w;
+                acc.x += b3.x; acc.y += b3.y; acc.z += b3.z; acc.w += b3.w;
+            }
+            for (; sp < n_splits; ++sp) {
+                const float4 b = Vec4<float>::load(p + sp * split_stride);
+                acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            }
+            v[i].x += to_float(from_float<TA>(acc.x));
+            v[i].y += to_float(from_float<TA>(acc.y));
+            v[i].z += to_float(from_float<TA>(acc.z));
+            v[i].w += to_float(from_float<TA>(acc.w));
+            if (write_h) Vec4<float>::store(hrow + 4 * c, v[i]);
+            ss += v[i].x * v[i].x;
+            ss += v[i].y * v[i].y;
+            ss += v[i].z * v[i].z;
+            ss += v[i].w * v[i].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x < C) {
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&slots[rank]);
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(ss) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float total = 0.f;
+    for (int k = 0; k < C; ++k) total += slots[k];
+    const float inv = rsqrtf(total / (float)d + eps);
+    TA* orow = out + (int64_t)r * d;
+#pragma unroll
+    for (int i = 0; i < CN_MAX_V; ++i) {
+        const int c = (int)rank * CN_THREADS + threadIdx.x + i * C * CN_THREADS;
+        if (c < nv) {
+            float4 o;
+            o.x = v[i].x * inv * (wv[i].x + weight_offset);
+            o.y = v[i].y * inv * (wv[i].y + weight_offset);
+            o.z = v[i].z * inv * (wv[i].z + weight_offset);
+            o.w = v[i].w * inv * (wv[i].w + weight_offset);
+            Vec4<TA>::store(orow + 4 * c, o);
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static cudaError_t launch_split_cluster(int C, int n_out_rows, cudaStream_t s, float* h, const void* w, void* out, const int* rows,
+                                        int d, float eps, float weight_offset, int write_h, const float* part,
+                                        int64_t split_stride, int n_splits) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(C, n_out_rows);
+    cfg.blockDim = dim3(CN_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = imp_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, add_rmsnorm_split_cluster_kernel<TA, TW>, h, (const TW*)w, (TA*)out, rows, d, eps,
+                              weight_offset, write_h, part, split_stride, n_splits);
+}
+
+// h += (sum of the n_splits partial results, rounded to the activation type); out = rmsnorm(h) * (w + offset).
+// part: [n_splits][n_rows_total, d] 32-bit, split_stride floats apart.  IMP_ERR_UNSUPPORTED for widths the
+// register-resident kernel does not take (the caller then sums first).
+IMP_API int imp_add_rmsnorm_split(float* h, const float* part, int64_t split_stride, int n_splits, const void* w, void* out,
+                                  const int* rows, int n_out_rows, int d, float eps, float weight_offset, int act_dtype,
+                                  int w_dtype, int write_h, void* stream) {
+    if (n_out_rows == 0) return 0;
+    IMP_CHECK_ARG(h && part && w && out && d > 0 && n_splits >= 1, "imp_add_rmsnorm_split: bad argument");
+    IMP_CHECK_ARG(!(rows && write_h), "imp_add_rmsnorm_split: write_h with a row list is not allowed");
+    if (!(d % 4 == 0 && d <= NORM_BLOCK * NORM_MAX_V4 * 4 && (uintptr_t)h % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+          (uintptr_t)out % 16 == 0 && (uintptr_t)part % 16 == 0 && split_stride % 4 == 0))
+        return IMP_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    static int use_cluster = -1;    // IMP_B200_NORM_CLUSTER=0: one CTA per row whatever the number of rows
+    if (use_cluster < 0) { const char* e = getenv("IMP_B200_NORM_CLUSTER"); use_cluster = e ? atoi(e) : 1; }
+    if (use_cluster && n_out_rows <= 128 && d >= 1024) {
+        // a row over several CTAs while the rows alone would leave most of the device idle
+        const int nv = d / 4;
+        int C = (nv + CN_THREADS - 1) / CN_THREADS;
+        if (C > CN_MAX_C) C = CN_MAX_C;
+        if (nv <= C * CN_THREADS * CN_MAX_V) {
+            cudaError_t e;
+            if (act_dtype == IMP_F32 && w_dtype == IMP_F32)
+                e = launch_split_cluster<float, float>(C, n_out_rows, s, h, w, out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits);
+            else if (act_dtype == IMP_F32)
+                e = launch_split_cluster<float, __nv_bfloat16>(C, n_out_rows, s, h, w, out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits);
+            else if (w_dtype == IMP_F32)
+                e = launch_split_cluster<__nv_bfloat16, float>(C, n_out_rows, s, h, w, out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits);
+            else
+                e = launch_split_cluster<__nv_bfloat16, __nv_bfloat16>(C, n_out_rows, s, h, w, out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits);
+            if (e != cudaSuccess) { imp_set_error("imp_add_rmsnorm_split: %s", cudaGetErrorString(e)); return (int)e; }
+            return 0;
+        }
+    }
+#define LAUNCH(TA, TW)                                                                                          \
+    imp_launch(add_rmsnorm_vec_kernel<TA, TW, true>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h, (const TA*)out, \
+               (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits)
     if (act_dtype == IMP_F32 && w_dtype == IMP_F32) LAUNCH(float, float);
     else if (act_dtype == IMP_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dtype == IMP_F32) LAUNCH(__nv_bfloat16, float);

@@ -48,6 +48,14 @@ class DecoderModel:
         self.head = build_part("head", plan.head, take(plan.head), rt)
 
         self.order: List[int] = plan.run_order()
+        # A block may hand on an unsummed branch only if whoever normalises the stream after it, at every place
+        # it has in the run order, adds the parts itself.
+        after_ok = {i: True for i in range(len(self.blocks))}
+        for j, i in enumerate(self.order):
+            nxt = self.blocks[self.order[j + 1]] if j + 1 < len(self.order) else self.final_norm
+            after_ok[i] = after_ok[i] and bool(nxt.takes_split_sum)
+        for i, blk in enumerate(self.blocks):
+            blk.defer_pending = after_ok[i]
         # Cache needs per run position, and which position's cache each position uses.
         self.cache_specs: List[Optional[object]] = []
         self.cache_position: List[int] = []

@@ -139,11 +139,66 @@ def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     return dst
 
 
-def add_rmsnorm(h: torch.Tensor, branch: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+DEFER_SPLIT_SUMS = _os.environ.get("IMP_B200_DEFER_SUM", "1") != "0"   # 0: always run the summing kernel
+
+
+class SplitSum:
+    """A matrix product whose contraction was cut over CTAs and whose parts have not been added yet.
+
+    `parts` [n_splits, M, N] float32 holds what each split contributes; the value is their sum in split order,
+    rounded to `out`'s type, and `out` [M, N] is where it belongs.  `linear(..., may_defer=True)` returns one
+    instead of a tensor when that saves the summing kernel; `add_rmsnorm` takes one and adds the parts while it
+    reads them.  Anyone else calls `summed()` first.  (The rotary kernel adding the parts of the q, k, v product
+    was tried too and measured slower than the summing kernel before it.)"""
+
+    __slots__ = ("out", "parts", "n_splits")
+
+    def __init__(self, out: torch.Tensor, parts: torch.Tensor, n_splits: int):
+        self.out, self.parts, self.n_splits = out, parts, n_splits
+
+    @property
+    def shape(self):
+        return self.out.shape
+
+    def summed(self) -> torch.Tensor:
+        """Add the parts into `out` (the separate summing kernel) and return it."""
+        M, N = self.out.shape
+        epi = TC_OUT_F32 if self.out.dtype == torch.float32 else TC_OUT_BF16
+        L.check(L.load().imp_gemm_bf16_tc_swap_sum(self.out.data_ptr(), self.out.stride(0), epi, self.parts.data_ptr(),
+                                                   M, N, self.n_splits, _stream()), "gemm_bf16_tc_swap_sum")
+        return self.out
+
+
+def summed(x):
+    """x itself, or the tensor a SplitSum stands for."""
+    return x.summed() if isinstance(x, SplitSum) else x
+
+
+def add_rmsnorm(h: torch.Tensor, branch, weight: torch.Tensor, out: torch.Tensor,
                 eps: float, weight_offset: float = 0.0, rows: Optional[torch.Tensor] = None,
                 write_h: bool = True) -> torch.Tensor:
     """h (+= branch); out = rmsnorm(h) * (weight + offset).  With `rows`, output row r reads stream row rows[r]
-    and h is left untouched."""
+    and h is left untouched.  `branch` may be a SplitSum: its parts are added on the way."""
+    if isinstance(branch, SplitSum):
+        sp = branch
+        _need_cuda(h, sp.parts, weight, out, rows)
+        d = h.shape[1]
+        assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous() and out.shape[1] == d
+        assert weight.numel() == d and weight.is_contiguous()
+        assert sp.out.shape == h.shape and sp.out.dtype == out.dtype and sp.parts.is_contiguous()
+        n_out = out.shape[0]
+        if rows is not None:
+            assert rows.dtype == torch.int32 and rows.numel() == n_out and rows.is_contiguous()
+            write_h = False
+        else:
+            assert n_out == h.shape[0]
+        rc = L.load().imp_add_rmsnorm_split(h.data_ptr(), sp.parts.data_ptr(), sp.parts.stride(0), sp.n_splits,
+                                            weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, d, float(eps),
+                                            float(weight_offset), _dt(out), _dt(weight), 1 if write_h else 0, _stream())
+        if rc != -2:
+            L.check(rc, "add_rmsnorm_split")
+            return out
+        branch = sp.summed()
     _need_cuda(h, branch, weight, out, rows)
     d = h.shape[1]
     assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous() and out.shape[1] == d
@@ -362,8 +417,33 @@ def gemm_bf16_tc_swap(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
     return True
 
 
-def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def gemm_bf16_tc_swap_partials(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor,
+                               status: Optional[torch.Tensor] = None) -> Optional[SplitSum]:
+    """a[M,K] @ w[N,K]^T left as the partial results of the K splits of the swap-AB tcgen05 kernel; None where
+    that kernel would not split this shape (or cannot take it)."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and a.dtype == w.dtype == torch.bfloat16 and M <= TC_SWAP_MAX_M and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    lib = L.load()
+    n_splits = lib.imp_gemm_bf16_tc_swap_splits(M, N, K)
+    if n_splits < 2:
+        return None
+    parts = torch.empty((n_splits, M, N), dtype=torch.float32, device=a.device)
+    rc = lib.imp_gemm_bf16_tc_swap_partials(parts.data_ptr(), a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0),
+                                            M, N, K, _ptr(status), _stream())
+    if rc == -2:
+        return None
+    L.check(rc, "gemm_bf16_tc_swap_partials")
+    return SplitSum(out, parts, n_splits)
+
+
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, may_defer: bool = False):
     """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
+
+    may_defer: the caller hands the result to add_rmsnorm (or calls summed() on it), so a
+    product the tcgen05 kernel splits over K may come back as a SplitSum, its summing kernel saved.
 
     float32 x float32 -> the plain FFMA kernel (never a reduced-precision mode).
     bfloat16 x bfloat16 -> the weight-streaming kernel for few rows, else the library GEMM.
@@ -385,17 +465,27 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         return out
     if x.dtype != torch.bfloat16:
         raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
+    defer = may_defer and DEFER_SPLIT_SUMS and out.is_contiguous()
     if M <= SMALL_M_MAX:
         # The weight-streaming kernel, except where the swap-AB tcgen05 kernel measured faster: from 8 rows up,
         # and at any row count for products with a long contraction and few output columns (K split over CTAs).
         N, Kd = w.shape
-        if (LARGE_M_BACKEND == "tcgen05" and (M > STREAM_M_MAX or (Kd >= 2 * N and N >= 1024))
-                and gemm_bf16_tc_swap(out, x, w)):
-            return out
+        if LARGE_M_BACKEND == "tcgen05" and (M > STREAM_M_MAX or (Kd >= 2 * N and N >= 1024)):
+            if defer:
+                sp = gemm_bf16_tc_swap_partials(out, x, w)
+                if sp is not None:
+                    return sp
+            if gemm_bf16_tc_swap(out, x, w):
+                return out
         return gemm_bf16_stream(out, x, w)
     if LARGE_M_BACKEND == "tcgen05":
-        if M <= TC_SWAP_MAX_M and gemm_bf16_tc_swap(out, x, w):
-            return out
+        if M <= TC_SWAP_MAX_M:
+            if defer:
+                sp = gemm_bf16_tc_swap_partials(out, x, w)
+                if sp is not None:
+                    return sp
+            if gemm_bf16_tc_swap(out, x, w):
+                return out
         if gemm_bf16_tc(out, x, w):
             return out
     if out.dtype == torch.bfloat16:

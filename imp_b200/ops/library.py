@@ -58,6 +58,12 @@ _SIGNATURES = {
     "imp_gemm_bf16_tc_swap": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
                                       c_void_p, c_void_p, c_void_p]),
     "imp_gemm_bf16_tc_swap_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
+    "imp_gemm_bf16_tc_swap_splits": (c_int, [c_int, c_int, c_int]),
+    "imp_gemm_bf16_tc_swap_partials": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
+                                               c_void_p, c_void_p]),
+    "imp_gemm_bf16_tc_swap_sum": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "imp_add_rmsnorm_split": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_float, c_float, c_int, c_int, c_int, c_void_p]),
     "imp_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "imp_argmax_scratch_words": (c_int, [c_int]),
     "imp_apply_penalties": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

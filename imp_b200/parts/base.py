@@ -23,6 +23,16 @@ Categories and what each must provide:
 
 Every part class also provides `tensor_specs(params)` (classmethod): the
 checkpoint tensors it needs, by local name, with shapes.
+
+Unsummed branch outputs.  A matrix product of few rows is cut over the
+contraction and leaves partial results that someone has to add
+(ops.kernels.SplitSum).  A norm that can add them while it reads the branch
+sets `takes_split_sum = True`; a mixer or feed-forward whose `defer_out` has
+been set to True by whoever arranges it may then return a SplitSum instead of
+a tensor.  Both default to False, so a part that knows nothing of this never
+meets one.  A block says through `takes_split_sum` whether the `pending` it is
+given may be one, and is told through `defer_pending` whether the `pending`
+it returns may be one.
 """
 from __future__ import annotations
 
@@ -54,6 +64,8 @@ class Runtime:
 
 class Part:
     category = "part"
+    takes_split_sum = False   # norm: add_norm accepts an unsummed branch
+    defer_out = False         # mixer, feed_forward: forward may return an unsummed branch
 
     def __init__(self, params: Dict[str, Any], tensors: Dict[str, torch.Tensor], rt: Runtime):
         self.params = params
@@ -141,6 +153,8 @@ class Block:
     """Arrangement of one layer.  Built from the layer's already built parts."""
 
     category = "block"
+    takes_split_sum = False   # the pending it is given may be an unsummed branch
+    defer_pending = False     # set by the model: the pending it returns may be an unsummed branch
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm, rt: Runtime):
         self.mixer = mixer

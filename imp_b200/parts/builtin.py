@@ -46,6 +46,8 @@ class RMSNorm(Norm):
     def tensor_specs(cls, params):
         return {"weight": TensorSpec((params["size"],), role="norm", init="one_plus_normal")}
 
+    takes_split_sum = True
+
     def __init__(self, params, tensors, rt):
         super().__init__(params, tensors, rt)
         self.weight = tensors["weight"]
@@ -153,7 +155,7 @@ class GQAAttention(Mixer):
                 attn = rt.empty((T, self.hq * self.dh))
                 self.attend(attn, q, ctx, cache)
                 out = rt.empty((T, self.w_o.shape[0]))
-                return K.linear(out, attn, self.w_o)
+                return K.linear(out, attn, self.w_o, may_defer=self.defer_out)
         qkv = rt.empty((T, (self.hq + 2 * self.hkv) * self.dh))
         K.linear(qkv, x, self.w_qkv)
         k_cache = cache.kv[0] if cache.writes else None
@@ -176,7 +178,7 @@ class GQAAttention(Mixer):
         attn = rt.empty((T, self.hq * self.dh))
         self.attend(attn, qkv[:, :self.hq * self.dh], ctx, cache)
         out = rt.empty((T, self.w_o.shape[0]))
-        return K.linear(out, attn, self.w_o)
+        return K.linear(out, attn, self.w_o, may_defer=self.defer_out)
 
     def attend(self, out, q, ctx, cache: LayerCache):
         """out[t] = softmax(scale * q[t] K^T) V over the cached positions token t may see."""
@@ -219,7 +221,7 @@ class SwiGLU(FeedForward):
             K.linear(gu, x, self.w_gu)
             K.swiglu(act, gu)
         out = rt.empty((T, self.w_down.shape[0]))
-        return K.linear(out, act, self.w_down)
+        return K.linear(out, act, self.w_down, may_defer=self.defer_out)
 
 
 # -------------------------------------------------------------------------- block
@@ -229,10 +231,21 @@ class PreNormBlock(Block):
     The second sum is handed on as `pending` and added by whoever normalises the stream
     next (the next block's first norm, or the final norm), in the same kernel."""
 
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, rt):
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, rt)
+        # the mixer's output goes to this block's second norm and nowhere else
+        if ffn_norm.takes_split_sum:
+            mixer.defer_out = True
+
+    @property
+    def takes_split_sum(self):
+        return self.mixer_norm.takes_split_sum
+
     def forward(self, h, pending, ctx, cache):
         x = self.mixer_norm.add_norm(h, pending)
         a = self.mixer.forward(x, ctx, cache)
         x = self.ffn_norm.add_norm(h, a)
+        self.feed_forward.defer_out = self.defer_pending
         f = self.feed_forward.forward(x, ctx)
         return h, f
 

@@ -211,8 +211,8 @@ def test_gemm_bf16_tcgen05(K, M, N, K_, odtype):
     assert not K.gemm_bf16_tc(out, odd[:, :K_], w, None, status)
 
 
-@pytest.mark.parametrize("M", [17, 33, 64, 65, 100, 128])
-@pytest.mark.parametrize("N,K_", [(128, 64), (130, 72), (1000, 4104), (4096, 1024), (200, 12288)])
+@pytest.mark.parametrize("M", [1, 8, 17, 32, 33, 64, 65, 100, 128])
+@pytest.mark.parametrize("N,K_", [(128, 64), (130, 72), (1000, 4104), (4096, 1024), (200, 12288), (260, 2560)])
 @pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
 def test_gemm_bf16_tcgen05_few_rows(K, M, N, K_, odtype):
     """Weights on the M side of the MMA, K split over CTAs: every edge case of rows, columns and K."""
@@ -916,3 +916,59 @@ def test_sample_large_vocabulary_short_list_and_general_passes(K, scale, filters
         assert keep[tok], f"token {tok} is outside the kept set of {filters}"
         lo, hi, _ = S.draw_interval(x, 0.8, tok, **filters)
         assert lo - 2e-5 <= u <= hi + 2e-5, f"u={u} does not select token {tok} (interval [{lo}, {hi}))"
+
+
+# ------------------------------------------------------------------ products left unsummed
+@pytest.mark.parametrize("M,N,K_", [(8, 4096, 4096), (1, 1024, 3072), (20, 200, 12288), (64, 1000, 4104)])
+def test_split_sum_summed_equals_the_plain_product(K, M, N, K_):
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=60).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=61).to(DEV)
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert K.gemm_bf16_tc_swap(want, a, w)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sp = K.gemm_bf16_tc_swap_partials(out, a, w)
+    assert sp is not None and sp.n_splits >= 2 and sp.parts.shape == (sp.n_splits, M, N)
+    assert torch.isnan(out.float()).all()                      # nothing summed yet
+    assert K.summed(sp) is out and torch.equal(out, want)
+    assert K.summed(out) is out
+
+
+@pytest.mark.parametrize("adtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [9, 40])
+@pytest.mark.parametrize("d,splits,use_rows", [(4096, 8, False), (200, 3, False), (1032, 2, True), (8200, 2, False),
+                                               (5120, 7, False), (8192, 4, True)])
+def test_add_rmsnorm_of_an_unsummed_branch(K, adtype, wdtype, d, splits, use_rows, T):
+    """h += round(sum of parts); out = rmsnorm(h): the stream gets the same bits as by summing first, the output
+    the same up to the order in which the squares are added (few rows: a row is shared by a cluster of CTAs).
+    d = 8200 is wider than the register-resident kernels take, so the wrapper sums first by itself."""
+    h0 = rnd(T, d, seed=62).to(DEV)
+    parts = rnd(splits, T, d, seed=63).to(DEV)
+    w = (1 + 0.1 * rnd(d, seed=64)).to(wdtype).to(DEV)
+    acc = torch.zeros(T, d, device=DEV)
+    for s in range(splits):
+        acc += parts[s]
+    branch = acc.to(adtype)
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32, device=DEV) if use_rows else None
+    n_out = 3 if use_rows else T
+    h_a, h_b = h0.clone(), h0.clone()
+    out_a = torch.empty(n_out, d, dtype=adtype, device=DEV)
+    out_b = torch.empty_like(out_a)
+    K.add_rmsnorm(h_a, branch, w, out_a, 1e-5, 0.0, rows=rows)
+    sp = K.SplitSum(torch.full((T, d), float("nan"), dtype=adtype, device=DEV), parts, splits)
+    K.add_rmsnorm(h_b, sp, w, out_b, 1e-5, 0.0, rows=rows)
+    assert torch.equal(h_a, h_b)
+    close(out_b, out_a.double().cpu(), adtype)
+    if use_rows:
+        assert torch.equal(h_b, h0)
+
+
+def test_linear_defers_only_when_asked_and_only_split_products(K):
+    a, w = rnd(8, 4096, dtype=torch.bfloat16, seed=68).to(DEV), rnd(4096, 4096, dtype=torch.bfloat16, seed=69).to(DEV)
+    out = torch.empty(8, 4096, dtype=torch.bfloat16, device=DEV)
+    assert K.linear(out, a, w) is out
+    got = K.linear(torch.empty_like(out), a, w, may_defer=True)
+    assert isinstance(got, K.SplitSum) and torch.equal(got.summed(), out)
+    big = rnd(32000, 4096, dtype=torch.bfloat16, seed=70).to(DEV)       # enough weight-row tiles: no split, a tensor
+    assert isinstance(K.linear(torch.empty(8, 32000, dtype=torch.bfloat16, device=DEV), a, big, may_defer=True), torch.Tensor)
+    a2 = a[:2]                                                          # two rows: the weight-streaming kernel
+    assert isinstance(K.linear(torch.empty(2, 4096, dtype=torch.bfloat16, device=DEV), a2, w, may_defer=True), torch.Tensor)
