@@ -192,13 +192,16 @@ def run_ours(args):
     cfgd = dict(MODEL)
     n_layers = args.layers or MODEL["num_hidden_layers"]
     cfgd["num_hidden_layers"] = n_layers
+    if args.only == "decode" and args.context > cfgd["max_position_embeddings"]:
+        cfgd["max_position_embeddings"] = args.context
     mc = config_from_dict(cfgd)
     torch.cuda.set_device(0)
     B = args.batch
     maxB = max(B, 64) if not args.only else B
     _, _, kv_per_tok = model_numbers(cfgd, n_layers)
-    ecfg = EngineConfig(max_batch_size=maxB, max_seq_len=CONTEXT, kv_block_size=PAGE,
-                        kv_cache_tokens=maxB * CONTEXT + 4 * CONTEXT, max_batch_tokens=PREFILL_TOKENS,
+    max_ctx = max(CONTEXT, args.context) if args.only == "decode" else CONTEXT
+    ecfg = EngineConfig(max_batch_size=maxB, max_seq_len=max_ctx, kv_block_size=args.page or PAGE,
+                        kv_cache_tokens=maxB * max_ctx + 4 * CONTEXT, max_batch_tokens=PREFILL_TOKENS,
                         compute_dtype="bfloat16", enable_cuda_graphs=not args.no_graphs)
     t0 = time.time()
     eng = Engine.from_random(mc, ecfg, seed=0, std=0.02)
@@ -210,7 +213,7 @@ def run_ours(args):
 
     gen = torch.Generator().manual_seed(0)
     if args.only == "decode":
-        ctx = min(max(args.context or CONTEXT, args.steps + args.warmup + 1), CONTEXT)
+        ctx = max(args.context or CONTEXT, args.steps + args.warmup + 1)
         ms, calls = time_decode(eng, B, ctx, args.steps, args.warmup, torch, K, StepEntry)
         print(json.dumps({"only": "decode", "batch": B, "layers": n_layers, "context": ctx, "ms_per_step": round(ms, 4),
                           "launcher_calls_per_step": calls}))
@@ -297,7 +300,7 @@ def run_ours(args):
                    "hidden": cfgd["hidden_size"], "q_heads": cfgd["num_attention_heads"],
                    "kv_heads": cfgd["num_key_value_heads"], "head_dim": cfgd["head_dim"],
                    "intermediate": cfgd["intermediate_size"], "vocab": cfgd["vocab_size"],
-                   "global_batch": B, "seq_len": CONTEXT, "page_size": PAGE, "weights": "random N(0,0.02) seed 0",
+                   "global_batch": B, "seq_len": CONTEXT, "page_size": args.page or PAGE, "weights": "random N(0,0.02) seed 0",
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (16 GB of weights per step)",
                    "cache_fill": "random pages for value/points, real prefill for e2e",
                    "peaks": peak_src},
@@ -336,7 +339,8 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--context", type=int, default=0,
-                    help="with --only decode: the contexts end here instead of at the configured length")
+                    help="with --only decode: the contexts end here instead of at the configured length (may be longer)")
+    ap.add_argument("--page", type=int, default=0, help="tokens per cache page (0 = the default of the engine's configuration)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":

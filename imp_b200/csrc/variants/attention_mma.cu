@@ -697,13 +697,21 @@ IMP_API int64_t imp_attn_decode_scratch_floats(int n_tokens, int Hq, int n_split
 // ------------------------------------------------------------------ decode, bulk-copy ring
 // The same split-key decode for page sizes that are multiples of 16: the 16 keys of a step then lie
 // in one page, 16 consecutive rows of a kv head = one contiguous run of 32*DH bytes for keys and one
-// for values.  A fifth warp's lane 0 is the producer: per stage of 64 keys it issues up to eight
-// cp.async.bulk copies (global -> shared, completion counted in bytes on the stage's mbarrier) into
-// a three-deep ring; the four consumer warps each take one 16-key step of the stage from shared
-// memory and hand the stage back through a second mbarrier.  A CTA so keeps two stages (up to
-// 64 x DH x 4 bytes each) in flight without holding them in registers.  Every wait is bounded
-// (IMP_WAIT_TIMEOUT in the status word, then the CTA drains and leaves).
-constexpr int DT_KEYS = 64, DT_STAGES = 3, DT_CONSUMERS = 4;
+// for values.  A fifth warp is the producer: per stage of 64 keys its lanes 0..7 issue one cp.async.bulk
+// copy each (global -> shared, completion counted in bytes on the stage's mbarrier; keys and values of
+// the four steps, fewer and larger copies where 2 or 4 steps share a page) into a three-deep ring; the
+// page ids come from one coalesced read of the block table per eight stages, one id a lane.  The four
+// consumer warps each take one 16-key step of the stage from shared memory and hand the stage back
+// through a second mbarrier.  A CTA so keeps two stages (up to 64 x DH x 4 bytes each) in flight without
+// holding them in registers.  Measured: the copies of a stage issued by one thread, and that thread
+// reading the block table stage by stage, held a CTA to about 19 GB/s whatever the ring's depth (4.7-5.0
+// TB/s for the device at two CTAs per SM); issued side by side the same ring reaches 6.1-6.7 TB/s.  Copies
+// cost per piece, not per byte: 32 copies of 1 KB a stage were as slow as the single thread.  Every wait
+// is bounded (IMP_WAIT_TIMEOUT in the status word, then the CTA drains and leaves).
+#ifndef IMP_DT_STAGES
+#define IMP_DT_STAGES 3
+#endif
+constexpr int DT_KEYS = 64, DT_STAGES = IMP_DT_STAGES, DT_CONSUMERS = 4;
 constexpr int DT_RUN_BYTES = 16 * DH * 2;                 // keys (or values) of one step
 constexpr int DT_STAGE_BYTES = 2 * DT_CONSUMERS * DT_RUN_BYTES;
 constexpr uint32_t DT_WAIT_LIMIT = 1u << 20;
@@ -876,55 +884,69 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
 
     if (warp == DT_CONSUMERS) {
         // ---------------------------------------------------------------------- producer
+        // The whole warp runs the loop: every lane keeps the page id of one 16-key step (32 steps = 8 stages,
+        // one coalesced read of the block table), lane 0 waits for the slot, lanes 0..7 issue.
+        constexpr int STAGES_PER_FILL = 32 / DT_CONSUMERS;
+        static_assert(DT_CONSUMERS == 4, "the grouping of steps into copies assumes four steps a stage");
+        // steps of a stage that one copy may cover: the 64 keys of a stage start at a multiple of 64
+        const int run_steps = P % 64 == 0 ? 4 : (P % 32 == 0 ? 2 : 1);
         bool ok = true;
         int issued = 0;
+        int page_reg = -1, fill_base = -(1 << 30);
         auto issue_stage = [&](int s) {
-            const int it = s - stage_lo, slot = it % DT_STAGES;
-            const int j_stage = first_al + DT_KEYS * s;
-            uint32_t bytes = 0;
-            int64_t off[DT_CONSUMERS];
-#pragma unroll
-            for (int w = 0; w < DT_CONSUMERS; ++w) {
-                const int j0 = j_stage + 16 * w;
-                off[w] = -1;
-                if (j0 > pos || j0 + 15 < first) continue;          // every key of the step is masked: not fetched
-                const int lp = j0 / P;
-                const int page = bt[lp];
-                if (page < 0 || page >= num_pages) { imp_report(status, IMP_BAD_PAGE); continue; }
-                off[w] = (((int64_t)page * Hkv + hk) * P + (j0 - lp * P)) * DH;
-                bytes += 2 * DT_RUN_BYTES;
+            if (s < fill_base || s >= fill_base + STAGES_PER_FILL) {
+                const int j0 = first_al + DT_KEYS * s + 16 * lane;
+                page_reg = (j0 <= pos && j0 + 15 >= first) ? bt[j0 / P] : -1;    // pos / P < bt_stride was checked above
+                fill_base = s;
             }
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * slot), "r"(bytes) : "memory");
-            const uint32_t sbase = ring + slot * DT_STAGE_BYTES;
+            // Lane kind * C + step requests the keys (kind 0) or values (kind 1) of one step, so that a stage's copies
+            // go out together: one thread issuing them one after the other held a CTA to about 20 GB/s.  Where the page
+            // size allows, 2 or 4 steps that lie in one page travel as one copy (copies cost per piece, not per byte).
+            const int it = s - stage_lo, slot = it % DT_STAGES;
+            const int w = lane % DT_CONSUMERS;
+            const int j0 = first_al + DT_KEYS * s + 16 * w;
+            const int page = __shfl_sync(0xffffffffu, page_reg, (s - fill_base) * DT_CONSUMERS + w);
+            const bool wanted = j0 <= pos && j0 + 15 >= first;          // else every key of the step is masked: not fetched
+            const bool good = wanted && page >= 0 && page < num_pages;
+            if (wanted && !good && lane < DT_CONSUMERS) imp_report(status, IMP_BAD_PAGE);
+            const uint32_t steps = __ballot_sync(0xffffffffu, good) & ((1u << DT_CONSUMERS) - 1u);
+            // the steps of this lane's group (run_steps consecutive steps in one page) that are fetched
+            const uint32_t group = (steps >> (w & ~(run_steps - 1))) & ((1u << run_steps) - 1u);
+            const int lead = __ffs(group) - 1;                          // first fetched step of the group
+            const int n_run = 32 - __clz(group) - lead;                 // up to its last one (the steps between come along)
+            uint32_t bytes = 0;
+            if (lane < 2 * DT_CONSUMERS && group && (w & (run_steps - 1)) == lead) bytes = (uint32_t)n_run * DT_RUN_BYTES;
+            uint32_t total = bytes;
 #pragma unroll
-            for (int w = 0; w < DT_CONSUMERS; ++w) {
-                if (off[w] < 0) continue;
+            for (int o = 1; o < 2 * DT_CONSUMERS; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * slot), "r"(total) : "memory");
+            __syncwarp();
+            if (bytes) {
+                const bool is_v = lane >= DT_CONSUMERS;
+                const int64_t off = (((int64_t)page * Hkv + hk) * P + (j0 % P)) * DH;
+                const uint32_t dst = ring + slot * DT_STAGE_BYTES + ((is_v ? DT_CONSUMERS : 0) + w) * DT_RUN_BYTES;
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(sbase + w * DT_RUN_BYTES), "l"(kc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(sbase + (DT_CONSUMERS + w) * DT_RUN_BYTES), "l"(vc + off[w]), "r"(DT_RUN_BYTES), "r"(full0 + 8 * slot) : "memory");
+                             ::"r"(dst), "l"((is_v ? vc : kc) + off), "r"(bytes), "r"(full0 + 8 * slot) : "memory");
             }
             issued = it + 1;
         };
-        if (lane == 0) {
-            // stages that end before this step's own position hold keys of earlier steps only
-            for (int s = stage_lo; s < stage_hi && s - stage_lo < DT_STAGES; ++s) {
-                if (first_al + DT_KEYS * s + DT_KEYS - 1 >= pos) break;
-                issue_stage(s);
-            }
+        // stages that end before this step's own position hold keys of earlier steps only
+        for (int s = stage_lo; s < stage_hi && s - stage_lo < DT_STAGES; ++s) {
+            if (first_al + DT_KEYS * s + DT_KEYS - 1 >= pos) break;
+            issue_stage(s);
         }
         pdl_wait();
-        if (lane == 0) {
-            for (int s = stage_lo + issued; s < stage_hi && ok; ++s) {
-                const int it = s - stage_lo, slot = it % DT_STAGES;
-                ok = dt_wait(empty0 + 8 * slot, ((uint32_t)(it / DT_STAGES) & 1u) ^ 1u, status);
-                if (!ok) break;
-                issue_stage(s);
-            }
-            if (!ok) {   // a bounded chance for the copies in flight to land before the memory is released
-                for (int it = issued > DT_STAGES ? issued - DT_STAGES : 0; it < issued; ++it)
-                    dt_wait(full0 + 8 * (it % DT_STAGES), (uint32_t)(it / DT_STAGES) & 1u, nullptr);
-            }
+        for (int s = stage_lo + issued; s < stage_hi; ++s) {
+            const int it = s - stage_lo, slot = it % DT_STAGES;
+            if (lane == 0) ok = dt_wait(empty0 + 8 * slot, ((uint32_t)(it / DT_STAGES) & 1u) ^ 1u, status);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) break;
+            issue_stage(s);
+        }
+        if (!ok && lane == 0) {   // a bounded chance for the copies in flight to land before the memory is released
+            for (int it = issued > DT_STAGES ? issued - DT_STAGES : 0; it < issued; ++it)
+                dt_wait(full0 + 8 * (it % DT_STAGES), (uint32_t)(it / DT_STAGES) & 1u, nullptr);
         }
     } else {
         // -------------------------------------------------------------------- consumers
@@ -946,11 +968,13 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
             const bool ok = __all_sync(0xffffffffu, dt_wait(full0 + 8 * slot, (uint32_t)(it / DT_STAGES) & 1u, status));
             if (!ok) break;
             const int j0 = first_al + DT_KEYS * s + 16 * warp;
+#ifndef IMP_DT_SKIP_COMPUTE
             if (j0 <= pos && j0 + 15 >= first) {
                 const unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
                 dec_compute_smem<NR>(st, qa, rows, sb + warp * DT_RUN_BYTES, sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES, j0,
                                      scale_log2, lane);
             }
+#endif
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * slot) : "memory");
         }

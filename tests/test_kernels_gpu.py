@@ -447,7 +447,8 @@ def test_attention_mma_every_head_size(K, Dh):
 
 
 @pytest.mark.parametrize("Hq,Hkv,page,window", [(4, 4, 16, 0), (5, 1, 4, 0), (12, 3, 1, 0), (40, 2, 16, 0), (8, 2, 8, 19),
-                                                (3, 3, 64, 100), (4, 1, 3, 16)])
+                                                (3, 3, 64, 100), (4, 1, 3, 16), (4, 2, 32, 0), (6, 2, 32, 45), (4, 1, 48, 0),
+                                                (8, 2, 128, 70), (2, 2, 64, 0), (4, 4, 96, 33)])
 def test_attention_mma_groups_pages_windows(K, Hq, Hkv, page, window):
     from imp_b200.ops import attention as A
     Dh = 64
