@@ -968,13 +968,11 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
             const bool ok = __all_sync(0xffffffffu, dt_wait(full0 + 8 * slot, (uint32_t)(it / DT_STAGES) & 1u, status));
             if (!ok) break;
             const int j0 = first_al + DT_KEYS * s + 16 * warp;
-#ifndef IMP_DT_SKIP_COMPUTE
             if (j0 <= pos && j0 + 15 >= first) {
                 const unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
                 dec_compute_smem<NR>(st, qa, rows, sb + warp * DT_RUN_BYTES, sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES, j0,
                                      scale_log2, lane);
             }
-#endif
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * slot) : "memory");
         }
