@@ -126,8 +126,11 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 1
     depend on the context length); short contexts simply leave the later splits empty.
 
     The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with
-    fewer (token, kv head) pairs than such slots the keys are split until the slots are full; with
-    more, the smallest split count whose CTAs fill whole waves of slots to 95% is taken."""
+    fewer (token, kv head) pairs than such slots the keys are split until the slots are full.  With
+    more, the split count with the least modelled time is taken.  The model (fitted to measurements at
+    40 to 128 sequences): a CTA alone streams about 1/150 of what the device can, so a wave of CTAs
+    runs at full speed from 150 CTAs up, and a last wave of fewer runs as slowly as each of its CTAs;
+    splitting costs the merge kernel and the partial results, about a tenth of one CTA's work."""
     base = n_tokens * n_kv_heads * ((group + 15) // 16)
     if page_size % 16:
         return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_CTAS // max(base, 1)))
@@ -137,15 +140,15 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 1
         # sequences, 8 beat 9 at four, although the latter fill more slots)
         s = max(1, min(DECODE_MAX_SPLITS, slots // base))
         return 1 << (s.bit_length() - 1)
-    best, best_eff = 1, 0.0
-    for s in range(1, 9):
+    saturating = 150.0
+
+    def modelled_time(s: int) -> float:
         ctas = base * s
-        eff = ctas / (-(-ctas // slots) * slots)
-        if eff >= 0.95:
-            return s
-        if eff > best_eff + 1e-9:
-            best, best_eff = s, eff
-    return best
+        full, tail = divmod(ctas, slots)
+        t = full * slots / saturating + (tail / min(saturating, tail) if tail else 0.0)
+        return t / s + (0.1 + 0.01 * s if s > 1 else 0.0)
+
+    return min(range(1, 9), key=modelled_time)
 
 
 def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,

@@ -1,0 +1,27 @@
+"""Key splits of the decode attention: chosen from the batch alone, within bounds, and as measured."""
+from imp_b200.ops.attention import DECODE_MAX_SPLITS, decode_splits
+
+
+def test_splits_fill_the_device_for_small_batches_and_stop_for_large_ones():
+    slots = 2 * 148
+    for batch in range(1, 300):
+        s = decode_splits(batch, 8, 4, 16)
+        assert 1 <= s <= DECODE_MAX_SPLITS
+        base = batch * 8
+        if base <= slots:
+            assert base * s <= slots and s & (s - 1) == 0           # resident at once, a power of two
+            assert base * s * 2 > slots or s == DECODE_MAX_SPLITS   # and no further doubling would fit
+    # measured at 8 kv heads of 128, context 4096: 64 sequences unsplit beat 4 splits, 40 and 48 do not
+    assert decode_splits(64, 8, 4, 16) == 1
+    assert decode_splits(32, 8, 4, 16) == 1
+    assert decode_splits(40, 8, 4, 16) > 1 and decode_splits(48, 8, 4, 16) > 1
+    assert decode_splits(8, 8, 4, 16) == 4 and decode_splits(1, 8, 4, 16) == 32
+
+
+def test_groups_above_sixteen_count_as_several_row_tiles():
+    assert decode_splits(4, 2, 40, 16) == decode_splits(4, 6, 4, 16)
+
+
+def test_other_page_sizes_use_the_direct_kernel_rule():
+    assert decode_splits(1, 8, 4, 3) >= 1
+    assert decode_splits(1000, 8, 4, 3) == 1
