@@ -660,7 +660,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w,
                                                               const __grid_constant__ CUtensorMap map_x, void* __restrict__ Cv,
                                                               int64_t ldc, int64_t split_stride, int M, int N, int K,
-                                                              int kb_per_split, int* status) {
+                                                              int kb_per_split, int tile_rows, int* status) {
     constexpr int TCS_STAGES = tcs_stages<BN>();
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -668,7 +668,10 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TCS_STAGES * STAGE);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TCS_STAGES + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * 128;
+    // A CTA owns tile_rows (<= 128, a multiple of 16) weight rows: map_w's box has that many rows, the MMA still
+    // spans 128 and works on whatever the stage holds beyond them; those accumulator lanes are never stored.
+    const int n0 = blockIdx.x * tile_rows;
+    const uint32_t stage_tx = (uint32_t)(tile_rows + BN) * (TC_BK * 2);   // bytes the two boxes of a stage bring
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_lo = blockIdx.z * kb_per_split;
     const int kb_hi = min(total_kb, kb_lo + kb_per_split);
@@ -702,7 +705,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         // the weights of the first stages do not depend on the kernel before this one
         const int early = k_blocks < TCS_STAGES ? k_blocks : TCS_STAGES;
         for (int i = 0; i < early; ++i) {
-            mbar_expect_tx(full0 + 8 * i, STAGE);
+            mbar_expect_tx(full0 + 8 * i, stage_tx);
             tma_load_2d(smem_u32(tiles + i * STAGE), &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * i);
         }
         pdl_wait();
@@ -714,7 +717,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
             ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status);
             if (!ok) break;
             const uint32_t w_dst = smem_u32(tiles + s * STAGE), x_dst = w_dst + TCS_W_BYTES;
-            mbar_expect_tx(full0 + 8 * s, STAGE);
+            mbar_expect_tx(full0 + 8 * s, stage_tx);
             tma_load_2d(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * s);
             tma_load_2d(x_dst, &map_x, (kb_lo + i) * TC_BK, 0, full0 + 8 * s);
             issued = i + 1;
@@ -767,10 +770,10 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
                 for (int i = 0; i < 32; ++i) {
                     const float up = __shfl_xor_sync(0xffffffffu, v[i], 8);   // lane r + 8 holds the matching up row
                     const int tok = c * 32 + i;
-                    if (is_gate && tok < M && col + 8 < N)
+                    if (is_gate && tok < M && col + 8 < N && r < tile_rows)
                         base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
                 }
-            } else if (col < N) {
+            } else if (col < N && r < tile_rows) {
                 if (EPI == TC_OUT_F32) {
                     float* base = reinterpret_cast<float*>(Cv) + (int64_t)blockIdx.z * split_stride;
 #pragma unroll
@@ -905,16 +908,45 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
 
 // ---- few rows (16 < M <= 128) -----------------------------------------------------------------------
 // Number of K splits imp_gemm_bf16_tc_swap will use, and the floats of scratch it then needs.
-static int tcs_splits(int M, int N, int K, int epilogue) {
-    if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
+#ifndef TCS_MIN_KB_PER_SPLIT
+#define TCS_MIN_KB_PER_SPLIT 6     // blocks of K a split has at least
+#endif
+static int tcs_sms() {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         sms = 148;
+    return sms;
+}
+
+// Weight rows of a CTA's tile when K is not split.  All CTAs are resident at once (two per SM up to 64 tokens),
+// handed out round robin, so the SM with the most CTAs sets the time: 192 tiles of 128 rows put two tiles on 44 SMs
+// and one on the others (256 rows at most per SM), 256 tiles of 96 rows put 192 at most.  Smaller tiles are
+// taken while they lower that maximum; more CTAs than slots are left alone (several waves even out by themselves).
+static int tcs_tile_rows(int M, int N, int splits) {
+    static int fixed = -1;             // IMP_B200_TCS_ROWS=128 (or another multiple of 16): no choice
+    if (fixed < 0) { const char* e = getenv("IMP_B200_TCS_ROWS"); fixed = e ? atoi(e) : 0; }
+    if (fixed >= 16 && fixed <= 128 && fixed % 16 == 0) return fixed;
+    if (splits > 1) return 128;
+    const int sms = tcs_sms();
+    const int slots = M <= 64 ? 2 * sms : sms;
+    int best = 128, best_load = -1;
+    for (int rows = 128; rows >= 64; rows -= 16) {
+        const int ctas = (N + rows - 1) / rows;
+        if (ctas > slots) { if (rows == 128) return 128; break; }
+        const int load = ((ctas + sms - 1) / sms) * rows;     // rows the busiest SM streams
+        if (best_load < 0 || load < best_load) { best = rows; best_load = load; }
+    }
+    return best;
+}
+
+static int tcs_splits(int M, int N, int K, int epilogue) {
+    if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
+    const int sms = tcs_sms();
     const int slots = M <= 64 ? 2 * sms : sms;          // resident CTAs: two per SM with 64-column tiles
     const int tiles = (N + 127) / 128;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int splits = slots / tiles;                          // as many CTAs as fit in one wave
-    const int max_splits = total_kb / 8 > 0 ? total_kb / 8 : 1;   // at least 8 blocks of K per split
+    const int max_splits = total_kb / TCS_MIN_KB_PER_SPLIT > 0 ? total_kb / TCS_MIN_KB_PER_SPLIT : 1;
     if (splits > max_splits) splits = max_splits;
     if (splits > 16) splits = 16;
     return splits < 1 ? 1 : splits;
@@ -927,7 +959,7 @@ IMP_API int64_t imp_gemm_bf16_tc_swap_scratch_floats(int M, int N, int K, int ep
 
 template <int BN, int EPI>
 static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensorMap& mw, const CUtensorMap& mx, int M, int N,
-                      int K, int splits, int kb_per_split, int* status, cudaStream_t s) {
+                      int K, int splits, int kb_per_split, int tile_rows, int* status, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -935,9 +967,9 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
         if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
-    dim3 grid((N + 127) / 128, 1, splits);
+    dim3 grid((N + tile_rows - 1) / tile_rows, 1, splits);
     cudaError_t e = imp_launch(gemm_tc_swap_kernel<BN, EPI>, grid, dim3(128), (size_t)tcs_smem_bytes<BN>(), s, mw, mx, C, ldc,
-                               split_stride, M, N, K, kb_per_split, status);
+                               split_stride, M, N, K, kb_per_split, tile_rows, status);
     if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -960,16 +992,17 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
     static int bn32 = -1;                     // IMP_B200_TCS_BN32=0 keeps 64 columns for up to 32 rows (measurements)
     if (bn32 < 0) { const char* e = getenv("IMP_B200_TCS_BN32"); bn32 = e ? atoi(e) : 1; }
     const int BN = (M <= 32 && bn32) ? 32 : (M <= 64 ? 64 : 128);
+    const int tile_rows = tcs_tile_rows(M, N, splits);
     CUtensorMap mw, mx;
-    if (int rc = make_map(&mw, W, N, K, ldw, 128)) return rc;
+    if (int rc = make_map(&mw, W, N, K, ldw, tile_rows)) return rc;
     if (int rc = make_map(&mx, A, M, K, lda, BN)) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = 0;
     if (splits > 1) {
         const int64_t split_stride = (int64_t)M * N;
-        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
-           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s)
-                      : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, status, s);
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
+                      : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s);
         if (rc) return rc;
         if (partials_only) IMP_RETURN_LAUNCH();
         const int64_t total = (int64_t)M * N;
@@ -983,17 +1016,17 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
                            (const float*)scratch, split_stride, M, N, splits);
         if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     } else if (epilogue == TC_OUT_BF16) {
-        rc = BN == 32 ? launch_tcs<32, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-           : BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-                      : launch_tcs<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                      : launch_tcs<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s);
     } else if (epilogue == TC_OUT_F32) {
-        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-                      : launch_tcs<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                      : launch_tcs<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s);
     } else {
-        rc = BN == 32 ? launch_tcs<32, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-           : BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s)
-                      : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, status, s);
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+           : BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                      : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s);
     }
     if (rc) return rc;
     IMP_RETURN_LAUNCH();
