@@ -634,10 +634,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
 }
 
 // ------------------------------------------------------- few rows: weights on the M side
-// For 16 < M <= 128 activation rows the product is turned round, as in the decode kernel of
-// gemm_stream.cu: 128 weight rows are the M side of the MMA (one accumulator lane per weight row),
-// the activation rows its N side (BN = 64 or 128 columns of tensor memory).  A CTA streams its 128
-// weight rows through a six-deep TMA ring; with few weight-row tiles the K range is cut into
+// For up to 128 activation rows the product is turned round, as in the decode kernel of
+// gemm_stream.cu: up to 128 weight rows are the M side of the MMA (one accumulator lane per weight row),
+// the activation rows its N side (BN = 32, 64 or 128 columns of tensor memory).  A CTA streams its
+// weight rows through a TMA ring; with few weight-row tiles the K range is cut into
 // `splits` parts (grid.z) so that every SM pulls on the memory, each part writing a 32-bit partial
 // result that gemm_tc_reduce_kernel adds up in split order.
 // Epilogue: lane r of the accumulator is output column n0 + r, column t is token t, so consecutive
@@ -906,7 +906,7 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
     return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
 }
 
-// ---- few rows (16 < M <= 128) -----------------------------------------------------------------------
+// ---- few rows (M <= 128) ----------------------------------------------------------------------------
 // Number of K splits imp_gemm_bf16_tc_swap will use, and the floats of scratch it then needs.
 #ifndef TCS_MIN_KB_PER_SPLIT
 #define TCS_MIN_KB_PER_SPLIT 6     // blocks of K a split has at least

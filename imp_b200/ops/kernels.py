@@ -16,18 +16,18 @@ from . import library as L
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
-# Matrix products with more rows than SMALL_M_MAX: "tcgen05" = this library's TMA + tcgen05 kernel
-# (csrc/gemm_tc.cu), "cublas" = the library GEMM through torch.mm (what the reference's engine calls
-# for its T>1 products).  IMP_B200_GEMM overrides the default.
+# bfloat16 matrix products beyond the weight-streaming kernel's rows: "tcgen05" = this library's TMA + tcgen05
+# kernels (csrc/gemm_tc.cu), "cublas" = the library GEMM through torch.mm (what the reference's engine calls for
+# its T>1 products, src/compute/gemm.cu:303-445; kept as a yardstick).  IMP_B200_GEMM overrides the default.
 import os as _os
 
 LARGE_M_BACKEND = _os.environ.get("IMP_B200_GEMM", "tcgen05")
 if LARGE_M_BACKEND not in ("tcgen05", "cublas"):
     raise ValueError(f"IMP_B200_GEMM must be 'tcgen05' or 'cublas', got {LARGE_M_BACKEND!r}")
 
-# Rows up to which the weight-streaming kernel is used for bfloat16 products; above it the
-# library GEMM (cuBLAS through torch.mm) runs, as the reference does for its T>1 products
-# (src/compute/gemm.cu:303-445).
+# Which kernel takes a bfloat16 product, by its rows (see linear): the weight-streaming kernel (csrc/gemm_stream.cu)
+# up to STREAM_M_MAX, the tcgen05 kernels above; with IMP_B200_GEMM=cublas the streaming kernel up to SMALL_M_MAX
+# and the library above.
 SMALL_M_MAX = 16        # most rows the weight-streaming kernel takes
 STREAM_M_MAX = 7         # rows up to which it is the first choice (measured: from 8 rows the tcgen05 swap-AB kernel wins)
 
@@ -446,7 +446,9 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, may_defer: bool 
     product the tcgen05 kernel splits over K may come back as a SplitSum, its summing kernel saved.
 
     float32 x float32 -> the plain FFMA kernel (never a reduced-precision mode).
-    bfloat16 x bfloat16 -> the weight-streaming kernel for few rows, else the library GEMM.
+    bfloat16 x bfloat16 -> by rows: the weight-streaming kernel (up to 7), the swap-AB tcgen05 kernel (up to 128, and
+    long contractions at any row count), the persistent tcgen05 kernel (up to 255), CTA pairs (more); shapes the TMA
+    descriptors cannot take, and IMP_B200_GEMM=cublas, go to the small-M kernel or the library GEMM.
     bfloat16 x float32 weight (a tensor the checkpoint stores in 32-bit) -> x is widened, FFMA kernel.
     `out` may be bfloat16 or float32.
     """
