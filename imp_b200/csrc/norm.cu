@@ -47,7 +47,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
 }
 
 // Fast path for rows of up to 8192 floats whose width is a multiple of 4: the row is read once
-// with 16-byte loads issued together, kept in registers, and written from there.  The per-thread
+// with 16-byte loads issued together, kept in registers (NV float4 a thread: 1, 2, 4 or 8, the least that
+// holds the row, so that narrow rows leave room for more blocks on an SM), and written from there.  The per-thread
 // partial sums and the block reduction add in an order fixed by the width alone.
 constexpr int NORM_MAX_V4 = 8;   // float4 per thread: 256 threads x 8 x 4 = 8192 columns
 
@@ -75,7 +76,7 @@ template <> struct Vec4<__nv_bfloat16> {
 // SPLIT: the branch has not been summed yet.  `part` holds n_splits 32-bit partial results [n_rows_total, d] of a
 // product whose contraction was cut over CTAs, split_stride floats apart; the branch value is their sum in split
 // order rounded to TA, bit for bit what the summing kernel would have stored.
-template <typename TA, typename TW, bool SPLIT>
+template <typename TA, typename TW, bool SPLIT, int NV>
 __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch,
                                                                      const TW* __restrict__ w, TA* __restrict__ out,
                                                                      const int* __restrict__ rows, int d, float eps,
@@ -90,19 +91,16 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
     float* hrow = h + src * d;
     const TA* brow = (SPLIT || branch) ? branch + src * d : nullptr;   // with SPLIT only its null-ness is used
     const int nv = d >> 2;
-    float4 v[NORM_MAX_V4], wv[NORM_MAX_V4];
+    float4 v[NV];
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_V4; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * NORM_BLOCK;
-        if (c < nv) {
-            v[i] = Vec4<float>::load(hrow + 4 * c);
-            wv[i] = Vec4<TW>::load(w + 4 * c);
-        }
+        if (c < nv) v[i] = Vec4<float>::load(hrow + 4 * c);
     }
     if (SPLIT) {
         const float* prow = part + src * d;
 #pragma unroll
-        for (int i = 0; i < NORM_MAX_V4; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int c = threadIdx.x + i * NORM_BLOCK;
             if (c < nv) {
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -118,7 +116,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
         }
     } else if (brow) {
 #pragma unroll
-        for (int i = 0; i < NORM_MAX_V4; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int c = threadIdx.x + i * NORM_BLOCK;
             if (c < nv) {
                 const float4 b = Vec4<TA>::load(brow + 4 * c);
@@ -128,7 +126,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
     }
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_V4; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * NORM_BLOCK;
         if (c < nv) {
             if (write_h && brow) Vec4<float>::store(hrow + 4 * c, v[i]);
@@ -142,14 +140,15 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
     const float inv = rsqrtf(ss / (float)d + eps);
     TA* orow = out + (int64_t)r * d;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_V4; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * NORM_BLOCK;
         if (c < nv) {
+            const float4 wv = Vec4<TW>::load(w + 4 * c);     // the weight row stays in the caches: read when used
             float4 o;
-            o.x = v[i].x * inv * (wv[i].x + weight_offset);
-            o.y = v[i].y * inv * (wv[i].y + weight_offset);
-            o.z = v[i].z * inv * (wv[i].z + weight_offset);
-            o.w = v[i].w * inv * (wv[i].w + weight_offset);
+            o.x = v[i].x * inv * (wv.x + weight_offset);
+            o.y = v[i].y * inv * (wv.y + weight_offset);
+            o.z = v[i].z * inv * (wv.z + weight_offset);
+            o.w = v[i].w * inv * (wv.w + weight_offset);
             Vec4<TA>::store(orow + 4 * c, o);
         }
     }
@@ -164,12 +163,28 @@ IMP_API int imp_add_rmsnorm(float* h, const void* branch, const void* w, void* o
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = d % 4 == 0 && d <= NORM_BLOCK * NORM_MAX_V4 * 4 && (uintptr_t)h % 16 == 0 &&
                      (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 && (!branch || (uintptr_t)branch % 16 == 0);
+// the vector kernel with the fewest float4 a thread that hold a row of d floats
+#define VEC_BY_WIDTH(TA, TW, SPLIT, BRANCH, PART, STRIDE, NSPLITS)                                               \
+    do {                                                                                                         \
+        const int per_thread = (d / 4 + NORM_BLOCK - 1) / NORM_BLOCK;                                            \
+        if (per_thread <= 1)                                                                                     \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW, SPLIT, 1>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,    \
+                       BRANCH, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, PART, STRIDE, NSPLITS); \
+        else if (per_thread <= 2)                                                                                \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW, SPLIT, 2>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,    \
+                       BRANCH, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, PART, STRIDE, NSPLITS); \
+        else if (per_thread <= 4)                                                                                \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW, SPLIT, 4>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,    \
+                       BRANCH, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, PART, STRIDE, NSPLITS); \
+        else                                                                                                     \
+            imp_launch(add_rmsnorm_vec_kernel<TA, TW, SPLIT, 8>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h,    \
+                       BRANCH, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, PART, STRIDE, NSPLITS); \
+    } while (0)
+
 #define LAUNCH(TA, TW)                                                                                     \
     do {                                                                                                   \
         if (vec)                                                                                           \
-            imp_launch(add_rmsnorm_vec_kernel<TA, TW, false>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h, \
-                       (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h,    \
-                       (const float*)nullptr, (int64_t)0, 0);                                              \
+            VEC_BY_WIDTH(TA, TW, false, (const TA*)branch, (const float*)nullptr, (int64_t)0, 0);          \
         else                                                                                               \
             add_rmsnorm_kernel<TA, TW><<<n_out_rows, NORM_BLOCK, 0, s>>>(                                  \
                 h, (const TA*)branch, (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h);       \
@@ -323,9 +338,7 @@ IMP_API int imp_add_rmsnorm_split(float* h, const float* part, int64_t split_str
             return 0;
         }
     }
-#define LAUNCH(TA, TW)                                                                                          \
-    imp_launch(add_rmsnorm_vec_kernel<TA, TW, true>, dim3(n_out_rows), dim3(NORM_BLOCK), 0, s, h, (const TA*)out, \
-               (const TW*)w, (TA*)out, rows, d, eps, weight_offset, write_h, part, split_stride, n_splits)
+#define LAUNCH(TA, TW) VEC_BY_WIDTH(TA, TW, true, (const TA*)out, part, split_stride, n_splits)
     if (act_dtype == IMP_F32 && w_dtype == IMP_F32) LAUNCH(float, float);
     else if (act_dtype == IMP_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dtype == IMP_F32) LAUNCH(__nv_bfloat16, float);
