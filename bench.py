@@ -219,13 +219,16 @@ def run_ours(args):
                           "launcher_calls_per_step": calls}))
         return 0
     # ---- prefill: one prompt of 2,048 tokens in one step --------------------------------------------
-    prompt = torch.randint(0, mc.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+    n_prompt = PREFILL_TOKENS
+    if args.only == "prefill" and 0 < args.tokens <= PREFILL_TOKENS:
+        n_prompt = args.tokens
+    prompt = torch.randint(0, mc.vocab_size, (n_prompt,), generator=gen).tolist()
     pf_ms = []
-    for i in range(1 + 3):
+    for i in range(1 + 7):      # one warm-up, seven timed: the products run at the power cap and vary by a few per cent
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        eng.stepper.step([StepEntry("pf", prompt, [PREFILL_TOKENS - 1])])
+        eng.stepper.step([StepEntry("pf", prompt, [n_prompt - 1])])
         e1.record()
         torch.cuda.synchronize()
         eng.stepper.finish("pf")
@@ -234,7 +237,7 @@ def run_ours(args):
     eng.stepper.check_device_status("prefill bench")
     pf = statistics.median(pf_ms)
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PREFILL_TOKENS, "ms": round(pf, 3)}))
+        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": n_prompt, "ms": round(pf, 3)}))
         return 0
     pf_flops = prefill_flops(cfgd, n_layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pf * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
@@ -340,6 +343,7 @@ def main():
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--context", type=int, default=0,
                     help="with --only decode: the contexts end here instead of at the configured length (may be longer)")
+    ap.add_argument("--tokens", type=int, default=0, help="with --only prefill: tokens of the prompt (at most 2048)")
     ap.add_argument("--page", type=int, default=0, help="tokens per cache page (0 = the default of the engine's configuration)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = ap.parse_args()

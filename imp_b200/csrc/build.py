@@ -178,7 +178,11 @@ def variant_hash(source: str, defines: dict) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + LINK_FLAGS).encode())
     h.update(repr(sorted(defines.items())).encode())
-    for path in [os.path.join(VARIANT_DIR, source)] + [os.path.join(CSRC_DIR, f) for f in headers()]:
+    # everything that goes into the image: the source, runtime.cu (compiled in), and every header beside them
+    variant_headers = sorted(f for f in os.listdir(VARIANT_DIR) if f.endswith((".cuh", ".h")))
+    paths = ([os.path.join(VARIANT_DIR, source), os.path.join(CSRC_DIR, "runtime.cu")] +
+             [os.path.join(CSRC_DIR, f) for f in headers()] + [os.path.join(VARIANT_DIR, f) for f in variant_headers])
+    for path in paths:
         with open(path, "rb") as fh:
             h.update(fh.read())
     return h.hexdigest()[:16]

@@ -506,8 +506,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status,
                         const __grid_constant__ QkvRopeArgs qkv) {
-    pdl_wait();
-    pdl_launch_dependents();
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * TC2_STAGE_BYTES);
@@ -544,6 +542,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     cluster_sync_all();        // the partner's barriers are initialised before anything can arrive on them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Up to here nothing read or wrote what an earlier kernel of the stream may still be working on.
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -870,15 +871,20 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
     if (mode == 0 && pair_mode == 1 && M >= 256) {
         const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
         const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
-        gemm_tc_pair_kernel<EPI><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, s>>>(ma, mw128, C, ldc, M, N, K, status, QkvRopeArgs{});
-        IMP_RETURN_LAUNCH();
+        cudaError_t e = imp_launch(gemm_tc_pair_kernel<EPI>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES, s, ma, mw128,
+                                   C, ldc, M, N, K, status, QkvRopeArgs{});
+        if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
+        return 0;
     }
     const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
     if (mode == 1) {
         gemm_tc_kernel<EPI><<<dim3(num_m, num_n), 128, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
     } else {
         const int total = num_m * num_n;
-        gemm_tc_persistent_kernel<EPI><<<total < sms ? total : sms, TCP_THREADS, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
+        cudaError_t e = imp_launch(gemm_tc_persistent_kernel<EPI>, dim3(total < sms ? total : sms), dim3(TCP_THREADS),
+                                   (size_t)TC_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, status);
+        if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
+        return 0;
     }
     IMP_RETURN_LAUNCH();
 }
@@ -1116,7 +1122,8 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     a.Hq = Hq; a.Hkv = Hkv; a.Dh = Dh; a.page_size = page_size; a.num_pages = num_pages;
     const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
     const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
-    gemm_tc_pair_kernel<TC_OUT_QKV_ROPE><<<2 * pairs, TCP_THREADS, TC2_SMEM_BYTES, (cudaStream_t)stream>>>(
-        ma, mw128, nullptr, 0, M, N, K, status, a);
-    IMP_RETURN_LAUNCH();
+    cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
+                               (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a);
+    if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
 }
