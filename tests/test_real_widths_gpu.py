@@ -109,3 +109,88 @@ def test_float32_at_real_widths_is_exact_under_cutting(wide):
     cut = run(eng, small, [[("b", 70), ("c", 2)], [("b", 69), ("c", 30)], [("b", 1), ("c", 1)]])
     for r in small:
         assert np.array_equal(whole[r].numpy(), cut[r].numpy()), f"request {r}: logits depend on the cut"
+
+
+def test_a_norm_that_knows_nothing_of_unsummed_branches_gets_tensors(wide, tmp_path, monkeypatch):
+    """Products of few rows leave their K-split partial sums to the norm that reads them next, but only to a norm
+    that says it takes them.  Here the second norm of layer 1 and the final norm are a norm defined in this test
+    (the same formula, in torch): it must be handed plain tensors, the built-in norms around it still get unsummed
+    branches, and the logits are those of the built-in model (the random weights depend on seed and tensor name
+    only)."""
+    from dataclasses import dataclass
+
+    from imp_b200 import Engine, EngineConfig, StepEntry, register_architecture, register_part, write_model_folder
+    from imp_b200.architectures.qwen3 import qwen3_plan
+    from imp_b200.config.model_config import Qwen3Config
+    from imp_b200.config.registry import config_from_dict, unregister_architecture
+    from imp_b200.ops import kernels as K
+    from imp_b200.parts.base import Norm
+    from imp_b200.parts.plan import PartSpec, TensorSpec
+    from imp_b200.parts.registry import unregister_part
+
+    seen = {"toy": 0, "unsummed": 0}
+
+    class TorchRMSNorm(Norm):
+        @classmethod
+        def tensor_specs(cls, params):
+            return {"weight": TensorSpec((params["size"],), role="norm", init="one_plus_normal")}
+
+        def add_norm(self, h, branch, rows=None):
+            assert branch is None or isinstance(branch, torch.Tensor), type(branch)
+            seen["toy"] += 1
+            v = h if branch is None else h + branch.float()
+            if rows is None:
+                if branch is not None:
+                    h.copy_(v)
+            else:
+                v = v[rows.long()]
+            y = v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + self.params["eps"]) * self.tensors["weight"].float()
+            return y.to(branch.dtype if branch is not None else torch.bfloat16)
+
+    @dataclass
+    class ToyNormConfig(Qwen3Config):
+        pass
+
+    def plan_with_toy_norms(cfg):
+        plan = qwen3_plan(cfg)
+        last = plan.layers[-1]
+        last.ffn_norm = PartSpec("torch_rms", last.ffn_norm.params, last.ffn_norm.tensors)
+        plan.final_norm = PartSpec("torch_rms", plan.final_norm.params, plan.final_norm.tensors)
+        return plan
+
+    real_add_rmsnorm = K.add_rmsnorm
+
+    def counting_add_rmsnorm(h, branch, *args, **kwargs):
+        seen["unsummed"] += isinstance(branch, K.SplitSum)
+        return real_add_rmsnorm(h, branch, *args, **kwargs)
+
+    register_part("norm", "torch_rms", TorchRMSNorm)
+    register_architecture("ToyNormForCausalLM", ToyNormConfig, plan_with_toy_norms)
+    try:
+        folder = str(tmp_path / "toy_norm")
+        write_model_folder(folder, config_from_dict(dict(WIDE, architectures=["ToyNormForCausalLM"])), seed=3, std=0.02)
+        monkeypatch.setattr(K, "add_rmsnorm", counting_add_rmsnorm)
+        eng = Engine.from_folder(folder, EngineConfig(compute_dtype="bfloat16", kv_block_size=16, max_batch_size=24,
+                                                      max_seq_len=512, kv_cache_tokens=24 * 512, max_batch_tokens=640,
+                                                      enable_cuda_graphs=False))
+        blocks = eng.model.blocks
+        assert [b.mixer.defer_out for b in blocks] == [True, False]
+        assert [b.defer_pending for b in blocks] == [True, False]
+        _, ids, ref = wide
+        c = ids["c"]
+        many = [f"c{i}" for i in range(20)]
+        eng.step_tokens([StepEntry(r, c[:30], []) for r in many[:10]])
+        eng.step_tokens([StepEntry(r, c[:30], []) for r in many[10:]])
+        seen["toy"] = seen["unsummed"] = 0
+        for t in range(30, 33):
+            lg = eng.step_tokens([StepEntry(r, [c[t]], [0]) for r in many])
+            want = ref["c"][t]
+            scale = float(want.abs().max())
+            assert ((lg - want[None]).abs() <= 0.03 * scale + 0.03 * want.abs()[None]).all(), f"position {t}"
+        # three steps: the own norm ran twice a step, and the two built-in norms before it got unsummed branches
+        assert seen["toy"] == 6 and seen["unsummed"] == 6
+        for r in many:
+            eng.end(r)
+    finally:
+        unregister_architecture("ToyNormForCausalLM")
+        unregister_part("norm", "torch_rms")
