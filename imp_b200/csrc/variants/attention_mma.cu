@@ -831,13 +831,128 @@ __device__ __forceinline__ void dec_compute_smem(DecState<NR>& st, const uint32_
     }
 }
 
+// The decode step straight from the projection: with `qkv` set, q is read raw from the fused q|k|v rows
+// (q heads first, then k heads, then v heads) and normalised and rotated here, and the CTA whose keys include
+// the token's own position does the same for the new key, writes key and value into their page and into its
+// own copy of the page in shared memory (the producer fetched that row as it was).  This is the work of the
+// rotary kernel (csrc/rope_kv.cu, same formulas and roundings), saved as a launch.  Head sizes that are
+// multiples of 64, rotated over their whole width: a lane then holds both elements of every rotary pair.
+struct DecFused {
+    const __nv_bfloat16* qkv;      // null: q is ready and the pages hold this step's key and value
+    int64_t stride;                // elements between rows of qkv
+    const float* q_norm_w;         // [DH] or null
+    const float* k_norm_w;
+    const float* cos_tab;          // [max_pos, DH / 2]
+    const float* sin_tab;
+    __nv_bfloat16* k_pages;        // the caches again, to write
+    __nv_bfloat16* v_pages;
+    float eps;
+    int max_pos;
+};
+
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+
+// Query fragments (see load_row_frags for which dimensions a lane holds): per-head RMSNorm, then rotation of the
+// pairs (d, d + DH/2).  k-step ks < KSTEPS/2 holds d = 32 (ks / 2) + 8 t + 4 (ks % 2) + {0,1} and {2,3}; its
+// partner is k-step ks + KSTEPS/2.  The four lanes t of a row share the sum of squares.
+template <int NR>
+__device__ __forceinline__ void dec_q_norm_rope(uint32_t (&qa)[KSTEPS][4], const DecFused& fz, int pos, int t) {
+    constexpr int HALF = DH / 2, HK = KSTEPS / 2;
+    const float* cs = fz.cos_tab + (int64_t)pos * HALF;
+    const float* sn = fz.sin_tab + (int64_t)pos * HALF;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        float ss = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float2 v = unpack_bf16(qa[ks][2 * j + r]);
+                ss += v.x * v.x + v.y * v.y;
+            }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        const float inv = fz.q_norm_w ? rsqrtf(ss / (float)DH + fz.eps) : 1.f;
+#pragma unroll
+        for (int ks = 0; ks < HK; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int d = 32 * (ks >> 1) + 8 * t + 4 * (ks & 1) + 2 * j;
+                float2 a = unpack_bf16(qa[ks][2 * j + r]), b = unpack_bf16(qa[ks + HK][2 * j + r]);
+                a.x *= inv; a.y *= inv; b.x *= inv; b.y *= inv;
+                if (fz.q_norm_w) {
+                    a.x *= fz.q_norm_w[d]; a.y *= fz.q_norm_w[d + 1];
+                    b.x *= fz.q_norm_w[d + HALF]; b.y *= fz.q_norm_w[d + 1 + HALF];
+                }
+                const float2 c = *reinterpret_cast<const float2*>(cs + d), sv = *reinterpret_cast<const float2*>(sn + d);
+                qa[ks][2 * j + r] = pack_bf16(a.x * c.x - b.x * sv.x, a.y * c.y - b.y * sv.y);
+                qa[ks + HK][2 * j + r] = pack_bf16(a.x * sv.x + b.x * c.x, a.y * sv.y + b.y * c.y);
+            }
+    }
+}
+
+// The token's own key and value: k normalised and rotated, both written to row `pos` of their page and to the
+// rows `ksm_row` / `vsm_row` of this warp's copy of the page in shared memory.  One warp; lane l holds the pairs
+// (2l, 2l+1) of both rotary halves (and the next 64 dimensions for head sizes above 128), as the rotary kernel does.
+__device__ __forceinline__ void dec_write_own_key(const DecFused& fz, const __nv_bfloat16* __restrict__ kraw,
+                                                  const __nv_bfloat16* __restrict__ vraw, int64_t page_row_off, int pos,
+                                                  unsigned char* ksm_row, unsigned char* vsm_row, int lane) {
+    constexpr int HALF = DH / 2;
+    const float* cs = fz.cos_tab + (int64_t)pos * HALF;
+    const float* sn = fz.sin_tab + (int64_t)pos * HALF;
+    float2 a[2], b[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int j = lane + 32 * r;
+        a[r] = b[r] = make_float2(0.f, 0.f);
+        if (2 * j < HALF) {
+            a[r] = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(kraw)[j]);
+            b[r] = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(kraw + HALF)[j]);
+            ss += a[r].x * a[r].x + a[r].y * a[r].y + b[r].x * b[r].x + b[r].y * b[r].y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = fz.k_norm_w ? rsqrtf(ss / (float)DH + fz.eps) : 1.f;
+    __nv_bfloat16* kdst = fz.k_pages + page_row_off;
+    __nv_bfloat16* vdst = fz.v_pages + page_row_off;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int j = lane + 32 * r;
+        if (2 * j >= HALF) continue;
+        float2 av = make_float2(a[r].x * inv, a[r].y * inv), bv = make_float2(b[r].x * inv, b[r].y * inv);
+        if (fz.k_norm_w) {
+            av.x *= fz.k_norm_w[2 * j]; av.y *= fz.k_norm_w[2 * j + 1];
+            bv.x *= fz.k_norm_w[2 * j + HALF]; bv.y *= fz.k_norm_w[2 * j + 1 + HALF];
+        }
+        const float2 c = *reinterpret_cast<const float2*>(cs + 2 * j), sv = *reinterpret_cast<const float2*>(sn + 2 * j);
+        const uint32_t lo = pack_bf16(av.x * c.x - bv.x * sv.x, av.y * c.y - bv.y * sv.y);
+        const uint32_t hi = pack_bf16(av.x * sv.x + bv.x * c.x, av.y * sv.y + bv.y * c.y);
+        reinterpret_cast<uint32_t*>(ksm_row)[j] = lo;
+        reinterpret_cast<uint32_t*>(ksm_row + HALF * 2)[j] = hi;
+        reinterpret_cast<uint32_t*>(kdst)[j] = lo;
+        reinterpret_cast<uint32_t*>(kdst + HALF)[j] = hi;
+    }
+    for (int i = lane * 4; i < DH; i += 128) {
+        const uint2 v = *reinterpret_cast<const uint2*>(vraw + i);
+        *reinterpret_cast<uint2*>(vsm_row + 2 * i) = v;
+        *reinterpret_cast<uint2*>(vdst + i) = v;
+    }
+    // the slot is refilled by a bulk copy later: order these ordinary stores before it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+}
+
 template <int NR>
 __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kernel(
     __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
     int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int* status) {
+    float* __restrict__ part_ml, int* status, const DecFused fz) {
     // pdl_wait() comes later: the batch arrays and the keys before this step's position do not depend on the
     // kernel before this one, so the first stages are requested while it still runs.
     extern __shared__ __align__(128) unsigned char dt_smem[];
@@ -852,7 +967,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     const int tok = blockIdx.z;
     const int seq = seq_of_token[tok];
     const int pos = positions[tok];
-    if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride) {
+    if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride || (fz.qkv && pos >= fz.max_pos)) {
         if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
         return;
     }
@@ -963,11 +1078,28 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         }
         uint32_t qa[KSTEPS][4];
         load_q(qa, qrow[0], qrow[1], t4);
+        if constexpr (DH % 64 == 0) {
+            if (fz.qkv) dec_q_norm_rope<NR>(qa, fz, pos, t4);
+        }
         for (int s = stage_lo; s < stage_hi; ++s) {
             const int it = s - stage_lo, slot = it % DT_STAGES;
             const bool ok = __all_sync(0xffffffffu, dt_wait(full0 + 8 * slot, (uint32_t)(it / DT_STAGES) & 1u, status));
             if (!ok) break;
             const int j0 = first_al + DT_KEYS * s + 16 * warp;
+            if constexpr (DH % 64 == 0) {
+                if (fz.qkv && pos >= j0 && pos < j0 + 16) {
+                    // this warp's 16 keys include the token's own: its key and value are made here
+                    const int page = bt[pos / P];
+                    if (page >= 0 && page < num_pages) {     // else the producer has reported it already
+                        unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
+                        const __nv_bfloat16* kraw = fz.qkv + (int64_t)tok * fz.stride + (int64_t)(Hq + hk) * DH;
+                        dec_write_own_key(fz, kraw, kraw + (int64_t)Hkv * DH,
+                                          (((int64_t)page * Hkv + hk) * P + (pos % P)) * DH, pos,
+                                          sb + warp * DT_RUN_BYTES + (pos - j0) * DH * 2,
+                                          sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES + (pos - j0) * DH * 2, lane);
+                    }
+                }
+            }
             if (j0 <= pos && j0 + 15 >= first) {
                 const unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
                 dec_compute_smem<NR>(st, qa, rows, sb + warp * DT_RUN_BYTES, sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES, j0,
@@ -1052,7 +1184,7 @@ template <int NR>
 static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_stride, const void* q, int64_t q_stride,
                              const void* kc, const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                              const int* positions, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2,
-                             int window, int n_splits, float* part_o, float* part_ml, int* status) {
+                             int window, int n_splits, float* part_o, float* part_ml, int* status, const DecFused& fz) {
     constexpr int MERGE = (DT_CONSUMERS - 1) * (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);
     constexpr int SMEM = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
     static bool attr_set = false;
@@ -1064,7 +1196,7 @@ static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_s
     cudaError_t e = imp_launch(attn_decode_tma_kernel<NR>, grid, dim3((DT_CONSUMERS + 1) * 32), (size_t)SMEM, s,
                                (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                                (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P,
-                               num_pages, scale_log2, window, n_splits, part_o, part_ml, status);
+                               num_pages, scale_log2, window, n_splits, part_o, part_ml, status, fz);
     if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1089,10 +1221,11 @@ static int launch_decode(dim3 grid, cudaStream_t s, void* out, int64_t out_strid
     return 0;
 }
 
-IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+static int attn_decode_impl(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
                             const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                             const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages,
-                            float scale, int window, int n_splits, float* scratch, int* status, void* stream) {
+                            float scale, int window, int n_splits, float* scratch, int* status, void* stream,
+                            const DecFused& fz) {
     if (n_tokens == 0) return 0;
     if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
     IMP_CHECK_ARG(seq_of_token && positions, "imp_attn_decode: null pointer");
@@ -1108,8 +1241,9 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, Hkv * tiles_per_group, n_tokens);
     const bool bulk = P % 16 == 0 && getenv("IMP_B200_ATTN_DIRECT") == nullptr;   // whole 16-key steps per page
+    if (fz.qkv && !(bulk && DH % 64 == 0)) return IMP_ERR_UNSUPPORTED;               // only the bulk-copy kernel does that
 #define DEC_ARGS grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, \
-                 Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml, status
+                 Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml, status, fz
     if (bulk) {
         if (int rc = (G <= 8) ? launch_decode_tma<1>(DEC_ARGS) : launch_decode_tma<2>(DEC_ARGS)) return rc;
     } else if (G <= 8) {
@@ -1129,6 +1263,36 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
                    (const float*)part_o, (const float*)part_ml, Hq, n_splits);
     }
     IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+                            const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                            const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages,
+                            float scale, int window, int n_splits, float* scratch, int* status, void* stream) {
+    return attn_decode_impl(out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_tokens,
+                            n_seqs, Hq, Hkv, P, num_pages, scale, window, n_splits, scratch, status, stream, DecFused{});
+}
+
+// The decode step from the projection's raw rows: qkv [n_tokens, qkv_stride] holds q heads, k heads, v heads of
+// every token as the q,k,v product left them.  q and k are normalised per head (weights [DH] in 32-bit, or null)
+// and rotated over the whole head (cos/sin [max_pos, DH/2]) inside the attention kernel, which also writes the new
+// key and value into their pages; the rotary kernel is not run for such a step.  IMP_ERR_UNSUPPORTED (and nothing
+// done) for head sizes that are no multiple of 64 and page sizes that are no multiple of 16.
+IMP_API int imp_attn_decode_fused(void* out, int64_t out_stride, const void* qkv, int64_t qkv_stride, void* kc, void* vc,
+                                  const int* block_table, int bt_stride, const int* seq_of_token, const int* positions,
+                                  int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale, int window,
+                                  int n_splits, float* scratch, const float* q_norm_w, const float* k_norm_w, float eps,
+                                  const float* cos_tab, const float* sin_tab, int max_pos, int* status, void* stream) {
+    IMP_CHECK_ARG(qkv && cos_tab && sin_tab && max_pos > 0, "imp_attn_decode_fused: null pointer");
+    IMP_CHECK_ARG((q_norm_w == nullptr) == (k_norm_w == nullptr), "imp_attn_decode_fused: q and k norm weights must both be set or both be null");
+    IMP_CHECK_ARG(qkv_stride >= (int64_t)(Hq + 2 * Hkv) * DH && qkv_stride % 8 == 0, "imp_attn_decode_fused: bad row stride");
+    IMP_CHECK_ARG((uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0, "imp_attn_decode_fused: unaligned tables");
+    DecFused fz;
+    fz.qkv = (const __nv_bfloat16*)qkv; fz.stride = qkv_stride; fz.q_norm_w = q_norm_w; fz.k_norm_w = k_norm_w;
+    fz.cos_tab = cos_tab; fz.sin_tab = sin_tab; fz.k_pages = (__nv_bfloat16*)kc; fz.v_pages = (__nv_bfloat16*)vc;
+    fz.eps = eps; fz.max_pos = max_pos;
+    return attn_decode_impl(out, out_stride, qkv, qkv_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_tokens,
+                            n_seqs, Hq, Hkv, P, num_pages, scale, window, n_splits, scratch, status, stream, fz);
 }
 
 // ================================================================================= prefill

@@ -51,6 +51,11 @@ def variant(head_dim: int) -> ctypes.CDLL:
         lib.imp_attn_decode.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                         c_int, c_void_p, c_void_p, c_void_p]
+        lib.imp_attn_decode_fused.restype = c_int
+        lib.imp_attn_decode_fused.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                              c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_void_p]
         lib.imp_attn_prefill.restype = c_int
         lib.imp_attn_prefill.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -172,6 +177,47 @@ def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, 
         None if scratch is None else scratch.data_ptr(), None if status is None else status.data_ptr(),
         torch.cuda.current_stream().cuda_stream), "attention decode")
     return out
+
+
+DECODE_FUSED = os.environ.get("IMP_B200_ATTN_FUSED", "1") != "0"   # 0: the rotary kernel runs before every decode attention
+
+
+def decode_attention_fused(out, qkv, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token,
+                           positions, scale, window, q_norm_w, k_norm_w, eps, cos, sin, status, n_splits=None) -> bool:
+    """The decode step from the raw rows of the q,k,v product (bfloat16, q heads | k heads | v heads): per-head norm
+    (32-bit weights or None) and rotation of q and of the new key happen inside the attention kernel, which writes
+    the new key and value into their pages.  Returns False, with nothing done, where that kernel does not apply
+    (head sizes that are no multiple of 64, page sizes that are no multiple of 16, IMP_B200_ATTN_FUSED=0)."""
+    if not DECODE_FUSED or head_dim % 64 or k_cache.shape[2] % 16:
+        return False
+    lib = variant(head_dim)
+    T = qkv.shape[0]
+    num_pages, hk, page_size, dh = k_cache.shape
+    assert hk == n_kv_heads and dh == head_dim and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert qkv.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert qkv.shape[1] >= (n_q_heads + 2 * n_kv_heads) * head_dim
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape
+    assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] * 2 == head_dim
+    if q_norm_w is not None:
+        assert q_norm_w.dtype == torch.float32 and k_norm_w.dtype == torch.float32
+        assert q_norm_w.numel() == head_dim and k_norm_w.numel() == head_dim
+    if n_splits is None:
+        n_splits = decode_splits(T, n_kv_heads, n_q_heads // n_kv_heads, page_size)
+    scratch = None
+    n_floats = lib.imp_attn_decode_scratch_floats(T, n_q_heads, n_splits)
+    if n_floats:
+        scratch = torch.empty(n_floats, dtype=torch.float32, device=qkv.device)
+    rc = lib.imp_attn_decode_fused(
+        out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
+        block_table.shape[0], n_q_heads, n_kv_heads, page_size, num_pages, float(scale), int(window), n_splits,
+        None if scratch is None else scratch.data_ptr(), None if q_norm_w is None else q_norm_w.data_ptr(),
+        None if k_norm_w is None else k_norm_w.data_ptr(), float(eps), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+        None if status is None else status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if rc == -2:
+        return False
+    _check(lib, rc, "attention decode (fused)")
+    return True
 
 
 def prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,

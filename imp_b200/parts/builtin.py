@@ -158,6 +158,16 @@ class GQAAttention(Mixer):
                 return K.linear(out, attn, self.w_o, may_defer=self.defer_out)
         qkv = rt.empty((T, (self.hq + 2 * self.hkv) * self.dh))
         K.linear(qkv, x, self.w_qkv)
+        if tables is not None and cache.writes and not rt.is_float32 and tables[2] == self.dh and ctx.decode_only:
+            # decode steps: the attention kernel normalises and rotates q and the new key itself and writes the new
+            # key and value into their pages (no rotary kernel)
+            from ..ops import attention as A
+            attn = rt.empty((T, self.hq * self.dh))
+            if A.decode_attention_fused(attn, qkv, self.hq, self.hkv, self.dh, cache.kv[0], cache.kv[1], cache.block_table,
+                                        ctx.seq_of_token, ctx.positions, self.scale, self.window, self.q_norm_f32,
+                                        self.k_norm_f32, self.norm_eps, tables[0], tables[1], rt.status):
+                out = rt.empty((T, self.w_o.shape[0]))
+                return K.linear(out, attn, self.w_o, may_defer=self.defer_out)
         k_cache = cache.kv[0] if cache.writes else None
         v_cache = cache.kv[1] if cache.writes else None
         if self.position is not None and tables is None:

@@ -973,3 +973,54 @@ def test_linear_defers_only_when_asked_and_only_split_products(K):
     assert isinstance(K.linear(torch.empty(8, 32000, dtype=torch.bfloat16, device=DEV), a, big, may_defer=True), torch.Tensor)
     a2 = a[:2]                                                          # two rows: the weight-streaming kernel
     assert isinstance(K.linear(torch.empty(2, 4096, dtype=torch.bfloat16, device=DEV), a2, w, may_defer=True), torch.Tensor)
+
+
+# ------------------------------------------------------------------ decode attention from the raw q,k,v rows
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window,with_norm", [(8, 2, 128, 16, 0, True), (4, 4, 64, 16, 0, True),
+                                                             (12, 1, 64, 32, 0, False), (2, 1, 256, 16, 0, True),
+                                                             (6, 3, 128, 64, 40, True), (3, 1, 192, 48, 0, True)])
+def test_decode_attention_from_raw_qkv_equals_rotary_kernel_then_attention(K, Hq, Hkv, Dh, page, window, with_norm):
+    """One kernel does what two do: q and the new key are normalised and rotated inside the decode attention, the
+    new key and value land in their pages (the same bits as the rotary kernel writes; lengths put the new key at a
+    page's first row, its last row, inside a 16-key step, and at position 0), outputs agree to bfloat16 rounding."""
+    from imp_b200.ops import attention as A
+    lengths = [page * 3 + 1, page * 2, 70, 1, 300]
+    B = len(lengths)
+    bt, num_pages = paged_layout(lengths, page, seed=9)
+    N = (Hq + 2 * Hkv) * Dh
+    kc0 = 0.5 * rnd(num_pages, Hkv, page, Dh, dtype=torch.bfloat16, seed=90)     # history (and stale rows) everywhere
+    vc0 = 0.5 * rnd(num_pages, Hkv, page, Dh, dtype=torch.bfloat16, seed=91)
+    qkv = rnd(B, N, dtype=torch.bfloat16, seed=92).to(DEV)
+    qw = (1 + 0.2 * rnd(Dh, seed=93)).to(DEV) if with_norm else None
+    kw = (1 + 0.2 * rnd(Dh, seed=94)).to(DEV) if with_norm else None
+    max_pos = 512
+    i = torch.arange(Dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-2.0 * i / Dh))[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    btd = bt.to(DEV)
+    status = K.new_status(DEV)
+    for splits in (1, 3, None):
+        # two kernels
+        kc_a, vc_a, qkv_a = kc0.to(DEV).clone(), vc0.to(DEV).clone(), qkv.clone()
+        K.qk_norm_rope_kv_write(qkv_a, Hq, Hkv, Dh, qw, kw, 1e-6, cos, sin, Dh, pos, seq, btd, kc_a, vc_a, status)
+        out_a = torch.full((B, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        A.decode_attention(out_a, qkv_a[:, :Hq * Dh], Hq, Hkv, Dh, kc_a, vc_a, btd, seq, pos, 1 / math.sqrt(Dh), window, status,
+                           n_splits=splits)
+        # one kernel
+        kc_b, vc_b = kc0.to(DEV).clone(), vc0.to(DEV).clone()
+        out_b = torch.full((B, Hq * Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert A.decode_attention_fused(out_b, qkv, Hq, Hkv, Dh, kc_b, vc_b, btd, seq, pos, 1 / math.sqrt(Dh), window,
+                                        qw, kw, 1e-6, cos, sin, status, n_splits=splits)
+        K.check_status(status)
+        assert torch.equal(vc_a, vc_b)
+        assert (kc_a != kc_b).float().mean() < 1e-3                    # the sum of squares adds in another order
+        close(kc_b, kc_a.double().cpu(), torch.bfloat16)
+        close(out_b, out_a.double().cpu(), torch.bfloat16)
+    # head sizes and page sizes the one-kernel path does not take are declined, nothing written
+    kc_c = torch.zeros(4, 1, 8, 64, dtype=torch.bfloat16, device=DEV)
+    assert not A.decode_attention_fused(torch.empty(1, 64, dtype=torch.bfloat16, device=DEV),
+                                        torch.zeros(1, 192, dtype=torch.bfloat16, device=DEV), 1, 1, 64, kc_c, kc_c.clone(),
+                                        torch.zeros(1, 4, dtype=torch.int32, device=DEV), seq[:1], pos[:1], 0.125, 0, None, None,
+                                        1e-6, cos[:, :32].contiguous(), sin[:, :32].contiguous(), status)
