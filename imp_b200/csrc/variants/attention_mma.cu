@@ -952,7 +952,9 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
     int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int* status, const DecFused fz) {
+    float* __restrict__ part_ml, int* status, const DecFused fz, int cluster_merge) {
+    // cluster_merge: the CTAs of the key splits of one (token, kv head) form a cluster (grid.x == cluster size) and
+    // merge their results in the first CTA's shared memory: no partial results in global memory, no merge kernel.
     // pdl_wait() comes later: the batch arrays and the keys before this step's position do not depend on the
     // kernel before this one, so the first stages are requested while it still runs.
     extern __shared__ __align__(128) unsigned char dt_smem[];
@@ -1132,7 +1134,8 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp != 0 && !cluster_merge) return;
+    if (warp == 0)
     for (int w = 1; w < DT_CONSUMERS; ++w) {
         const float* src = smem + (size_t)(w - 1) * PER_WARP * 32;
 #pragma unroll
@@ -1151,12 +1154,57 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
             }
         }
     }
+    if (cluster_merge) {
+        // Every CTA of the cluster is past its ring (first barrier; it also says that all of them run), then the
+        // splits 1.. store their state into the first CTA's shared memory behind its own merge buffer (second
+        // barrier), and its first warp folds them in, in split order.  Every thread of every CTA takes part in
+        // both barriers, whatever happened before.
+        float* xch = smem + (size_t)(DT_CONSUMERS - 1) * PER_WARP * 32;
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp == 0 && split > 0) {
+            const uint32_t local = (uint32_t)__cvta_generic_to_shared(xch + (size_t)(split - 1) * PER_WARP * 32 + lane);
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+                for (int c = 0; c < 2 * NR; ++c)
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((i * 2 * NR + c) * 32) * 4u), "f"(st.o[i][c]) : "memory");
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((NACC + r) * 32) * 4u), "f"(st.m[r]) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((NACC + NR + r) * 32) * 4u), "f"(st.l[r]) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp != 0 || split != 0) return;
+        for (int w = 1; w < n_splits; ++w) {
+            const float* src = xch + (size_t)(w - 1) * PER_WARP * 32;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const float mo = src[(NACC + r) * 32 + lane];
+                const float lo = src[(NACC + NR + r) * 32 + lane];
+                const float m_new = fmaxf(st.m[r], mo);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float ca = exp2f(st.m[r] - m_use), cb = exp2f(mo - m_use);
+                st.l[r] = st.l[r] * ca + lo * cb;
+                st.m[r] = m_new;
+#pragma unroll
+                for (int i = 0; i < NTILES; ++i) {
+                    st.o[i][2 * r] = st.o[i][2 * r] * ca + src[(i * 2 * NR + 2 * r) * 32 + lane] * cb;
+                    st.o[i][2 * r + 1] = st.o[i][2 * r + 1] * ca + src[(i * 2 * NR + 2 * r + 1) * 32 + lane] * cb;
+                }
+            }
+        }
+    }
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
         const int hr = row0 + g + 8 * r;
         if (hr >= G) continue;
         const int head = hk * G + hr;
-        if (n_splits == 1) {
+        if (n_splits == 1 || cluster_merge) {
             const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
             __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
 #pragma unroll
@@ -1180,24 +1228,68 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     }
 }
 
+// Most key splits that merge inside a cluster.  Measured on the whole decode step (8B shape, context 4096): two
+// splits (16 sequences) 4.74 against 4.87 ms with the merge kernel, four (8 sequences) 3.97 against 3.98, eight
+// (4 sequences) 3.81 against 3.76: larger clusters wait longer for their slowest member than the kernel saves.
+constexpr int DT_CLUSTER_MAX = 4;
+
+// *merged is set when the key splits merged inside the kernel (a cluster per (token, kv head)): no merge kernel then.
 template <int NR>
 static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_stride, const void* q, int64_t q_stride,
                              const void* kc, const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                              const int* positions, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2,
-                             int window, int n_splits, float* part_o, float* part_ml, int* status, const DecFused& fz) {
-    constexpr int MERGE = (DT_CONSUMERS - 1) * (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);
+                             int window, int n_splits, float* part_o, float* part_ml, int* status, const DecFused& fz,
+                             bool* merged) {
+    constexpr int SLOT = (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);      // one warp's (or split's) state
+    constexpr int MERGE = (DT_CONSUMERS - 1 + DT_CLUSTER_MAX - 1) * SLOT;           // the warps' merge, then the splits'
     constexpr int SMEM = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
+    auto kernel = attn_decode_tma_kernel<NR>;
     static bool attr_set = false;
     if (!attr_set) {   // always: the kernel's static barriers come on top of the ring
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
-    cudaError_t e = imp_launch(attn_decode_tma_kernel<NR>, grid, dim3((DT_CONSUMERS + 1) * 32), (size_t)SMEM, s,
-                               (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
-                               (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P,
-                               num_pages, scale_log2, window, n_splits, part_o, part_ml, status, fz);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((DT_CONSUMERS + 1) * 32);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    static int use_cluster = -1;      // IMP_B200_ATTN_CLUSTER=0: partial results through global memory and a merge kernel
+    if (use_cluster < 0) { const char* e = getenv("IMP_B200_ATTN_CLUSTER"); use_cluster = e ? atoi(e) : 1; }
+    int cluster_merge = 0;
+    if (use_cluster && n_splits >= 2 && n_splits <= DT_CLUSTER_MAX) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)n_splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        // whether the device can place such a cluster is asked once per size, not found out by a failed launch
+        static int placeable[DT_CLUSTER_MAX + 1] = {};       // 0 unknown, 1 yes, -1 no
+        if (placeable[n_splits] == 0) {
+            int n = 0;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+            if (e != cudaSuccess) (void)cudaGetLastError();
+            placeable[n_splits] = (e == cudaSuccess && n > 0) ? 1 : -1;
+        }
+        if (placeable[n_splits] > 0) { cluster_merge = 1; n_attr = 1; }
+    }
+    if (imp_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
+                                       (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_stride, seq_of_token,
+                                       positions, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml,
+                                       status, fz, cluster_merge);
     if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
+    *merged = cluster_merge != 0;
     return 0;
 }
 
@@ -1243,7 +1335,8 @@ static int attn_decode_impl(void* out, int64_t out_stride, const void* q, int64_
     const bool bulk = P % 16 == 0 && getenv("IMP_B200_ATTN_DIRECT") == nullptr;   // whole 16-key steps per page
     if (fz.qkv && !(bulk && DH % 64 == 0)) return IMP_ERR_UNSUPPORTED;               // only the bulk-copy kernel does that
 #define DEC_ARGS grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, \
-                 Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml, status, fz
+                 Hkv, P, num_pages, scale_log2, window, n_splits, part_o, part_ml, status, fz, &merged
+    bool merged = false;
     if (bulk) {
         if (int rc = (G <= 8) ? launch_decode_tma<1>(DEC_ARGS) : launch_decode_tma<2>(DEC_ARGS)) return rc;
     } else if (G <= 8) {
@@ -1258,7 +1351,7 @@ static int attn_decode_impl(void* out, int64_t out_stride, const void* q, int64_
             return rc;
     }
 #undef DEC_ARGS
-    if (n_splits > 1) {
+    if (n_splits > 1 && !merged) {
         imp_launch(attn_merge_kernel, dim3(n_tokens * Hq), dim3(128), 0, s, (__nv_bfloat16*)out, out_stride,
                    (const float*)part_o, (const float*)part_ml, Hq, n_splits);
     }
