@@ -13,6 +13,11 @@ device-to-host read of the tokens.  `prefill` is one 2,048-token prompt in one s
 decode at batch 1 and 64.  Roofline fractions use MEASURED_PEAKS.json when the driver wrote it,
 else the stated fallback.  Every decode step streams all weights (about 16 GB), far more than the
 126 MB L2, so no explicit L2 flush is needed between timed iterations ("inputs larger than L2").
+
+For profiling and for other sizes one phase can be run alone; it prints its own short JSON line:
+    python bench.py --only decode [--batch B] [--context C] [--page P] [--layers N] [--no-graphs]
+    python bench.py --only prefill [--tokens T] [--layers N]
+(`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
 import argparse
 import json
