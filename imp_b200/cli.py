@@ -85,8 +85,6 @@ def main(argv: Optional[List[str]] = None) -> int:
         print("error: --prompt is required (or --bench)", file=sys.stderr)
         return 1
 
-    import torch
-
     from .config.engine_config import EngineConfig
     from .config.registry import load_config
     from .engine.engine import Engine, GenerateParams
@@ -98,16 +96,16 @@ def main(argv: Optional[List[str]] = None) -> int:
                         kv_block_size=args.page_size, prefill_chunk_size=args.prefill_chunk_size,
                         max_batch_tokens=max(2048, args.max_batch, args.bench_batch), compute_dtype=dtype,
                         enable_cuda_graphs=not args.no_cuda_graphs)
-    torch.cuda.set_device(args.device)
     t0 = time.time()
     if args.random_weights:
         mc = load_config(args.model)
         eng = Engine.from_random(mc, ecfg, seed=args.weights_seed, std=args.weights_std)
     else:
         eng = Engine.from_folder(args.model, ecfg)
-    print(f"model ready in {time.time() - t0:.1f}s ({eng.model_config.architecture}, {dtype}, "
-          f"{eng.cache.num_pages} cache pages of {eng.cache.page_size})", file=sys.stderr)
-    V = eng.model.vocab_size
+    cache = eng.info()["cache"]
+    print(f"model ready in {time.time() - t0:.1f}s ({eng.model.architecture}, {dtype}, "
+          f"{cache['num_pages']} cache pages of {cache['page_size']})", file=sys.stderr)
+    V = eng.vocab_size
 
     if args.bench:
         return run_bench(eng, args, V)
@@ -123,23 +121,24 @@ def main(argv: Optional[List[str]] = None) -> int:
                         ignore_eos=args.ignore_eos)
     req = eng.submit(prompt, gp)
     if req.done:
-        print(f"error: request refused: {req.status.value}", file=sys.stderr)
+        print(f"error: request refused: {req.status.name.lower()}", file=sys.stderr)
         return 1
-    torch.cuda.synchronize()
+    # a step returns when its tokens have reached the host, so the wall clock brackets the device's work
     t_start = time.perf_counter()
     t_first = None
-    while not req.done:
+    n_out, finished = 0, False
+    while not finished:
         for out in eng.step():
+            finished = finished or out.finished
             if out.token >= 0:
                 if t_first is None:
-                    torch.cuda.synchronize()
                     t_first = time.perf_counter()
+                n_out += 1
                 sys.stdout.write(f"{out.token} ")
                 sys.stdout.flush()
-    torch.cuda.synchronize()
+    eng.drain()
     t_end = time.perf_counter()
     sys.stdout.write("\n")
-    n_out = len(req.output)
     pp_ms = ((t_first or t_end) - t_start) * 1e3
     tg_ms = (t_end - (t_first or t_end)) * 1e3
     print(f"pp {len(prompt):5d} tokens in {pp_ms:8.2f} ms  ({len(prompt) / max(pp_ms, 1e-9) * 1e3:7.2f} tok/s)",
@@ -152,8 +151,6 @@ def main(argv: Optional[List[str]] = None) -> int:
 def run_bench(eng, args, V: int) -> int:
     """The reference's --bench protocol (tools/imp-cli/main.cpp:142-215): ids i % vocab, one discarded
     warm-up cycle, timed prefills, timed greedy decode runs with EOS ignored; averages."""
-    import torch
-
     from .engine.engine import GenerateParams
 
     B, pp, tg, reps = args.bench_batch, args.bench_pp, args.max_tokens, args.bench_reps
@@ -163,32 +160,37 @@ def run_bench(eng, args, V: int) -> int:
 
     def prefill():
         reqs = [eng.submit(tokens, gp) for _ in range(B)]
-        while any(not r.output for r in reqs):
-            eng.step()
+        waiting = {r.rid for r in reqs}
+        while waiting:
+            for o in eng.step():
+                waiting.discard(o.rid)
         return reqs
 
     def drain(reqs):
-        while any(not r.done for r in reqs):
-            eng.step()
+        live = {r.rid for r in reqs}
+        while live:
+            for o in eng.step():
+                if o.finished:
+                    live.discard(o.rid)
+        eng.drain()
+        for r in reqs:
+            r.release()
 
     print("Warmup...", file=sys.stderr)
     drain(prefill())
     pp_ms = 0.0
     for _ in range(reps):
-        torch.cuda.synchronize()
         t0 = time.perf_counter()
         reqs = prefill()
-        torch.cuda.synchronize()
         pp_ms += (time.perf_counter() - t0) * 1e3
         for r in reqs:
-            eng.scheduler.cancel(r.rid)
+            eng.cancel(r)
+        eng.drain()
     tg_ms = 0.0
     for _ in range(reps):
         reqs = prefill()
-        torch.cuda.synchronize()
         t0 = time.perf_counter()
         drain(reqs)
-        torch.cuda.synchronize()
         tg_ms += (time.perf_counter() - t0) * 1e3
     pp_avg, tg_avg = pp_ms / reps, tg_ms / reps
     print(f"pp {pp * B:5d} tokens  avg {pp_avg:8.2f} ms  ({pp * B / pp_avg * 1e3:7.2f} tok/s)  [{reps} reps]",

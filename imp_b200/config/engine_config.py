@@ -4,11 +4,14 @@
 `compute_dtype`, `prefill_chunk_size`, `enable_cuda_graphs` come from
 include/imp/config.h:11-81 (defaults: src/api/imp_api.cpp:35-72);
 `kv_block_size` from src/runtime/engine.h:59.  `max_batch_tokens` (the token
-budget of one step) and `lookahead` are this engine's own.
+budget of one step) and `lookahead` are this engine's own.  The dataclass
+mirrors the C API's `ImpConfig` (include/imp_b200/imp.h).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
+
+from .. import capi
 
 
 @dataclass
@@ -37,3 +40,21 @@ class EngineConfig:
             raise ValueError("prefill_chunk_size must be >= 0")
         if self.max_batch_tokens < self.max_batch_size:
             raise ValueError("max_batch_tokens must be at least max_batch_size (one token per decoding request)")
+
+    def to_c(self) -> "capi.ImpConfig":
+        self.validate()
+        c = capi.load().imp_config_default()
+        c.device_id = self.device_id
+        c.kv_cache_max_blocks = self.kv_cache_max_blocks
+        c.kv_cache_tokens = self.kv_cache_tokens
+        c.kv_block_size = self.kv_block_size
+        c.max_batch_size = self.max_batch_size
+        c.max_seq_len = self.max_seq_len
+        c.max_batch_tokens = self.max_batch_tokens
+        c.prefill_chunk_size = self.prefill_chunk_size
+        c.compute_dtype = capi.COMPUTE_FP32 if self.compute_dtype == "float32" else capi.COMPUTE_BF16
+        c.enable_cuda_graphs = int(self.enable_cuda_graphs)
+        c.gpu_memory_fraction = self.gpu_memory_fraction
+        c.state_slots = self.state_slots
+        c.lookahead = int(self.lookahead)
+        return c

@@ -58,19 +58,33 @@ def find_nvcc() -> str:
                      "the CUDA kernels cannot be compiled")
 
 
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+INCLUDE_DIR = os.path.normpath(os.path.join(CSRC_DIR, "..", "..", "include"))
+HOST_FLAGS = ["-O2", "-std=c++20", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xcompiler", "-Wall"]
+
+
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    """The kernels (*.cu here) and the host (host/*.cpp), as paths relative to this folder."""
+    return (sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu")) +
+            sorted(os.path.join("host", f) for f in os.listdir(HOST_DIR) if f.endswith(".cpp")))
+
+
+def kernel_headers() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
 
 
 def headers() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+    own = kernel_headers()
+    host = sorted(os.path.join("host", f) for f in os.listdir(HOST_DIR) if f.endswith((".hpp", ".h")))
+    public = sorted(os.path.join(INCLUDE_DIR, "imp_b200", f) for f in os.listdir(os.path.join(INCLUDE_DIR, "imp_b200")))
+    return own + host + public
 
 
 def source_hash() -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS + LINK_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + HOST_FLAGS + LINK_FLAGS).encode())
     for f in sources() + headers():
-        h.update(f.encode())
+        h.update(os.path.basename(f).encode())
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())
     return h.hexdigest()[:16]
@@ -118,8 +132,11 @@ def library_path(create: bool = True) -> str:
 
 
 def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> None:
-    cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
-    if verbose:
+    if src.endswith(".cpp"):
+        cmd = [nvcc, *HOST_FLAGS, "-I", CSRC_DIR, "-I", HOST_DIR, "-I", INCLUDE_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
+    else:
+        cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
+    if verbose and not src.endswith(".cpp"):
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     t0 = time.time()
@@ -131,33 +148,57 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> None:
         sys.stderr.write(p.stderr)
 
 
+def _object_hash(src: str) -> str:
+    """What one object file depends on: its flags, its source, and the headers of its side."""
+    h = hashlib.sha256()
+    host = src.endswith(".cpp")
+    h.update(" ".join(HOST_FLAGS if host else NVCC_FLAGS).encode())
+    deps = [src] + ([f for f in headers()] if host else kernel_headers())
+    for f in deps:
+        with open(os.path.join(CSRC_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Build (if needed) and return the path of the shared library."""
+    """Build (if needed) and return the path of the shared library.  Object files are kept by the hash
+    of what they depend on, so an edit recompiles only what it touches."""
     out = library_path()
     if os.path.exists(out) and not force:
         return out
     nvcc = find_nvcc()
     bdir = build_dir()
-    tag = source_hash()
-    objdir = os.path.join(bdir, f"obj-{tag}-{os.getpid()}")
+    objdir = os.path.join(bdir, "obj")
     os.makedirs(objdir, exist_ok=True)
     srcs = sources()
-    _log(f"compiling {len(srcs)} CUDA files for sm_100a with {nvcc} (first use; this takes a minute)")
-    objs = [os.path.join(objdir, s[:-3] + ".o") for s in srcs]
-    try:
-        with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-            futs = [ex.submit(_compile_one, nvcc, s, o, verbose) for s, o in zip(srcs, objs)]
-            for f in futs:
-                f.result()
-        tmp = out + f".tmp-{os.getpid()}"
-        p = subprocess.run([nvcc, *LINK_FLAGS, "-o", tmp, *objs], capture_output=True, text=True)
-        if p.returncode != 0:
-            raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
-        os.replace(tmp, out)  # atomic: concurrent builders race benignly
-        _log(f"linked {os.path.basename(out)}")
-    finally:
-        shutil.rmtree(objdir, ignore_errors=True)
-    # Drop libraries of older source states.
+    objs = [os.path.join(objdir, f"{os.path.splitext(s)[0].replace(os.sep, '_')}-{_object_hash(s)}.o") for s in srcs]
+    todo = [(s, o) for s, o in zip(srcs, objs) if force or verbose or not os.path.exists(o)]
+    if todo:
+        _log(f"compiling {len(todo)} of {len(srcs)} source files for sm_100a with {nvcc} (this takes a minute the first time)")
+
+    def compile_to(src, obj):
+        tmp = f"{obj}.tmp-{os.getpid()}"
+        _compile_one(nvcc, src, tmp, verbose)
+        os.replace(tmp, obj)
+
+    with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, 16, max(len(todo), 1))) as ex:
+        futs = [ex.submit(compile_to, s, o) for s, o in todo]
+        for f in futs:
+            f.result()
+    tmp = out + f".tmp-{os.getpid()}"
+    p = subprocess.run([nvcc, *LINK_FLAGS, "-o", tmp, *objs, "-ldl"], capture_output=True, text=True)
+    if p.returncode != 0:
+        raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
+    os.replace(tmp, out)  # atomic: concurrent builders race benignly
+    _log(f"linked {os.path.basename(out)}")
+    # Drop libraries and objects of older source states.
+    keep = set(objs)
+    for f in os.listdir(objdir):
+        if f.endswith(".o") and os.path.join(objdir, f) not in keep:
+            try:
+                os.remove(os.path.join(objdir, f))
+            except OSError:
+                pass
     for f in os.listdir(bdir):
         if f.startswith("libimp_b200-") and f.endswith(".so") and os.path.join(bdir, f) != out:
             try:
@@ -181,7 +222,7 @@ def variant_hash(source: str, defines: dict) -> str:
     # everything that goes into the image: the source, runtime.cu (compiled in), and every header beside them
     variant_headers = sorted(f for f in os.listdir(VARIANT_DIR) if f.endswith((".cuh", ".h")))
     paths = ([os.path.join(VARIANT_DIR, source), os.path.join(CSRC_DIR, "runtime.cu")] +
-             [os.path.join(CSRC_DIR, f) for f in headers()] + [os.path.join(VARIANT_DIR, f) for f in variant_headers])
+             [os.path.join(CSRC_DIR, f) for f in kernel_headers()] + [os.path.join(VARIANT_DIR, f) for f in variant_headers])
     for path in paths:
         with open(path, "rb") as fh:
             h.update(fh.read())

@@ -1,9 +1,11 @@
-"""The Python entry point: load or make a model, then generate.
+"""The Python entry point: a thin layer over the C API (include/imp_b200/imp.h).
 
 In the reference's manner (include/imp/imp.h:34-143): a model handle, a
 context with engine settings, `generate` for whole requests, and the token
 level pair prefill / decode-step, here as `submit` + `step`.  Requests are
-lists of token ids (this engine has no tokenizer).
+lists of token ids (this engine has no tokenizer).  Everything that happens
+(loading, scheduling, the step function, sampling) happens in the library;
+this module converts arguments and results.
 
     from imp_b200 import Engine, EngineConfig, GenerateParams
     eng = Engine.from_folder("model_dir", EngineConfig(compute_dtype="bfloat16"))
@@ -11,20 +13,30 @@ lists of token ids (this engine has no tokenizer).
 """
 from __future__ import annotations
 
-import itertools
+import ctypes
+import enum
+import json
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Any, Dict, Hashable, List, Optional, Sequence
 
-import torch
-
-from ..cache.manager import CacheManager
+from .. import capi
 from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig
-from ..sampling.sampler import Sampler, SamplingParams
-from .loading import load_model, make_cache, random_model
-from .model import DecoderModel
-from .scheduler import Request, RequestStatus, ScheduledEntry, Scheduler, StepPlan
-from .step import StepEntry, Stepper
+
+
+class RequestStatus(enum.Enum):
+    WAITING = 0
+    RUNNING = 1
+    FINISHED = 2
+    CANCELLED = 3
+    OUT_OF_MEMORY = 4
+
+
+class FinishReason(enum.Enum):
+    NONE = 0
+    EOS = 1
+    LENGTH = 2          # max_tokens reached
+    CONTEXT = 3         # the sequence reached max_seq_len
 
 
 @dataclass
@@ -52,240 +64,283 @@ class GenerateParams:
     mirostat_eta: float = 0.1
     ignore_eos: bool = False
 
-    def sampling(self) -> SamplingParams:
-        return SamplingParams(temperature=self.temperature, top_p=self.top_p, top_k=self.top_k, min_p=self.min_p,
-                              repetition_penalty=self.repetition_penalty, frequency_penalty=self.frequency_penalty,
-                              presence_penalty=self.presence_penalty, repeat_last_n=self.repeat_last_n,
-                              typical_p=self.typical_p, dry_multiplier=self.dry_multiplier, dry_base=self.dry_base,
-                              dry_allowed_length=self.dry_allowed_length,
-                              dry_penalty_last_n=self.dry_penalty_last_n, mirostat=self.mirostat,
-                              mirostat_tau=self.mirostat_tau, mirostat_eta=self.mirostat_eta, seed=self.seed)
+    def to_c(self) -> "capi.ImpGenerateParams":
+        p = capi.ImpGenerateParams()
+        for name, _ in capi.ImpGenerateParams._fields_:
+            setattr(p, name, int(getattr(self, name)) if name in ("ignore_eos", "seed") else getattr(self, name))
+        return p
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request, and which of them should yield logits."""
+
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)   # indices into `tokens`
 
 
 @dataclass
 class StepOutput:
-    rid: Hashable
+    rid: int
     token: int
     finished: bool
     status: RequestStatus
+    finish_reason: FinishReason = FinishReason.NONE
 
 
-@dataclass
-class _InFlight:
-    """A step that has been queued on the device and whose tokens have not been read yet."""
+class Request:
+    """Handle of a submitted request: its state is read from the engine when asked for."""
 
-    plan: StepPlan
-    rows: List[Request]              # the requests that get a token, in the order of the sampled tokens
-    tokens_dev: Optional[torch.Tensor]   # int32 [len(rows)] on the device
-    tokens_host: Optional[torch.Tensor]  # pinned copy of the same, valid once `event` has passed
-    status_host: torch.Tensor            # pinned copy of the device status word
-    event: torch.cuda.Event
-    early: List[StepOutput]          # outputs known at launch (requests the scheduler gave up on)
+    def __init__(self, engine: "Engine", rid: int, prompt: Sequence[int], refused: bool = False):
+        self._engine, self.rid, self.prompt = engine, rid, list(prompt)
+        self._refused = refused
+        self._final: Optional[Dict[str, Any]] = None
+
+    def _info(self) -> Dict[str, Any]:
+        if self._final is not None:
+            return self._final
+        if self._refused:
+            return {"status": RequestStatus.OUT_OF_MEMORY, "finish_reason": FinishReason.NONE, "n_output": 0,
+                    "n_computed": 0, "n_preempted": 0, "output": []}
+        lib, ctx = capi.load(), self._engine._ctx
+        info = capi.ImpRequestInfo()
+        capi.check(lib.imp_request_info(ctx, self.rid, ctypes.byref(info)))
+        out = {"status": RequestStatus(info.status), "finish_reason": FinishReason(info.finish_reason),
+               "n_output": info.n_output, "n_computed": info.n_computed, "n_preempted": info.n_preempted}
+        return out
+
+    @property
+    def status(self) -> RequestStatus:
+        return self._info()["status"]
+
+    @property
+    def finish_reason(self) -> FinishReason:
+        return self._info()["finish_reason"]
+
+    @property
+    def n_preempted(self) -> int:
+        return self._info()["n_preempted"]
+
+    @property
+    def done(self) -> bool:
+        return self.status in (RequestStatus.FINISHED, RequestStatus.CANCELLED, RequestStatus.OUT_OF_MEMORY)
+
+    @property
+    def output(self) -> List[int]:
+        if self._final is not None:
+            return self._final["output"]
+        if self._refused:
+            return []
+        lib, ctx = capi.load(), self._engine._ctx
+        n = ctypes.c_int(0)
+        capi.check(lib.imp_request_output(ctx, self.rid, None, 0, ctypes.byref(n)))
+        buf = (ctypes.c_int32 * max(n.value, 1))()
+        capi.check(lib.imp_request_output(ctx, self.rid, buf, n.value, ctypes.byref(n)))
+        return list(buf[:n.value])
+
+    def release(self) -> None:
+        """Keep the final state here and let the engine forget the request."""
+        if self._final is None and not self._refused:
+            info = self._info()
+            info["output"] = self.output
+            if info["status"] in (RequestStatus.FINISHED, RequestStatus.CANCELLED, RequestStatus.OUT_OF_MEMORY):
+                capi.check(capi.load().imp_request_release(self._engine._ctx, self.rid))
+                self._final = info
+
+
+class Model:
+    """A model handle: configuration, plan, and where the tensors come from (a folder, or a seed)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def load(cls, model_dir: str) -> "Model":
+        h = ctypes.c_void_p()
+        capi.model_error(capi.load().imp_model_load(str(model_dir).encode(), ctypes.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def random(cls, config, seed: int = 0, std: float = 0.02, norm_std: float = 0.01) -> "Model":
+        """`config`: a ModelConfig, a config.json dictionary, or a path."""
+        if isinstance(config, ModelConfig):
+            text = config.to_json()
+        elif isinstance(config, dict):
+            text = json.dumps(config)
+        else:
+            text = str(config)
+        h = ctypes.c_void_p()
+        capi.model_error(capi.load().imp_model_random(text.encode(), int(seed), float(std), float(norm_std), ctypes.byref(h)))
+        return cls(h)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                capi.load().imp_model_free(h)
+            except Exception:
+                pass
+
+    @property
+    def architecture(self) -> str:
+        return capi.text(capi.load().imp_model_arch(self._h))
+
+    @property
+    def vocab_size(self) -> int:
+        return capi.load().imp_model_vocab_size(self._h)
+
+    @property
+    def config(self) -> ModelConfig:
+        from ..config.registry import config_class_of
+        d = json.loads(capi.text(capi.load().imp_model_config_json(self._h)))
+        return config_class_of(d["architectures"][0])(d)
+
+    def plan_json(self) -> Dict[str, Any]:
+        return json.loads(capi.text(capi.load().imp_model_plan_json(self._h)))
+
+    def tensor_info(self, compute_dtype: str = "bfloat16") -> Dict[str, Any]:
+        c = capi.COMPUTE_FP32 if compute_dtype == "float32" else capi.COMPUTE_BF16
+        return json.loads(capi.text(capi.load().imp_model_tensor_info_json(self._h, c)))
 
 
 class Engine:
-    """Model + cache + step function + scheduler + sampler on one GPU."""
+    """Model + cache + step function + scheduler + sampler on one GPU (the library's context)."""
 
-    def __init__(self, model: DecoderModel, model_config: ModelConfig, config: Optional[EngineConfig] = None):
+    def __init__(self, model: Model, config: Optional[EngineConfig] = None):
         self.config = config or EngineConfig()
-        self.config.validate()
         self.model = model
-        self.model_config = model_config
-        cfg = self.config
-        rt = model.rt
-        if cfg.compute_dtype not in ("bfloat16", "float32") or \
-                (cfg.compute_dtype == "float32") != (rt.dtype == torch.float32):
-            raise ValueError(f"engine compute_dtype {cfg.compute_dtype} does not match the model's {rt.dtype}")
-        self.max_seq_len = min(cfg.max_seq_len, model.plan.max_positions)
-        num_pages = self._decide_pages()
-        slots = cfg.state_slots or cfg.max_batch_size
-        self.cache: CacheManager = make_cache(model, cfg.kv_block_size, num_pages, slots)
-        self.stepper = Stepper(model, self.cache, rt, cfg.max_batch_tokens, cfg.max_batch_size, self.max_seq_len,
-                               use_cuda_graphs=cfg.enable_cuda_graphs)
-        self.scheduler = Scheduler(self.cache, cfg.max_batch_size, cfg.max_batch_tokens, cfg.prefill_chunk_size,
-                                   self.max_seq_len)
-        self.sampler = Sampler(model.vocab_size, cfg.max_batch_size, rt.device)
-        self._inflight: Optional[_InFlight] = None
-        # two pinned landing places for (tokens, status): a step in flight and the one launched ahead of it
-        self._landing = [(torch.zeros(cfg.max_batch_size, dtype=torch.int32).pin_memory(),
-                          torch.zeros(1, dtype=torch.int32).pin_memory()) for _ in range(2)]
-        self._landing_turn = 0
-        self._ids = itertools.count()
-        eos = model_config.eos_token_id
-        self.eos_token_ids: Tuple[int, ...] = () if eos is None else (int(eos),)
+        self._ids: Dict[Hashable, int] = {}     # step_tokens: the caller's request ids -> integers
+        self._next_replay_id = 1 << 40
+        c = self.config.to_c()
+        ctx = ctypes.c_void_p()
+        capi.check(capi.load().imp_context_create(model._h, ctypes.byref(c), ctypes.byref(ctx)))
+        self._ctx = ctx
+        self.vocab_size = model.vocab_size
+        self._outs = (capi.ImpStepOutput * max(self.config.max_batch_size * 2, 8))()
 
     # ------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, model_dir: str, config: Optional[EngineConfig] = None) -> "Engine":
-        config = config or EngineConfig()
-        mc, model = load_model(model_dir, config.compute_dtype, f"cuda:{config.device_id}")
-        return cls(model, mc, config)
+        return cls(Model.load(model_dir), config)
 
     @classmethod
-    def from_random(cls, model_config: ModelConfig, config: Optional[EngineConfig] = None, seed: int = 0,
-                    std: float = 0.02) -> "Engine":
-        config = config or EngineConfig()
-        model = random_model(model_config, seed, std, dtype=config.compute_dtype,
-                             device=f"cuda:{config.device_id}")
-        return cls(model, model_config, config)
+    def from_random(cls, model_config, config: Optional[EngineConfig] = None, seed: int = 0, std: float = 0.02,
+                    norm_std: float = 0.01) -> "Engine":
+        return cls(Model.random(model_config, seed, std, norm_std), config)
 
-    def _decide_pages(self) -> int:
-        """Pages per cache group: explicit, or from a token count, or from free memory
-        (the reference gives 80% of free memory, clamped to 1-2x the configured worst case:
-        src/runtime/engine.cpp:226-243; an explicit block count wins, :531-535)."""
-        cfg = self.config
-        P = cfg.kv_block_size
-        if cfg.kv_cache_max_blocks > 0:
-            return cfg.kv_cache_max_blocks
-        if cfg.kv_cache_tokens > 0:
-            return (cfg.kv_cache_tokens + P - 1) // P
-        worst = ((self.max_seq_len + P - 1) // P) * cfg.max_batch_size
-        probe = CacheManager(self.model.cache_specs, P, 1, 1)
-        per_page = max(1, probe.storage_bytes(torch.empty((), dtype=self.model.rt.dtype).element_size()))
-        free, _ = torch.cuda.mem_get_info(self.model.rt.device)
-        by_memory = int(free * cfg.gpu_memory_fraction) // per_page
-        return max(1, min(worst, by_memory))
+    def close(self) -> None:
+        ctx, self._ctx = getattr(self, "_ctx", None), None
+        if ctx:
+            capi.load().imp_context_free(ctx)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def model_config(self) -> ModelConfig:
+        return self.model.config
+
+    def info(self) -> Dict[str, Any]:
+        """State of the context: cache groups and free pages, run positions, counters."""
+        return json.loads(capi.text(capi.load().imp_context_info_json(self._ctx)))
+
+    def reset(self) -> None:
+        capi.check(capi.load().imp_context_reset(self._ctx))
+        self._ids.clear()
 
     # ---------------------------------------------------------------- requests
-    def submit(self, prompt: Sequence[int], params: Optional[GenerateParams] = None,
-               rid: Optional[Hashable] = None) -> Request:
+    def submit(self, prompt: Sequence[int], params: Optional[GenerateParams] = None) -> Request:
         """Queue one request; returns its handle (check `.status` for OUT_OF_MEMORY)."""
-        params = params or GenerateParams()
-        V = self.model.vocab_size
-        for t in prompt:
-            if not 0 <= int(t) < V:
-                raise ValueError(f"token id {t} outside the vocabulary of {V}")
-        req = Request(rid=next(self._ids) if rid is None else rid, prompt=[int(t) for t in prompt],
-                      max_tokens=params.max_tokens, params=params.sampling(), eos_token_ids=self.eos_token_ids,
-                      ignore_eos=params.ignore_eos)
-        return self.scheduler.add(req)
+        p = (params or GenerateParams()).to_c()
+        toks, n = capi.int32_array([int(t) for t in prompt])
+        rid = ctypes.c_int64(-1)
+        rc = capi.load().imp_submit(self._ctx, toks, n, ctypes.byref(p), ctypes.byref(rid))
+        if rc == capi.IMP_ERROR_OUT_OF_MEMORY:
+            return Request(self, rid.value, prompt, refused=True)
+        capi.check(rc)
+        return Request(self, rid.value, prompt)
+
+    def cancel(self, request) -> None:
+        capi.check(capi.load().imp_cancel(self._ctx, request.rid if isinstance(request, Request) else int(request)))
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return bool(capi.load().imp_has_work(self._ctx))
 
-    # ------------------------------------------------------------------- steps
-    def _launch(self, plan: StepPlan, device_tokens: Optional[torch.Tensor] = None,
-                early: Optional[List[StepOutput]] = None) -> _InFlight:
-        """Queue the plan's batch, its sampling and the copy of the results to pinned memory."""
-        entries, rows = [], []
-        for e in plan.entries:
-            toks = [0] * e.n_tokens if device_tokens is not None else e.request.tokens_slice(e.start, e.n_tokens)
-            entries.append(StepEntry(e.request.rid, toks, [e.n_tokens - 1] if e.samples else []))
-            if e.samples:
-                rows.append(e.request)
-        logits = self.stepper.step(entries, device_tokens)
-        tokens_dev = tokens_host = None
-        land_tokens, land_status = self._landing[self._landing_turn]
-        self._landing_turn ^= 1
-        if rows:
-            # a token launched ahead of the last one's arrival counts as one more output
-            ahead = 1 if device_tokens is not None else 0
-            tokens_dev = self.sampler.sample_device(
-                logits, [r.params for r in rows], [r.seed for r in rows], [len(r.output) + ahead for r in rows],
-                [r.all_tokens() for r in rows] if any(r.params.needs_history() for r in rows) else None,
-                [r.sampler_state for r in rows])
-            tokens_host = land_tokens[:len(rows)]
-            tokens_host.copy_(tokens_dev, non_blocking=True)
-        land_status.copy_(self.stepper.rt.status, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        return _InFlight(plan, rows, tokens_dev, tokens_host, land_status, ev, early or [])
-
-    def _finish(self, fl: _InFlight) -> List[StepOutput]:
-        """Wait for a queued step, hand its tokens to the scheduler, and report them."""
-        fl.event.synchronize()
-        code = int(fl.status_host[0])
-        if code != 0:
-            self.stepper.check_device_status()      # raises with the device's message and clears the word
-        outs = list(fl.early)
-        live = [r for r in fl.rows if not r.done]   # a request may have finished while this step was under way
-        toks = fl.tokens_host.tolist() if fl.rows else []
-        sampled = {r.rid: t for r, t in zip(fl.rows, toks)}
-        finished = set(id(r) for r in self.scheduler.complete_step(fl.plan, sampled))
-        for r in live:
-            outs.append(StepOutput(r.rid, sampled[r.rid], id(r) in finished, r.status))
-        return outs
-
-    def _plan_ahead(self, fl: _InFlight) -> Optional[StepPlan]:
-        """The step after `fl` if it can be decided before `fl`'s tokens are known: every running request
-        gets a token from `fl`, none of them ends with it for a reason known in advance (length, context),
-        none needs its token on the host to sample the next one, nothing waits for admission, and the pages
-        are there.  A request that ends on its end-of-sequence token takes part in one step too many; its
-        result is dropped."""
-        sch = self.scheduler
-        if not self.config.lookahead or not fl.rows or sch.waiting or len(fl.rows) != len(sch.running):
-            return None
-        if len(fl.plan.entries) != len(fl.rows) or fl.plan.preempted or fl.plan.failed:
-            return None
-        entries = []
-        for e in fl.plan.entries:
-            r = e.request
-            if r.done or r.params.needs_history() or r.params.mirostat:
-                return None
-            start = e.start + e.n_tokens
-            if len(r.output) + 1 >= r.max_tokens or start + 1 >= self.max_seq_len:
-                return None
-            entries.append(ScheduledEntry(r, start, 1, True))
-        probe = [StepEntry(e.request.rid, [0], [0]) for e in entries]
-        if self.stepper.pages_short(probe) > 0:
-            return None
-        return StepPlan(entries=entries)
+    def _outputs(self, fn) -> List[StepOutput]:
+        n = ctypes.c_int(0)
+        capi.check(fn(self._ctx, self._outs, len(self._outs), ctypes.byref(n)))
+        return [StepOutput(o.id, o.token, bool(o.finished), RequestStatus(o.status), FinishReason(o.finish_reason))
+                for o in self._outs[:n.value]]
 
     def step(self) -> List[StepOutput]:
-        """One engine step: schedule, run the batch, sample, finish.  Returns the new tokens.
-
-        With `lookahead` the step after this one is queued on the device before this one's tokens are
-        read (its token ids stay on the device), when `_plan_ahead` allows it; the host's work then
-        overlaps the device's.  Every call still returns the tokens of exactly one step."""
-        fl = self._inflight
-        self._inflight = None
-        if fl is None:
-            plan = self.scheduler.schedule()
-            early = [StepOutput(r.rid, -1, True, r.status) for r in plan.failed]
-            if not plan.entries:
-                return early
-            fl = self._launch(plan, early=early)
-        ahead = self._plan_ahead(fl)
-        if ahead is not None:
-            self._inflight = self._launch(ahead, device_tokens=fl.tokens_dev)
-        return self._finish(fl)
+        """One engine step: schedule, run the batch, sample, finish.  Returns the new tokens."""
+        return self._outputs(capi.load().imp_step)
 
     def drain(self) -> List[StepOutput]:
         """Finish a step that was launched ahead, if any (its requests may all have ended already)."""
-        fl, self._inflight = self._inflight, None
-        return self._finish(fl) if fl is not None else []
+        return self._outputs(capi.load().imp_drain)
 
     def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
         """Generate for every prompt (continuous batching inside); returns the new tokens per prompt.
-
-        `params` is one GenerateParams for all prompts or a list with one per prompt.
-        """
+        `params` is one GenerateParams for all prompts or a list with one per prompt."""
         if prompts and isinstance(prompts[0], int):
             raise TypeError("generate takes a list of prompts (each a list of token ids)")
         plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
         reqs = [self.submit(p, q) for p, q in zip(prompts, plist)]
         for r in reqs:
             if r.status == RequestStatus.OUT_OF_MEMORY:
-                raise MemoryError(f"request {r.rid!r}: prompt plus max_tokens needs more cache pages than the "
-                                  f"pool of {self.cache.num_pages} holds")
-        while any(not r.done for r in reqs):
-            self.step()
-        if not self.scheduler.has_work():
+                raise MemoryError(f"request {r.rid!r}: prompt plus max_tokens needs more cache pages than the pool holds")
+        live = {r.rid for r in reqs}
+        while live:
+            for o in self.step():
+                if o.finished:
+                    live.discard(o.rid)
+            if live and not self.has_work():
+                break
+        if not self.has_work():
             self.drain()
-        failed = [r for r in reqs if r.status != RequestStatus.FINISHED]
+        failed = [r.rid for r in reqs if r.status != RequestStatus.FINISHED]
         if failed:
-            raise MemoryError(f"{len(failed)} request(s) ran out of cache pages: "
-                              f"{[r.rid for r in failed]}")
-        return [list(r.output) for r in reqs]
+            raise MemoryError(f"{len(failed)} request(s) ran out of cache pages: {failed}")
+        outs = [r.output for r in reqs]
+        for r in reqs:
+            r.release()
+        return outs
 
     # ------------------------------------------------------------- token level
-    def step_tokens(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Run given tokens as one batch (no scheduling, no sampling); logits of the wanted rows on the host."""
-        logits = self.stepper.step(entries)
-        out = logits.cpu()
-        self.stepper.check_device_status()
+    def _rid(self, rid: Hashable) -> int:
+        if rid not in self._ids:
+            self._ids[rid] = self._next_replay_id
+            self._next_replay_id += 1
+        return self._ids[rid]
+
+    def step_tokens(self, entries: Sequence[StepEntry]):
+        """Run given tokens as one batch (no scheduling, no sampling).  Returns the logits of the wanted rows
+        as a float32 numpy array [wanted, vocab], in the order of the entries and of each `want`."""
+        import numpy as np
+        n = len(entries)
+        arr = (capi.ImpStepEntry * max(n, 1))()
+        keep = []
+        wanted = 0
+        for i, e in enumerate(entries):
+            toks, nt = capi.int32_array([int(t) for t in e.tokens])
+            want, nw = capi.int32_array([int(w) for w in e.want])
+            keep += [toks, want]
+            arr[i].id = self._rid(e.rid)
+            arr[i].tokens = toks
+            arr[i].n_tokens = nt
+            arr[i].want = want
+            arr[i].n_want = nw
+            wanted += nw
+        out = np.empty((wanted, self.vocab_size), dtype=np.float32)
+        capi.check(capi.load().imp_step_tokens(self._ctx, arr, n, out.ctypes.data_as(ctypes.c_void_p), out.size))
         return out
 
     def end(self, rid: Hashable) -> None:
         """Give back what a `step_tokens` request holds."""
-        self.stepper.finish(rid)
+        capi.check(capi.load().imp_end(self._ctx, self._rid(rid)))
+        self._ids.pop(rid, None)

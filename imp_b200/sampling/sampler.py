@@ -1,28 +1,19 @@
-"""Per-request sampling parameters and the batched sampler over 32-bit logits.
+"""Sampling parameters and the library's batched sampler, for tools and tests.
 
 Parameter names and defaults follow the reference's ImpGenerateParams
-(include/imp/imp.h:61-85; defaults src/api/imp_api.cpp:76-102, src/runtime/
-request.h:40-57): temperature, top_k, top_p, min_p, typical_p, repetition /
-frequency / presence penalties with their window `repeat_last_n`, the DRY
-penalty, Mirostat v2, seed.  Order of application as in the reference
-(src/graph/executor.cu:43-115): penalties, DRY, then either Mirostat v2 (which
-takes the temperature and ignores the other filters) or min-p, typical-p and
-greedy if temperature <= 0 or top_k == 1, else top-k/top-p at the given
-temperature.  The uniform number of a draw is a function of (seed,
-step index of the request) alone, so a request's tokens do not depend on the
-batch it was sampled in; the reference re-seeds its generator with the same
-seed at every call (src/compute/sampling.cu:541-543) and so repeats one draw.
+(include/imp/imp.h:61-85; defaults src/api/imp_api.cpp:76-102).  The sampler
+itself (order of penalties, DRY, Mirostat v2, typical-p, min-p, top-k/top-p;
+counter-based uniform numbers) is csrc/host/sampler.cpp over the kernels of
+csrc/sampling.cu; `Sampler` here drives it on logits that already live on the
+device.
 """
 from __future__ import annotations
 
-import os
+import ctypes
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
-import numpy as np
-import torch
-
-from ..ops import kernels as K
+from .. import capi
 
 
 @dataclass
@@ -49,34 +40,14 @@ class SamplingParams:
     def greedy(cls) -> "SamplingParams":
         return cls(temperature=0.0, top_p=1.0, top_k=0)
 
-    def is_greedy(self) -> bool:
-        return self.mirostat != 2 and (self.temperature <= 0.0 or self.top_k == 1)
-
-    def has_penalties(self) -> bool:
-        return self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
-
-    def has_dry(self) -> bool:
-        return self.dry_multiplier > 0.0
-
-    def has_typical(self) -> bool:
-        return self.mirostat != 2 and 0.0 < self.typical_p < 1.0
-
-    def needs_history(self) -> bool:
-        return self.has_penalties() or self.has_dry()
-
-    def validate(self) -> None:
-        if self.top_k < 0:
-            raise ValueError("top_k must be >= 0")
-        if self.min_p < 0 or self.min_p > 1:
-            raise ValueError("min_p must be in [0, 1]")
-        if self.repetition_penalty <= 0:
-            raise ValueError("repetition_penalty must be positive")
-        if self.repeat_last_n < 0:
-            raise ValueError("repeat_last_n must be >= 0")
-        if self.mirostat not in (0, 2):
-            raise ValueError("mirostat must be 0 (off) or 2 (Mirostat v2)")
-        if self.dry_multiplier < 0 or self.dry_base <= 0 or self.dry_allowed_length < 0 or self.dry_penalty_last_n < 0:
-            raise ValueError("DRY parameters must not be negative (base positive)")
+    def to_c(self, max_tokens: int = 256, ignore_eos: bool = False) -> "capi.ImpGenerateParams":
+        p = capi.load().imp_generate_params_default()
+        for name, _ in capi.ImpGenerateParams._fields_:
+            if hasattr(self, name):
+                setattr(p, name, getattr(self, name))
+        p.max_tokens = max_tokens
+        p.ignore_eos = int(ignore_eos)
+        return p
 
 
 @dataclass
@@ -86,163 +57,74 @@ class SamplerState:
     mirostat_mu: Optional[float] = None
 
 
-def dry_penalties(tokens: Sequence[int], multiplier: float, base: float, allowed_length: int,
-                  last_n: int = 0) -> dict:
-    """The DRY penalty per token id, from the request's tokens so far.
-
-    For every position `pos` in the window, the length of the match between the tokens before
-    `pos` and the end of the sequence says how long a repetition would become if `tokens[pos]`
-    came next; longer than `allowed_length` costs multiplier * base ** (length - allowed_length),
-    the longest match per token counting (src/compute/sampling.cu:826-880).
-    """
-    n = len(tokens)
-    if multiplier <= 0.0 or n < 2:
-        return {}
-    t = np.asarray(tokens, dtype=np.int64)
-    start = max(0, n - last_n) if last_n > 0 else 0
-    best: dict = {}
-    # only positions preceded by the sequence's last token can match at all
-    for pos in (np.flatnonzero(t[start:n - 1] == t[n - 1]) + start + 1).tolist():
-        a, b, m = pos - 1, n - 1, 0
-        while a >= start and t[a] == t[b]:
-            m += 1
-            a -= 1
-            b -= 1
-        if m > allowed_length:
-            tok = int(t[pos])
-            if m > best.get(tok, 0):
-                best[tok] = m
-    return {tok: multiplier * float(base) ** (m - allowed_length) for tok, m in best.items()}
-
-
-_MASK = (1 << 64) - 1
-
-
-def resolve_seed(seed: int) -> int:
-    """A concrete 63-bit seed: `seed` itself, or fresh randomness for -1."""
-    if seed is None or seed < 0:
-        return int.from_bytes(os.urandom(8), "little") >> 1
-    return int(seed)
-
-
 def uniform_for(seed: int, step: int) -> float:
-    """The uniform number in [0, 1) of draw `step` of a request seeded with `seed` (splitmix64)."""
-    z = (seed * 0x9E3779B97F4A7C15 + (step + 1) * 0xBF58476D1CE4E5B9) & _MASK
-    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
-    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
-    z ^= z >> 31
-    return (z >> 40) / float(1 << 24)
+    """The uniform number in [0, 1) of draw `step` of a request seeded with `seed`."""
+    lib = capi.load()
+    lib.imp_uniform_for.restype = ctypes.c_float
+    lib.imp_uniform_for.argtypes = [ctypes.c_uint64, ctypes.c_int64]
+    return float(lib.imp_uniform_for(seed, step))
+
+
+def dry_penalties(tokens: Sequence[int], multiplier: float, base: float, allowed_length: int, last_n: int = 0) -> dict:
+    """The DRY penalty per token id, from the request's tokens so far."""
+    lib = capi.load()
+    lib.imp_dry_penalties.restype = ctypes.c_int
+    lib.imp_dry_penalties.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int, ctypes.c_float, ctypes.c_float,
+                                      ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int32),
+                                      ctypes.POINTER(ctypes.c_float), ctypes.c_int]
+    toks, n = capi.int32_array([int(t) for t in tokens])
+    cap = max(n, 1)
+    out_t, out_v = (ctypes.c_int32 * cap)(), (ctypes.c_float * cap)()
+    k = lib.imp_dry_penalties(toks, n, multiplier, base, allowed_length, last_n, out_t, out_v, cap)
+    return {int(out_t[i]): float(out_v[i]) for i in range(min(k, cap))}
 
 
 class Sampler:
-    """Turns the logits rows of a step into one token per row."""
+    """Turns rows of logits on the device into one token per row, through the library's sampler."""
 
-    def __init__(self, vocab_size: int, max_rows: int, device):
-        self.V, self.max_rows, self.device = vocab_size, max_rows, device
-        self._counts: Optional[torch.Tensor] = None  # [max_rows, V] int32, made on first use of penalties
+    def __init__(self, vocab_size: int, max_rows: int, device="cuda:0"):
+        from ..parts.bench import PartBench
+        index = int(str(device).split(":")[1]) if ":" in str(device) else 0
+        self.V = vocab_size
+        self._bench = PartBench("float32", [], device_id=index)
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None,
+    def sample(self, logits, params: Sequence[SamplingParams], seeds: Sequence[int], steps: Sequence[int],
+               histories: Optional[Sequence[Sequence[int]]] = None,
                states: Optional[Sequence[SamplerState]] = None) -> List[int]:
-        """logits [R, V] float32 on the device (modified in place by penalties and filters); returns R token ids.
-
-        `seeds[r]`, `steps[r]` key the uniform number of row r; `histories[r]` are the request's
-        tokens so far (prompt and output), used by the penalties and DRY; `states[r]` carries
-        Mirostat's mu between calls (needed only for rows that use Mirostat).
-        """
-        if logits.shape[0] == 0:
-            return []
-        return self.sample_device(logits, params, seeds, steps, histories, states).tolist()
-
-    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-                      steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None,
-                      states: Optional[Sequence[SamplerState]] = None) -> torch.Tensor:
-        """`sample` with the token ids left on the device (int32 [R]).  Without Mirostat rows nothing
-        here waits for the device, so the caller can queue more work before it reads the tokens."""
+        """logits [R, V] float32 on the device (a torch tensor; modified in place by penalties and filters)."""
+        import torch
         R = logits.shape[0]
         if R == 0:
-            return torch.empty(0, dtype=torch.int32, device=self.device)
-        assert len(params) == R and len(seeds) == R and len(steps) == R
-        histories = histories or [[] for _ in range(R)]
-        if any(p.has_penalties() for p in params):
-            self._penalties(logits, params, histories)
-        if any(p.has_dry() for p in params):
-            self._dry(logits, params, histories)
-        if any(p.has_typical() for p in params):
-            tp = torch.tensor([[p.typical_p if p.has_typical() else 1.0 for p in params],
-                               [p.min_p for p in params]], dtype=torch.float32, device=self.device)
-            K.typical_filter(logits, tp[0], tp[1])
-        if all(p.is_greedy() for p in params):
-            return K.argmax(logits)
-        f = np.empty((5, R), dtype=np.float32)
-        k = np.empty((2, R), dtype=np.int32)
-        miro = [r for r, p in enumerate(params) if p.mirostat == 2]
-        if miro and states is None:
+            return []
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.is_cuda
+        if any(p.mirostat == 2 for p in params) and states is None:
             raise ValueError("Mirostat needs the requests' SamplerState objects")
-        for r, p in enumerate(params):
-            f[0, r] = 0.0 if (p.is_greedy() or p.mirostat == 2) else p.temperature
-            f[1, r] = p.top_p if 0.0 < p.top_p < 1.0 else 1.0
-            f[2, r] = p.min_p
-            f[3, r] = uniform_for(seeds[r], steps[r])
-            f[4, r] = 0.0
-            k[0, r] = p.top_k
-            k[1, r] = 0
-        for r in miro:
-            st = states[r]
-            if st.mirostat_mu is None:
-                st.mirostat_mu = 2.0 * params[r].mirostat_tau
-            f[4, r] = st.mirostat_mu
-            k[1, r] = 1
-        fd = torch.from_numpy(f).to(self.device)
-        kd = torch.from_numpy(k).to(self.device)
-        out = K.sample(logits, fd[0], kd[0], fd[1], fd[2], fd[3])
-        if miro:
-            temp = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=self.device)
-            surprise = torch.zeros(R, dtype=torch.float32, device=self.device)
-            K.sample_mirostat(logits, kd[1], temp, fd[4], fd[3], out, surprise)
-            sur = surprise.tolist()          # waits for the device: mu is host state
-            for r in miro:
-                p = params[r]
-                states[r].mirostat_mu -= p.mirostat_eta * (sur[r] - p.mirostat_tau)
-        return out
-
-    def _dry(self, logits, params, histories) -> None:
-        rows: List[int] = []
-        toks: List[int] = []
-        vals: List[float] = []
-        V = logits.shape[1]
-        for r, (p, h) in enumerate(zip(params, histories)):
-            if not p.has_dry():
-                continue
-            for tok, v in dry_penalties(h, p.dry_multiplier, p.dry_base, p.dry_allowed_length,
-                                        p.dry_penalty_last_n).items():
-                if 0 <= tok < V:
-                    rows.append(r)
-                    toks.append(tok)
-                    vals.append(v)
-        if not rows:
-            return
-        it = torch.tensor([rows, toks], dtype=torch.int32, device=self.device)
-        K.sparse_subtract(logits, it[0], it[1], torch.tensor(vals, dtype=torch.float32, device=self.device))
-
-    def _penalties(self, logits, params, histories) -> None:
-        R = logits.shape[0]
-        if self._counts is None or self._counts.shape[0] < R:
-            self._counts = torch.empty((max(R, self.max_rows), self.V), dtype=torch.int32, device=self.device)
-        flat: List[int] = []
-        start = [0]
-        max_hist = 0
-        for p, h in zip(params, histories):
-            h = list(h) if p.has_penalties() else []
-            if p.repeat_last_n > 0:
-                h = h[-p.repeat_last_n:]
-            flat.extend(h)
-            start.append(len(flat))
-            max_hist = max(max_hist, len(h))
-        if max_hist == 0:
-            return
-        hist = torch.tensor(flat, dtype=torch.int32, device=self.device)
-        hs = torch.tensor(start, dtype=torch.int32, device=self.device)
-        pen = torch.tensor([[p.repetition_penalty for p in params], [p.frequency_penalty for p in params],
-                            [p.presence_penalty for p in params]], dtype=torch.float32, device=self.device)
-        K.apply_penalties(logits, hist, hs, max_hist, pen[0], pen[1], pen[2], self._counts)
+        lib = capi.load()
+        lib.imp_bench_sample.restype = ctypes.c_int
+        lib.imp_bench_sample.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                         ctypes.POINTER(capi.ImpGenerateParams), ctypes.POINTER(ctypes.c_int64),
+                                         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int32),
+                                         ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float),
+                                         ctypes.POINTER(ctypes.c_int32)]
+        cp = (capi.ImpGenerateParams * R)(*[p.to_c() for p in params])
+        cs = (ctypes.c_int64 * R)(*[int(s) for s in seeds])
+        ct = (ctypes.c_int64 * R)(*[int(s) for s in steps])
+        histories = histories or [[] for _ in range(R)]
+        flat = [int(t) for h in histories for t in h]
+        starts = [0]
+        for h in histories:
+            starts.append(starts[-1] + len(h))
+        ch, _ = capi.int32_array(flat)
+        chs, _ = capi.int32_array(starts)
+        nan = float("nan")
+        mu = (ctypes.c_float * R)(*[nan if states is None or states[r].mirostat_mu is None else states[r].mirostat_mu
+                                    for r in range(R)])
+        out = (ctypes.c_int32 * R)()
+        torch.cuda.current_stream(logits.device).synchronize()
+        capi.check(lib.imp_bench_sample(self._bench.handle, logits.data_ptr(), logits.stride(0), R, self.V, cp, cs, ct, ch,
+                                        chs, mu, out))
+        if states is not None:
+            for r in range(R):
+                if mu[r] == mu[r]:
+                    states[r].mirostat_mu = float(mu[r])
+        return list(out)
