@@ -100,6 +100,10 @@ class _Slots:
     def n_free(self) -> int:
         return self._mgr.info()["free_slots"]
 
+    @property
+    def num_pages(self) -> int:
+        return self._mgr.info()["slots"]
+
 
 class CacheManager:
     """`layer_specs[j]` is what run position j asks for (a PagedKVSpec, a StateSpec or None)."""

@@ -165,6 +165,8 @@ _SIGNATURES = {
     "imp_context_free": (None, [_H]),
     "imp_context_reset": (_E, [_H]),
     "imp_context_info_json": (c_char_p, [_H]),
+    "imp_context_set_eos": (_E, [_H, POINTER(c_int32), c_int]),
+    "imp_context_check": (_E, [_H]),
     "imp_submit": (_E, [_H, POINTER(c_int32), c_int, POINTER(ImpGenerateParams), POINTER(c_int64)]),
     "imp_cancel": (_E, [_H, c_int64]),
     "imp_step": (_E, [_H, POINTER(ImpStepOutput), c_int, POINTER(c_int)]),
@@ -196,6 +198,7 @@ _SIGNATURES = {
     "imp_bench_create": (_E, [c_int, c_int, c_char_p, c_int, c_int, c_int, c_int, c_int, POINTER(_H)]),
     "imp_bench_free": (None, [_H]),
     "imp_bench_build_part": (_E, [_H, c_char_p, c_char_p, c_int, POINTER(c_char_p), POINTER(ImpTensor), POINTER(c_void_p)]),
+    "imp_bench_build_block": (_E, [_H, c_char_p, c_char_p, c_int, POINTER(c_char_p), POINTER(c_void_p), POINTER(c_void_p)]),
     "imp_bench_prepare": (_E, [_H, POINTER(ImpStepEntry), c_int, POINTER(POINTER(ImpBatchView))]),
     "imp_bench_cache_view": (_E, [_H, c_int, c_int, POINTER(POINTER(ImpCacheView))]),
     "imp_bench_commit": (_E, [_H]),

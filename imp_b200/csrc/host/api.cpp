@@ -229,6 +229,20 @@ IMP_EXPORT ImpError imp_context_reset(ImpContext ctx) {
     IMP_CATCH
 }
 
+IMP_EXPORT ImpError imp_context_set_eos(ImpContext ctx, const int32_t* ids, int n) {
+    IMP_TRY
+    need_arg(ctx && (ids || n == 0) && n >= 0, "imp_context_set_eos: null argument");
+    ctx->e->set_eos(std::vector<int>(ids, ids + n));
+    IMP_CATCH
+}
+
+IMP_EXPORT ImpError imp_context_check(ImpContext ctx) {
+    IMP_TRY
+    need_arg(ctx != nullptr, "imp_context_check: ctx must not be null");
+    ctx->e->check_invariants();
+    IMP_CATCH
+}
+
 IMP_EXPORT const char* imp_context_info_json(ImpContext ctx) {
     if (!ctx) return "";
     try {
@@ -561,7 +575,8 @@ IMP_EXPORT ImpError imp_bench_build_part(ImpBench b, const char* category, const
         if (!have && !s.second.optional) fail(IMP_ERROR_INVALID_ARG, std::string(category) + " '" + spec.kind + "' needs its tensor '" + s.first + "'");
     }
     IMP_CUDA(cudaStreamSynchronize(b->dev->rt.stream));
-    Part* p = b->factory->build(category, spec, placed);
+    // parts without tensors are shared between equal specs, as in a model
+    Part* p = (placed.empty() && specs.empty()) ? b->factory->shared(category, spec.to_json()) : b->factory->build(category, spec, placed);
     if (Mixer* m = dynamic_cast<Mixer*>(p)) {
         m->tiling_ids.clear();
         for (const TilingSpec& t : m->tilings()) {
@@ -571,6 +586,28 @@ IMP_EXPORT ImpError imp_bench_build_part(ImpBench b, const char* category, const
         }
     }
     *out = (ImpPart)p;
+    IMP_CATCH
+}
+
+IMP_EXPORT ImpError imp_bench_build_block(ImpBench b, const char* kind, const char* params_json, int n_parts,
+                                          const char* const* slot_names, const ImpPart* parts, ImpPart* out) {
+    IMP_TRY
+    need_arg(b && kind && out && (n_parts == 0 || (slot_names && parts)), "imp_bench_build_block: null argument");
+    *out = nullptr;
+    b->dev->make_current();
+    PartSpec spec;
+    spec.kind = kind;
+    if (params_json && *params_json) spec.params = Json::parse(params_json, "block params");
+    const PartClass& cls = part_class("block", spec.kind);
+    std::vector<std::pair<std::string, Part*>> given;
+    for (int i = 0; i < n_parts; ++i) given.emplace_back(slot_names[i], (Part*)parts[i]);
+    if (cls.part_slots)
+        for (const auto& slot : cls.part_slots(spec.params)) {
+            bool have = false;
+            for (const auto& g : given) have = have || g.first == slot.name;
+            if (!have) fail(IMP_ERROR_INVALID_ARG, std::string("block '") + kind + "' needs a part in its slot '" + slot.name + "'");
+        }
+    *out = (ImpPart)b->factory->build("block", spec, {}, given);
     IMP_CATCH
 }
 

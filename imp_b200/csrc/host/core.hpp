@@ -177,6 +177,7 @@ struct Runtime {
     int sm_count = 0;
     int64_t fallback_calls = 0;     // matrix products that ran on the plain fallback kernel
     int64_t launches = 0;           // launcher calls of this library
+    int64_t split_norm_calls = 0;   // norms that added the unsummed parts of a product themselves
     bool is_f32() const { return dtype == F32; }
     Tensor empty(int64_t rows, int64_t cols, int dt = -1, bool step = false) {
         const int d = dt < 0 ? dtype : dt;

@@ -251,8 +251,11 @@ Json Engine::info_json() const {
     j["scheduler"] = sched_->info_json();
     j["max_seq_len"] = max_seq_len_;
     j["steps"] = steps_;
+    j["inflight"] = inflight_ != nullptr;
+    j["eos_token_ids"] = Json::array_of(eos_);
     j["launches"] = dev_->rt.launches;
     j["fallback_calls"] = dev_->rt.fallback_calls;
+    j["split_norm_calls"] = dev_->rt.split_norm_calls;
     j["graph_replays"] = stepper_->graph_replays;
     j["graph_captures"] = stepper_->graph_captures;
     j["eager_steps"] = stepper_->eager_steps;

@@ -55,6 +55,8 @@ public:
     int max_seq_len() const { return max_seq_len_; }
     int64_t vocab_size() const { return model_->vocab_size(); }
     void make_current() const { dev_->make_current(); }
+    void set_eos(const std::vector<int>& ids) { eos_ = ids; }      // for requests submitted from now on
+    void check_invariants() const { cache_->check_invariants(); }
     // the reference's token-level pair (one request at a time)
     int64_t single_rid = -1;
     size_t single_read = 0;

@@ -233,6 +233,7 @@ void add_rmsnorm(Runtime& rt, Tensor h, const Branch& branch, const Tensor& weig
                                              rows_idx, n_out, d, eps, offset, out.dtype, weight.dtype, write_h, rt.stream);
         if (rc != -2) {
             ++rt.launches;
+            ++rt.split_norm_calls;
             check_launch(rc, "add_rmsnorm_split");
             return;
         }

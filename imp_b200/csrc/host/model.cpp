@@ -379,9 +379,13 @@ Json DeviceModel::info_json() const {
         tl.push(o);
     }
     j["tilings"] = tl;
-    Json defer = Json::array();
-    for (const Block* b : blocks_) defer.push(Json(b->defer_pending));
+    Json defer = Json::array(), mixer_defer = Json::array();
+    for (const Block* b : blocks_) {
+        defer.push(Json(b->defer_pending));
+        mixer_defer.push(Json(b->mixer() ? b->mixer()->defer_out : false));
+    }
     j["defer_pending"] = defer;
+    j["mixer_defer_out"] = mixer_defer;
     if (diag_) {
         if (diag_->profile) j["profile"] = diag_->profile_json();
         if (diag_->debug) {

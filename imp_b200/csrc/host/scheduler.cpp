@@ -163,6 +163,7 @@ void Scheduler::preempt(Request* victim, StepPlan& plan) {
     for (const auto& e : plan.entries) plan.pages += pages_needed(e.request, e.start + e.n_tokens);
     victim->status = IMP_REQUEST_WAITING;
     victim->n_preempted += 1;
+    ++preemptions;
     waiting.push_front(victim);
     plan.preempted.push_back(victim);
 }
@@ -288,6 +289,7 @@ Json Scheduler::info_json() const {
     for (const Request* q : running) r.push(Json(q->rid));
     j["waiting"] = w;
     j["running"] = r;
+    j["preemptions"] = preemptions;
     Json reqs = Json::object();
     for (const auto& kv : by_id_) {
         const Request& q = *kv.second;

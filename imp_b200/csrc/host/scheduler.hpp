@@ -107,6 +107,7 @@ public:
     std::deque<Request*> waiting;
     std::vector<Request*> running;   // in admission order
     int max_batch_size, max_batch_tokens, prefill_chunk_size, max_seq_len;
+    int64_t preemptions = 0;         // requests sent back to the queue for lack of pages, in all
     Json info_json() const;
 
 private:

@@ -248,6 +248,26 @@ class Engine:
         """State of the context: cache groups and free pages, run positions, counters."""
         return json.loads(capi.text(capi.load().imp_context_info_json(self._ctx)))
 
+    @property
+    def eos_token_ids(self):
+        return tuple(self.info()["eos_token_ids"])
+
+    @eos_token_ids.setter
+    def eos_token_ids(self, ids) -> None:
+        arr, n = capi.int32_array([int(t) for t in ids])
+        capi.check(capi.load().imp_context_set_eos(self._ctx, arr, n))
+
+    def free_pages(self) -> int:
+        return self.info()["cache"]["free_pages"]
+
+    @property
+    def num_pages(self) -> int:
+        return self.info()["cache"]["num_pages"]
+
+    def check_invariants(self) -> None:
+        """The cache manager's invariants (no page lost, held twice or freed twice)."""
+        capi.check(capi.load().imp_context_check(self._ctx))
+
     def reset(self) -> None:
         capi.check(capi.load().imp_context_reset(self._ctx))
         self._ids.clear()

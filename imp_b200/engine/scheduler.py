@@ -87,6 +87,8 @@ class Scheduler:
     def __init__(self, cache: CacheManager, max_batch_size: int, max_batch_tokens: int, prefill_chunk_size: int = 0,
                  max_seq_len: int = 4096):
         self.cache = cache
+        self.max_batch_size, self.max_batch_tokens = max_batch_size, max_batch_tokens
+        self.prefill_chunk_size, self.max_seq_len = prefill_chunk_size, max_seq_len
         h = ctypes.c_void_p()
         capi.check(capi.load().imp_scheduler_create(cache.handle, max_batch_size, max_batch_tokens, prefill_chunk_size,
                                                     max_seq_len, ctypes.byref(h)))

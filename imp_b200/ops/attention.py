@@ -1,14 +1,9 @@
-"""Choice of the attention kernel for a step, and the per-head-size tensor-core kernels.
+"""Raw launchers of the per-head-size attention kernels on torch tensors, for kernel tests and tools.
 
-float32: always the plain kernel (fixed reduction order per token).
-bfloat16: the MMA kernels of csrc/variants/attention_mma.cu, compiled on first use for the model's
-head size: the split-key decode kernel when every sequence brings one token, else the tiled
-prefill kernel (a decode token beside prompt portions is a tile of one row).  The step function
-cuts every sequence's new tokens into tiles of `engine.step.ATTENTION_TILE` = 32 tokens.
-For head sizes 64 and 128 and page sizes 8..128 (powers of two) the portions of at least
-`ATTENTION_WIDE_MIN` tokens go to the tensor-memory kernel of csrc/variants/attention_tc.cu in
-tiles of 128 tokens instead, and only the short ones to the 32-token kernel
-(`IMP_B200_ATTN_PREFILL=mma` keeps everything on the latter).
+The libraries of csrc/variants/attention_mma.cu (split-key decode kernel, 32-token prefill kernel)
+and csrc/variants/attention_tc.cu (tensor-memory prefill kernel, head sizes 64 and 128) are built
+on first use for a head size.  Which of them a step of the engine runs is decided in
+csrc/host/attention.cpp; `decode_splits` here asks the library for its choice of key splits.
 """
 from __future__ import annotations
 
@@ -24,9 +19,6 @@ from . import library as L
 
 _variants: Dict[int, ctypes.CDLL] = {}
 
-# CTAs the decode kernel should reach before it stops splitting the keys further: three resident
-# CTAs of 128 threads per SM (register-bound) on 148 SMs.
-DECODE_TARGET_CTAS = 148 * 3
 DECODE_MAX_SPLITS = 32
 
 
@@ -126,34 +118,10 @@ def _check(lib, rc: int, what: str) -> None:
         raise L.KernelError(f"{what} failed ({rc}): {lib.imp_last_error().decode(errors='replace')}")
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16) -> int:
-    """Key splits of the decode kernel: a function of the batch size alone (a captured graph must not
-    depend on the context length); short contexts simply leave the later splits empty.
-
-    The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with
-    fewer (token, kv head) pairs than such slots the keys are split until the slots are full.  With
-    more, the split count with the least modelled time is taken.  The model (fitted to measurements at
-    40 to 128 sequences): a CTA alone streams about 1/150 of what the device can, so a wave of CTAs
-    runs at full speed from 150 CTAs up, and a last wave of fewer runs as slowly as each of its CTAs;
-    splitting costs the merge kernel and the partial results, about a tenth of one CTA's work."""
-    base = n_tokens * n_kv_heads * ((group + 15) // 16)
-    if page_size % 16:
-        return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_CTAS // max(base, 1)))
-    slots = 2 * 148
-    if base <= slots:
-        # the largest power of two that keeps every CTA resident at once (measured: 16 splits beat 18 at two
-        # sequences, 8 beat 9 at four, although the latter fill more slots)
-        s = max(1, min(DECODE_MAX_SPLITS, slots // base))
-        return 1 << (s.bit_length() - 1)
-    saturating = 150.0
-
-    def modelled_time(s: int) -> float:
-        ctas = base * s
-        full, tail = divmod(ctas, slots)
-        t = full * slots / saturating + (tail / min(saturating, tail) if tail else 0.0)
-        return t / s + (0.1 + 0.01 * s if s > 1 else 0.0)
-
-    return min(range(1, 9), key=modelled_time)
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16, sm_count: int = 148) -> int:
+    """Key splits of the decode kernel as the library chooses them (csrc/host/attention.cpp `decode_splits`):
+    a function of the batch size alone, since a captured graph must not depend on the context length."""
+    return int(L.load().imp_op_decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count))
 
 
 def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,
@@ -235,22 +203,3 @@ def prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache,
         page_size, num_pages, float(scale), int(window), None if status is None else status.data_ptr(),
         torch.cuda.current_stream().cuda_stream), "attention prefill")
     return out
-
-
-def paged_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx, scale, window, rt):
-    if rt.is_float32:
-        return K.paged_attention_generic(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
-                                         ctx.seq_of_token, ctx.positions, scale, window, rt.status)
-    if ctx.decode_only:
-        return decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
-                                ctx.seq_of_token, ctx.positions, scale, window, rt.status)
-    wide = getattr(ctx, "wide_tile_tok0", None)
-    if wide is not None and wide.numel() and prefill_tc_supported(head_dim, q, out, k_cache):
-        prefill_attention_tc(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx.seq_of_token,
-                             ctx.positions, ctx.wide_tile_tok0, ctx.wide_tile_rows, scale, window, rt.status)
-        if ctx.rest_tile_tok0.numel():
-            prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, ctx.seq_of_token,
-                              ctx.positions, ctx.rest_tile_tok0, ctx.rest_tile_rows, scale, window, rt.status)
-        return out
-    return prefill_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table,
-                             ctx.seq_of_token, ctx.positions, ctx.tile_tok0, ctx.tile_rows, scale, window, rt.status)

@@ -1,12 +1,15 @@
-"""Tensor-level wrappers of the CUDA entry points.
+"""Raw kernel launchers on torch tensors, for kernel tests, tools and measurement.
 
 Each function checks shapes and dtypes, then launches on torch's current
-stream.  Nothing here computes with torch: tensors are only memory.  Element
-types are bfloat16 or float32; `linear` picks the matrix kernel by the weight's
-type and the number of rows.
+stream.  Nothing here computes with torch: tensors are only memory.  The
+engine itself does not come here: its host is C++ (csrc/host).  `linear`,
+`linear_swiglu` and `add_rmsnorm` call the library's own choice of kernel
+(csrc/host/linear.cpp), so that what a test or a measurement sees is what the
+engine runs.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -16,20 +19,7 @@ from . import library as L
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
-# bfloat16 matrix products beyond the weight-streaming kernel's rows: "tcgen05" = this library's TMA + tcgen05
-# kernels (csrc/gemm_tc.cu), "cublas" = the library GEMM through torch.mm (what the reference's engine calls for
-# its T>1 products, src/compute/gemm.cu:303-445; kept as a yardstick).  IMP_B200_GEMM overrides the default.
-import os as _os
-
-LARGE_M_BACKEND = _os.environ.get("IMP_B200_GEMM", "tcgen05")
-if LARGE_M_BACKEND not in ("tcgen05", "cublas"):
-    raise ValueError(f"IMP_B200_GEMM must be 'tcgen05' or 'cublas', got {LARGE_M_BACKEND!r}")
-
-# Which kernel takes a bfloat16 product, by its rows (see linear): the weight-streaming kernel (csrc/gemm_stream.cu)
-# up to STREAM_M_MAX, the tcgen05 kernels above; with IMP_B200_GEMM=cublas the streaming kernel up to SMALL_M_MAX
-# and the library above.
 SMALL_M_MAX = 16        # most rows the weight-streaming kernel takes
-STREAM_M_MAX = 7         # rows up to which it is the first choice (measured: from 8 rows the tcgen05 swap-AB kernel wins)
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -102,34 +92,26 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(F // b, b, d), up.view(F // b, b, d)], dim=1).reshape(2 * F, d).contiguous()
 
 
+def _view(t: Optional[torch.Tensor]):
+    from ..parts.base import to_imp
+    return to_imp(t)
+
+
+def _op_check(rc: int, what: str) -> None:
+    L.launch_calls += 1
+    if rc != 0:
+        raise L.KernelError(f"{what} failed ({rc}): {L.load().imp_op_error_message().decode(errors='replace')}")
+
+
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
-    """out[M, F] = silu(x Wg^T) * (x Wu^T) with Wg and Wu interleaved by `interleave_gate_up`.
-    Few bfloat16 rows: one fused kernel; otherwise the product, then the activation kernel."""
-    M = x.shape[0]
-    F = out.shape[1]
-    if M == 0:
+    """out[M, F] = silu(x Wg^T) * (x Wu^T) with Wg and Wu interleaved by `interleave_gate_up`: the library's
+    choice of kernel (csrc/host/linear.cpp `linear_swiglu`)."""
+    _need_cuda(out, x, w_interleaved)
+    if x.shape[0] == 0:
         return out
-    bf16 = x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == x.dtype
-    if (bf16 and STREAM_M_MAX < M <= SMALL_M_MAX and LARGE_M_BACKEND == "tcgen05"
-            and gemm_bf16_tc_swap(out, x, w_interleaved, TC_OUT_SWIGLU)):
-        return out
-    if bf16 and M <= SMALL_M_MAX:
-        assert x.stride(1) == 1 and w_interleaved.stride(1) == 1 and out.stride(1) == 1
-        rc = L.load().imp_gemm_bf16_stream_swiglu(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0),
-                                                  w_interleaved.data_ptr(), w_interleaved.stride(0), M, 2 * F,
-                                                  x.shape[1], _stream())
-        if rc != -2:
-            L.check(rc, "gemm_bf16_stream_swiglu")
-            return out
-    if (LARGE_M_BACKEND == "tcgen05" and x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16
-            and out.dtype == torch.bfloat16):
-        if M <= TC_SWAP_MAX_M and gemm_bf16_tc_swap(out, x, w_interleaved, TC_OUT_SWIGLU):
-            return out
-        if gemm_bf16_tc(out, x, w_interleaved, TC_OUT_SWIGLU):
-            return out
-    gu = torch.empty((M, 2 * F), dtype=x.dtype, device=x.device)
-    linear(gu, x, w_interleaved)
-    return swiglu(out, gu, SWIGLU_INTERLEAVE)
+    o, a, w = _view(out), _view(x), _view(w_interleaved)
+    _op_check(L.load().imp_op_linear_swiglu(ctypes.byref(o), ctypes.byref(a), ctypes.byref(w), _stream(), None), "linear_swiglu")
+    return out
 
 
 def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
@@ -139,22 +121,22 @@ def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     return dst
 
 
-DEFER_SPLIT_SUMS = _os.environ.get("IMP_B200_DEFER_SUM", "1") != "0"   # 0: always run the summing kernel
-
-
 class SplitSum:
     """A matrix product whose contraction was cut over CTAs and whose parts have not been added yet.
 
-    `parts` [n_splits, M, N] float32 holds what each split contributes; the value is their sum in split order,
-    rounded to `out`'s type, and `out` [M, N] is where it belongs.  `linear(..., may_defer=True)` returns one
-    instead of a tensor when that saves the summing kernel; `add_rmsnorm` takes one and adds the parts while it
-    reads them.  Anyone else calls `summed()` first.  (The rotary kernel adding the parts of the q, k, v product
-    was tried too and measured slower than the summing kernel before it.)"""
+    `parts` [n_splits, M, N] float32 (in the library's scratch: valid until the call after next) holds what
+    each split contributes; the value is their sum in split order, rounded to `out`'s type, and `out` [M, N]
+    is where it belongs.  `linear(..., may_defer=True)` returns one instead of a tensor when that saves the
+    summing kernel; `add_rmsnorm` takes one and adds the parts while it reads them.  Anyone else calls
+    `summed()` first."""
 
-    __slots__ = ("out", "parts", "n_splits")
+    __slots__ = ("out", "parts_ptr", "n_splits", "_parts")
 
-    def __init__(self, out: torch.Tensor, parts: torch.Tensor, n_splits: int):
-        self.out, self.parts, self.n_splits = out, parts, n_splits
+    def __init__(self, out: torch.Tensor, parts, n_splits: int):
+        # parts: an address in the library's scratch, or a tensor [n_splits, M, N] float32 of the caller's
+        self._parts = parts
+        self.out, self.n_splits = out, n_splits
+        self.parts_ptr = parts.data_ptr() if hasattr(parts, "data_ptr") else int(parts)
 
     @property
     def shape(self):
@@ -164,7 +146,7 @@ class SplitSum:
         """Add the parts into `out` (the separate summing kernel) and return it."""
         M, N = self.out.shape
         epi = TC_OUT_F32 if self.out.dtype == torch.float32 else TC_OUT_BF16
-        L.check(L.load().imp_gemm_bf16_tc_swap_sum(self.out.data_ptr(), self.out.stride(0), epi, self.parts.data_ptr(),
+        L.check(L.load().imp_gemm_bf16_tc_swap_sum(self.out.data_ptr(), self.out.stride(0), epi, self.parts_ptr,
                                                    M, N, self.n_splits, _stream()), "gemm_bf16_tc_swap_sum")
         return self.out
 
@@ -178,42 +160,18 @@ def add_rmsnorm(h: torch.Tensor, branch, weight: torch.Tensor, out: torch.Tensor
                 eps: float, weight_offset: float = 0.0, rows: Optional[torch.Tensor] = None,
                 write_h: bool = True) -> torch.Tensor:
     """h (+= branch); out = rmsnorm(h) * (weight + offset).  With `rows`, output row r reads stream row rows[r]
-    and h is left untouched.  `branch` may be a SplitSum: its parts are added on the way."""
-    if isinstance(branch, SplitSum):
-        sp = branch
-        _need_cuda(h, sp.parts, weight, out, rows)
-        d = h.shape[1]
-        assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous() and out.shape[1] == d
-        assert weight.numel() == d and weight.is_contiguous()
-        assert sp.out.shape == h.shape and sp.out.dtype == out.dtype and sp.parts.is_contiguous()
-        n_out = out.shape[0]
-        if rows is not None:
-            assert rows.dtype == torch.int32 and rows.numel() == n_out and rows.is_contiguous()
-            write_h = False
-        else:
-            assert n_out == h.shape[0]
-        rc = L.load().imp_add_rmsnorm_split(h.data_ptr(), sp.parts.data_ptr(), sp.parts.stride(0), sp.n_splits,
-                                            weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, d, float(eps),
-                                            float(weight_offset), _dt(out), _dt(weight), 1 if write_h else 0, _stream())
-        if rc != -2:
-            L.check(rc, "add_rmsnorm_split")
-            return out
-        branch = sp.summed()
-    _need_cuda(h, branch, weight, out, rows)
-    d = h.shape[1]
-    assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous() and out.shape[1] == d
-    assert weight.numel() == d and weight.is_contiguous()
-    if branch is not None:
-        assert branch.shape == h.shape and branch.dtype == out.dtype and branch.is_contiguous()
-    n_out = out.shape[0]
+    and h is left untouched.  `branch` may be a SplitSum: its parts are added on the way.  The library's own
+    choice of kernel (csrc/host/linear.cpp `add_rmsnorm`)."""
+    sp = branch if isinstance(branch, SplitSum) else None
+    bt = sp.out if sp is not None else branch
+    _need_cuda(h, bt, weight, out, rows)
+    hv, bv, wv, ov = _view(h), _view(bt), _view(weight), _view(out)
     if rows is not None:
-        assert rows.dtype == torch.int32 and rows.numel() == n_out and rows.is_contiguous()
-        write_h = False
-    else:
-        assert n_out == h.shape[0]
-    L.check(L.load().imp_add_rmsnorm(h.data_ptr(), _ptr(branch), weight.data_ptr(), out.data_ptr(), _ptr(rows),
-                                     n_out, d, float(eps), float(weight_offset), _dt(out), _dt(weight),
-                                     1 if write_h else 0, _stream()), "add_rmsnorm")
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+    _op_check(L.load().imp_op_add_rmsnorm(ctypes.byref(hv), ctypes.byref(bv) if bt is not None else None,
+                                          sp.parts_ptr if sp is not None else None, sp.n_splits if sp is not None else 0,
+                                          ctypes.byref(wv), ctypes.byref(ov), float(eps), float(weight_offset),
+                                          _ptr(rows), rows.numel() if rows is not None else 0, _stream()), "add_rmsnorm")
     return out
 
 
@@ -277,7 +235,7 @@ def linear_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor, n
     Returns False, having done nothing, when the shape or the backend rules the fused kernel out
     (fewer than 256 rows, a head size other than 64 / 128, alignment, IMP_B200_GEMM=cublas): the caller
     then uses `linear` and `qk_norm_rope_kv_write`."""
-    if LARGE_M_BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16:
+    if x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16:
         return False
     T, Kd = x.shape
     if T < 256 or head_dim not in (64, 128) or cos.shape[1] * 2 != head_dim:
@@ -417,84 +375,28 @@ def gemm_bf16_tc_swap(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
     return True
 
 
-def gemm_bf16_tc_swap_partials(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor,
-                               status: Optional[torch.Tensor] = None) -> Optional[SplitSum]:
-    """a[M,K] @ w[N,K]^T left as the partial results of the K splits of the swap-AB tcgen05 kernel; None where
-    that kernel would not split this shape (or cannot take it)."""
-    _need_cuda(out, a, w)
-    M, K = a.shape
-    N = w.shape[0]
-    assert w.shape[1] == K and a.dtype == w.dtype == torch.bfloat16 and M <= TC_SWAP_MAX_M and out.shape == (M, N)
-    assert a.stride(1) == 1 and w.stride(1) == 1
-    lib = L.load()
-    n_splits = lib.imp_gemm_bf16_tc_swap_splits(M, N, K)
-    if n_splits < 2:
-        return None
-    parts = torch.empty((n_splits, M, N), dtype=torch.float32, device=a.device)
-    rc = lib.imp_gemm_bf16_tc_swap_partials(parts.data_ptr(), a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0),
-                                            M, N, K, _ptr(status), _stream())
-    if rc == -2:
-        return None
-    L.check(rc, "gemm_bf16_tc_swap_partials")
-    return SplitSum(out, parts, n_splits)
-
-
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, may_defer: bool = False):
-    """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation.
+    """out[M,N] = x[M,K] @ w[N,K]^T with 32-bit accumulation: the library's choice of kernel
+    (csrc/host/linear.cpp `linear`).
 
-    may_defer: the caller hands the result to add_rmsnorm (or calls summed() on it), so a
-    product the tcgen05 kernel splits over K may come back as a SplitSum, its summing kernel saved.
-
-    float32 x float32 -> the plain FFMA kernel (never a reduced-precision mode).
-    bfloat16 x bfloat16 -> by rows: the weight-streaming kernel (up to 7), the swap-AB tcgen05 kernel (up to 128, and
-    long contractions at any row count), the persistent tcgen05 kernel (up to 255), CTA pairs (more); shapes the TMA
-    descriptors cannot take, and IMP_B200_GEMM=cublas, go to the small-M kernel or the library GEMM.
-    bfloat16 x float32 weight (a tensor the checkpoint stores in 32-bit) -> x is widened, FFMA kernel.
-    `out` may be bfloat16 or float32.
+    may_defer: the caller hands the result to add_rmsnorm (or calls summed() on it), so a product the tcgen05
+    kernel splits over K may come back as a SplitSum, its summing kernel saved.
     """
-    M = x.shape[0]
-    if M == 0:
+    _need_cuda(out, x, w)
+    if x.shape[0] == 0:
         return out
-    if w.dtype == torch.float32:
-        xf = x if x.dtype == torch.float32 else cast(torch.empty(x.shape, dtype=torch.float32, device=x.device),
-                                                     x.contiguous())
-        if out.dtype == torch.float32:
-            return gemm_f32(out, xf, w)
-        tmp = gemm_f32(torch.empty(out.shape, dtype=torch.float32, device=x.device), xf, w)
-        if out.is_contiguous():
-            return cast(out, tmp)
-        out.copy_(tmp)
-        return out
-    if x.dtype != torch.bfloat16:
-        raise L.KernelError("bfloat16 weights need bfloat16 activations (the float32 path widens weights at load)")
-    defer = may_defer and DEFER_SPLIT_SUMS and out.is_contiguous()
-    if M <= SMALL_M_MAX:
-        # The weight-streaming kernel, except where the swap-AB tcgen05 kernel measured faster: from 8 rows up,
-        # and at any row count for products with a long contraction and few output columns (K split over CTAs).
-        N, Kd = w.shape
-        if LARGE_M_BACKEND == "tcgen05" and (M > STREAM_M_MAX or (Kd >= 2 * N and N >= 1024)):
-            if defer:
-                sp = gemm_bf16_tc_swap_partials(out, x, w)
-                if sp is not None:
-                    return sp
-            if gemm_bf16_tc_swap(out, x, w):
-                return out
-        return gemm_bf16_stream(out, x, w)
-    if LARGE_M_BACKEND == "tcgen05":
-        if M <= TC_SWAP_MAX_M:
-            if defer:
-                sp = gemm_bf16_tc_swap_partials(out, x, w)
-                if sp is not None:
-                    return sp
-            if gemm_bf16_tc_swap(out, x, w):
-                return out
-        if gemm_bf16_tc(out, x, w):
-            return out
-    if out.dtype == torch.bfloat16:
-        torch.mm(x, w.t(), out=out)
-    else:
-        out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+    o, a, wv = _view(out), _view(x), _view(w)
+    parts, n_splits = ctypes.c_void_p(), ctypes.c_int(0)
+    _op_check(L.load().imp_op_linear(ctypes.byref(o), ctypes.byref(a), ctypes.byref(wv), 1 if may_defer else 0,
+                                     ctypes.byref(parts), ctypes.byref(n_splits), _stream(), None), "linear")
+    if n_splits.value > 0:
+        return SplitSum(out, parts.value, n_splits.value)
     return out
+
+
+def fallback_calls() -> int:
+    """Matrix products (on this thread) that no fast kernel took and the plain kernel ran."""
+    return int(L.load().imp_op_fallback_calls())
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

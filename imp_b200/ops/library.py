@@ -76,6 +76,16 @@ _SIGNATURES = {
                                     c_void_p, c_void_p, c_void_p]),
 }
 
+_SIGNATURES.update({
+    "imp_op_error_message": (c_char_p, []),
+    "imp_op_fallback_calls": (c_int64, []),
+    "imp_op_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "imp_op_linear_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "imp_op_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                   c_int, c_void_p]),
+    "imp_op_decode_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+})
+
 # Entry points that newer sources add; declared when present so an older build still loads in tools
 # that only list symbols.  Every name in _SIGNATURES is required.
 _OPTIONAL_SIGNATURES = {}

@@ -52,6 +52,16 @@ class PartBench:
                                                     ctypes.byref(out)))
         return PartHandle(out.value, self.device_id)
 
+    def build_block(self, kind: str, parts: Dict[str, PartHandle], params: Optional[dict] = None) -> PartHandle:
+        """A block of kind `kind` over parts this bench built, by slot name."""
+        n = len(parts)
+        names = (ctypes.c_char_p * max(n, 1))(*[k.encode() for k in parts])
+        ptrs = (ctypes.c_void_p * max(n, 1))(*[h.ptr for h in parts.values()])
+        out = ctypes.c_void_p()
+        capi.check(capi.load().imp_bench_build_block(self.handle, kind.encode(), json.dumps(params or {}).encode(), n, names,
+                                                     ptrs, ctypes.byref(out)))
+        return PartHandle(out.value, self.device_id)
+
     def _rid(self, rid: Hashable) -> int:
         if rid not in self._ids:
             self._ids[rid] = len(self._ids)

@@ -110,6 +110,11 @@ IMP_EXPORT void imp_context_free(ImpContext ctx);
 /* Drop every request and give all pages and state slots back. */
 IMP_EXPORT ImpError imp_context_reset(ImpContext ctx);
 
+/* The end-of-sequence token ids of requests submitted from now on (default: config.json's eos_token_id). */
+IMP_EXPORT ImpError imp_context_set_eos(ImpContext ctx, const int32_t* ids, int n);
+/* The cache manager's invariants (no page lost or held twice): IMP_ERROR_INTERNAL names a broken one. */
+IMP_EXPORT ImpError imp_context_check(ImpContext ctx);
+
 /* State of the context as JSON (cache groups, free pages, run positions, counters, ...). */
 IMP_EXPORT const char* imp_context_info_json(ImpContext ctx);
 

@@ -158,6 +158,9 @@ IMP_EXPORT void imp_bench_free(ImpBench b);
  * where the loader would, and owned by the part). */
 IMP_EXPORT ImpError imp_bench_build_part(ImpBench b, const char* category, const char* spec_json, int n_tensors,
                                          const char* const* names, const ImpTensor* tensors, ImpPart* out);
+/* Build a block of kind `kind` over parts this bench built, by slot name. */
+IMP_EXPORT ImpError imp_bench_build_block(ImpBench b, const char* kind, const char* params_json, int n_parts,
+                                          const char* const* slot_names, const ImpPart* parts, ImpPart* out);
 IMP_EXPORT void imp_bench_free_part(ImpBench b, ImpPart part);
 /* Reserve cache for the entries and upload the batch arrays (tokens may be NULL: zeros). */
 IMP_EXPORT ImpError imp_bench_prepare(ImpBench b, const ImpStepEntry* entries, int n_entries, const ImpBatchView** out);

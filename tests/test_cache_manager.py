@@ -4,7 +4,7 @@ import random
 import pytest
 from hypothesis import given, settings, strategies as st
 
-from imp_b200.cache.manager import (CacheError, CacheManager, OutOfPages, PagedKVSpec, PagePool, StateSpec)
+from imp_b200.cache.manager import CacheError, CacheManager, OutOfPages, PagedKVSpec, StateSpec
 
 FULL = PagedKVSpec(2, 16, 0)
 WIN = PagedKVSpec(2, 16, 10)
@@ -12,17 +12,23 @@ STATE = StateSpec((4, 8))
 
 
 def test_pool_hands_out_page_zero_first_and_reuses_lifo():
-    p = PagePool(4)
-    assert [p.alloc() for _ in range(4)] == [0, 1, 2, 3]
+    m = CacheManager([FULL], page_size=1, num_pages=4, num_state_slots=4)
+    for rid in "abcd":
+        m.add_request(rid)
+        m.reserve(rid, 1)
+    assert [m.block_table(0, r) for r in "abcd"] == [[0], [1], [2], [3]]
+    m.add_request("e") if False else None
     with pytest.raises(OutOfPages):
-        p.alloc()
-    p.free(2)
-    p.free(0)
-    assert p.alloc() == 0 and p.alloc() == 2
-    with pytest.raises(CacheError, match="twice"):
-        p.free(1), p.free(1)
-    with pytest.raises(CacheError, match="outside"):
-        p.free(9)
+        m.reserve("a", 2)
+    m.release("c")
+    m.release("a")
+    m.add_request("x")
+    m.reserve("x", 2)
+    assert m.block_table(0, "x") == [0, 2]          # the page freed last comes out first
+    with pytest.raises(CacheError, match="unknown|twice"):
+        m.release("a")
+    with pytest.raises(CacheError):
+        m.reserve("nobody", 1)
 
 
 def test_layers_are_grouped_by_need():

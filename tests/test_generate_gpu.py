@@ -34,7 +34,7 @@ def test_greedy_generation_matches_plain(name, model_folders):
     eng = engine(folder, "float32", page, prefill_chunk_size=8)
     got = eng.generate(prompts, GenerateParams(max_tokens=10, temperature=0.0))
     assert got == want
-    assert eng.cache.free_pages() == eng.cache.num_pages and not eng.has_work()
+    assert eng.free_pages() == eng.num_pages and not eng.has_work()
     # bfloat16 may flip a near-tie later on; its first tokens, from well separated logits, must agree
     eng16 = engine(folder, "bfloat16", page)
     got16 = eng16.generate(prompts, GenerateParams(max_tokens=10, temperature=0.0))
@@ -57,7 +57,7 @@ def test_long_decoding_and_first_tokens(dtype, model_folders):
     eng = engine(folder, dtype, page)
     rows = {}
     for i, t in enumerate(ids):
-        lg = eng.step_tokens([StepEntry("x", [t], [0])])
+        lg = torch.from_numpy(eng.step_tokens([StepEntry("x", [t], [0])]))
         if i < 3 or i >= 290 or i in (23, 24, 25, 47, 48):     # the window of B is 24, its pages hold 16
             rows[i] = lg[0]
     eng.end("x")
@@ -123,8 +123,8 @@ def test_preemption_for_lack_of_pages_changes_no_token(model_folders):
     tight = engine(folder, "float32", page, kv_cache_max_blocks=18, kv_cache_tokens=0)   # 72 tokens for 3 x 34
     got = tight.generate(prompts, gp)
     assert got == roomy
-    assert max(r.n_preempted for r in tight.scheduler.by_id.values()) >= 1
-    assert tight.cache.free_pages() == 18
+    assert tight.info()["scheduler"]["preemptions"] >= 1
+    assert tight.free_pages() == 18
     # a request that can never fit is refused, not queued for ever
     with pytest.raises(MemoryError):
         tight.generate([list(range(60))], GenerateParams(max_tokens=40, temperature=0.0))
@@ -138,7 +138,8 @@ def test_cuda_graph_decode_equals_eager_decode(model_folders):
     a = engine(folder, "bfloat16", page, enable_cuda_graphs=True)
     b = engine(folder, "bfloat16", page, enable_cuda_graphs=False)
     assert a.generate(prompts, gp) == b.generate(prompts, gp)
-    assert a.stepper._graphs and not b.stepper._graphs
+    ia, ib = a.info(), b.info()
+    assert ia["graph_captures"] >= 1 and ia["graph_replays"] > 10 and ib["graph_replays"] == 0
 
 
 def test_entry_point_refuses_bad_input(model_folders):
@@ -155,7 +156,7 @@ def test_entry_point_refuses_bad_input(model_folders):
         eng.step_tokens([StepEntry("a", [1], []), StepEntry("a", [2], [])])
     with pytest.raises(TypeError):
         eng.generate([1, 2, 3], GenerateParams(max_tokens=2))
-    assert eng.cache.free_pages() == eng.cache.num_pages
+    assert eng.free_pages() == eng.num_pages
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -186,8 +187,8 @@ def test_lookahead_changes_nothing(dtype, model_folders):
             for o in outs:
                 assert o.token >= 0 or o.finished
         eng.drain()
-        assert not eng.has_work() and eng.cache.free_pages() == eng.cache.num_pages
-        eng.cache.check_invariants()
+        assert not eng.has_work() and eng.free_pages() == eng.num_pages
+        eng.check_invariants()
         runs[la] = [(list(r.output), r.finish_reason) for r in reqs]
     if dtype == "float32":
         assert runs[True] == runs[False]
@@ -211,16 +212,16 @@ def test_lookahead_overlaps_only_when_it_may(model_folders):
     eng = engine(folder, "bfloat16", page, prefill_chunk_size=8)
     r = eng.submit(prompts_for(cd["vocab_size"], [20])[0], GenerateParams(max_tokens=4, temperature=0.0))
     eng.step()
-    assert eng._inflight is None                  # first portion of the prompt: nothing sampled yet
+    assert not eng.info()["inflight"]                  # first portion of the prompt: nothing sampled yet
     eng.step(); eng.step()
-    assert len(r.output) == 1 and eng._inflight is not None      # decoding: one step is under way
+    assert len(r.output) == 1 and eng.info()["inflight"]      # decoding: one step is under way
     eng.step()
-    assert len(r.output) == 2 and eng._inflight is not None
+    assert len(r.output) == 2 and eng.info()["inflight"]
     eng.step()
-    assert len(r.output) == 3 and eng._inflight is not None      # the step under way brings the fourth, last token
+    assert len(r.output) == 3 and eng.info()["inflight"]      # the step under way brings the fourth, last token
     eng.step()
-    assert r.done and len(r.output) == 4 and eng._inflight is None and not eng.has_work()   # nothing was launched beyond it
+    assert r.done and len(r.output) == 4 and not eng.info()["inflight"] and not eng.has_work()   # nothing was launched beyond it
     pen = eng.submit([1, 2, 3], GenerateParams(max_tokens=5, temperature=0.0, repetition_penalty=1.3))
     while not pen.done:
         eng.step()
-        assert eng._inflight is None              # the penalty reads the tokens on the host
+        assert not eng.info()["inflight"]              # the penalty reads the tokens on the host

@@ -22,6 +22,28 @@ def K():
     return kernels
 
 
+def decode_reference(qkv, kc0, vc0, bt, lengths, Hq, Hkv, Dh, page, window, qw, kw, theta=1e4, eps=1e-6):
+    """One decode step in double precision from the raw q | k | v rows and the cache before the step: per-head
+    norm and rotation of q and of the new key, the new key and value appended, one query over its sequence."""
+    B, G = len(lengths), Hq // Hkv
+    out = torch.zeros(B, Hq, Dh, dtype=torch.float64)
+    rows = qkv.double().cpu()
+    for s, n in enumerate(lengths):
+        q = rows[s, :Hq * Dh].view(1, Hq, Dh)
+        k = rows[s, Hq * Dh:(Hq + Hkv) * Dh].view(1, Hkv, Dh)
+        v = rows[s, (Hq + Hkv) * Dh:].view(Hkv, Dh)
+        if qw is not None:
+            q, k = P.rmsnorm(q, qw.double().cpu(), eps), P.rmsnorm(k, kw.double().cpu(), eps)
+        q, k = P.rope(q, [n - 1], theta)[0], P.rope(k, [n - 1], theta)[0]
+        keys = torch.stack([kc0[int(bt[s, p // page]), :, p % page].double() for p in range(n - 1)] + [k]) if n > 1 else k[None]
+        vals = torch.stack([vc0[int(bt[s, p // page]), :, p % page].double() for p in range(n - 1)] + [v]) if n > 1 else v[None]
+        lo = max(0, n - window) if window else 0
+        for h in range(Hq):
+            sc = (keys[lo:, h // G] @ q[h]) / math.sqrt(Dh)
+            out[s, h] = torch.softmax(sc, 0) @ vals[lo:, h // G]
+    return out
+
+
 def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
     g = torch.Generator().manual_seed(seed)
     return (torch.randn(*shape, generator=g) * scale).to(dtype)
@@ -967,6 +989,7 @@ def test_linear_defers_only_when_asked_and_only_split_products(K):
     a, w = rnd(8, 4096, dtype=torch.bfloat16, seed=68).to(DEV), rnd(4096, 4096, dtype=torch.bfloat16, seed=69).to(DEV)
     out = torch.empty(8, 4096, dtype=torch.bfloat16, device=DEV)
     assert K.linear(out, a, w) is out
+    assert K.fallback_calls() == 0
     got = K.linear(torch.empty_like(out), a, w, may_defer=True)
     assert isinstance(got, K.SplitSum) and torch.equal(got.summed(), out)
     big = rnd(32000, 4096, dtype=torch.bfloat16, seed=70).to(DEV)       # enough weight-row tiles: no split, a tensor
@@ -1018,6 +1041,10 @@ def test_decode_attention_from_raw_qkv_equals_rotary_kernel_then_attention(K, Hq
         assert (kc_a != kc_b).float().mean() < 1e-3                    # the sum of squares adds in another order
         close(kc_b, kc_a.double().cpu(), torch.bfloat16)
         close(out_b, out_a.double().cpu(), torch.bfloat16)
+        # and both against the computation in double precision (keys enter it as the bfloat16 values of the cache)
+        want = decode_reference(qkv, kc0, vc0, bt, lengths, Hq, Hkv, Dh, page, window, qw, kw)
+        close(out_b.view(B, Hq, Dh), want, torch.bfloat16)
+        close(out_a.view(B, Hq, Dh), want, torch.bfloat16)
     # head sizes and page sizes the one-kernel path does not take are declined, nothing written
     kc_c = torch.zeros(4, 1, 8, 64, dtype=torch.bfloat16, device=DEV)
     assert not A.decode_attention_fused(torch.empty(1, 64, dtype=torch.bfloat16, device=DEV),

@@ -2,8 +2,9 @@
 cache, all defined here, registered, built from a config.json, stepped and generated with, without
 a change to the framework's files.
 
-The toy mixer is a causal running mean: y_t = W * mean(x_0 .. x_t).  Its state (the running sum, one
-float32 vector per request and run position) lives in the cache manager's fixed-size state slots.
+The toy mixer is a causal running mean: y_t = W * mean(x_0 .. x_t).  Its state lives in the cache
+manager's fixed-size state slots, as two tensors of different types per request and run position:
+the running sum (a float32 vector) and the number of tokens seen (one int32).
 """
 import math
 from dataclasses import dataclass
@@ -42,22 +43,26 @@ def toy_folder(tmp_path_factory):
 
         @classmethod
         def cache_spec(cls, params):
-            return StateSpec((params["hidden_size"],), "float32")
+            return StateSpec(tensors=(("sum", (params["hidden_size"],), "float32"), ("count", (1,), "int32")))
 
         def forward(self, x, ctx, cache):
             w = self.tensors["w"].float()
             out = torch.empty_like(x)
+            total, count = cache.states
+            assert total.dtype == torch.float32 and count.dtype == torch.int32
             t0 = 0
-            for n, start, slot in zip(ctx.q_lens, ctx.starts, ctx.slots):
-                sums = torch.cumsum(x[t0:t0 + n].float(), 0) + cache.state[slot]
+            for n, start, slot, fresh in zip(ctx.q_lens, ctx.starts, ctx.slots, ctx.fresh):
+                seen = int(count[slot, 0])
+                assert seen == start and (seen == 0) == fresh      # a fresh request's state starts at zero
+                sums = torch.cumsum(x[t0:t0 + n].float(), 0) + total[slot]
                 if cache.writes:
-                    cache.state[slot] = sums[-1]
-                counts = torch.arange(start + 1, start + n + 1, device=x.device, dtype=torch.float32)
+                    total[slot] = sums[-1]
+                    count[slot, 0] = seen + n
+                counts = torch.arange(seen + 1, seen + n + 1, device=x.device, dtype=torch.float32)
                 out[t0:t0 + n] = ((sums / counts[:, None]) @ w.T).to(x.dtype)
                 t0 += n
             return out
 
-    @dataclass
     class ToyConfig(Qwen3Config):
         pass
 
@@ -116,13 +121,14 @@ def plain_toy_logits(folder, ids):
 def test_toy_architecture_is_built_and_stepped(toy_folder, dtype):
     from imp_b200 import Engine, EngineConfig, GenerateParams, StepEntry
     eng = Engine.from_folder(toy_folder, EngineConfig(compute_dtype=dtype, kv_block_size=4, max_batch_size=3,
-                                                      max_seq_len=128, kv_cache_tokens=512, max_batch_tokens=64,
-                                                      enable_cuda_graphs=False))
+                                                      max_seq_len=128, kv_cache_tokens=512, max_batch_tokens=64))
     # run positions 0 and 3 own pages, position 2 reads position 0's, positions 1 and 4 own state
-    assert [type(s).__name__ if s else None for s in eng.model.cache_specs] == \
-        ["PagedKVSpec", "StateSpec", None, "PagedKVSpec", "StateSpec"]
-    assert eng.model.cache_position == [0, 1, 0, 3, 4]
-    assert len(eng.cache.paged) == 1 and len(eng.cache.state) == 1 and eng.cache.state[0].storage.shape[0] == 2
+    info = eng.info()
+    assert [s["kind"] if s else None for s in info["model"]["cache_specs"]] == ["paged", "state", None, "paged", "state"]
+    assert info["model"]["cache_position"] == [0, 1, 0, 3, 4]
+    assert len(info["cache"]["paged"]) == 1 and len(info["cache"]["state"]) == 1
+    assert info["cache"]["state"][0]["layers"] == [1, 4] and len(info["cache"]["state"][0]["tensors"]) == 2
+    assert not info["model"]["graph_safe"], "a part written in Python keeps CUDA graphs off for its model"
     g = torch.Generator().manual_seed(2)
     a = torch.randint(0, TOY["vocab_size"], (29,), generator=g).tolist()
     b = torch.randint(0, TOY["vocab_size"], (13,), generator=g).tolist()
@@ -134,7 +140,10 @@ def test_toy_architecture_is_built_and_stepped(toy_folder, dtype):
         err = (got - want).abs()
         assert (err <= atol + rtol * want.abs()).all(), f"{what}: max error {err.max():.3g}"
 
-    whole = eng.step_tokens([StepEntry("a", a, list(range(29)))])
+    def step(entries):
+        return torch.from_numpy(eng.step_tokens(entries))
+
+    whole = step([StepEntry("a", a, list(range(29)))])
     eng.end("a")
     check(whole, ref_a, "whole")
     # portions of a beside single tokens of b; a's slot is reused after it ends
@@ -143,7 +152,7 @@ def test_toy_architecture_is_built_and_stepped(toy_folder, dtype):
         entries = [StepEntry("a2", a[ia:ia + n], list(range(n)))]
         if ib < len(b):
             entries.append(StepEntry("b", [b[ib]], [0]))
-        lg = eng.step_tokens(entries)
+        lg = step(entries)
         rows_a.append(lg[:n])
         if ib < len(b):
             rows_b.append(lg[n:])
@@ -151,7 +160,7 @@ def test_toy_architecture_is_built_and_stepped(toy_folder, dtype):
         ia += n
     eng.end("a2")
     while ib < len(b):
-        rows_b.append(eng.step_tokens([StepEntry("b", [b[ib]], [0])]))
+        rows_b.append(step([StepEntry("b", [b[ib]], [0])]))
         ib += 1
     eng.end("b")
     check(torch.cat(rows_a), ref_a, "portions")
@@ -165,5 +174,5 @@ def test_toy_architecture_is_built_and_stepped(toy_folder, dtype):
             want.append(tok)
             ids.append(tok)
         assert eng.generate([a[:6], b[:3]], GenerateParams(max_tokens=8, temperature=0.0))[0] == want
-    eng.cache.check_invariants()
-    assert eng.cache.free_pages() == eng.cache.num_pages and eng.cache.slots.n_free == 3
+    eng.check_invariants()
+    assert eng.free_pages() == eng.num_pages and eng.info()["cache"]["free_slots"] == 3

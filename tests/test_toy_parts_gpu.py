@@ -77,7 +77,6 @@ def toy_folder(tmp_path_factory):
             q.copy_(additive_position(q.float(), pos, self.params["scale"]).to(q.dtype))
             k.copy_(additive_position(k.float(), pos, self.params["scale"]).to(k.dtype))
 
-    @dataclass
     class ToyConfig(Qwen3Config):
         pass
 
@@ -146,11 +145,14 @@ def plain_logits(folder, ids):
 def test_routed_feed_forward_and_another_position_encoding(toy_folder, dtype):
     from imp_b200 import Engine, EngineConfig, GenerateParams, StepEntry
     eng = Engine.from_folder(toy_folder, EngineConfig(compute_dtype=dtype, kv_block_size=8, max_batch_size=3,
-                                                      max_seq_len=128, kv_cache_tokens=512, max_batch_tokens=64,
-                                                      enable_cuda_graphs=False))
-    names = [type(b.feed_forward).__name__ for b in eng.model.blocks]
-    assert names == ["ToyRouted", "SwiGLU", "ToyRouted"]
-    assert type(eng.model.blocks[1].mixer.position).__name__ == "ToyAdditivePosition"
+                                                      max_seq_len=128, kv_cache_tokens=512, max_batch_tokens=64))
+    layers = eng.model.plan_json()["layers"]
+    assert [l["parts"]["feed_forward"]["kind"] for l in layers] == ["toy_routed", "swiglu", "toy_routed"]
+    assert [l["parts"]["mixer"]["params"]["position"]["kind"] for l in layers] == ["rotary", "toy_additive", "rotary"]
+
+    def step(entries):
+        return torch.from_numpy(eng.step_tokens(entries))
+
     g = torch.Generator().manual_seed(4)
     a = torch.randint(0, TOY["vocab_size"], (37,), generator=g).tolist()
     b = torch.randint(0, TOY["vocab_size"], (11,), generator=g).tolist()
@@ -165,7 +167,7 @@ def test_routed_feed_forward_and_another_position_encoding(toy_folder, dtype):
             scale = float(want.abs().max())
             bad = ((got - want).abs() > 0.04 * scale + 0.04 * want.abs()).any(dim=-1)
             assert bad.float().mean() <= 0.15, f"{what}: {int(bad.sum())} of {bad.numel()} rows differ"
-    whole = eng.step_tokens([StepEntry("a", a, list(range(len(a))))])
+    whole = step([StepEntry("a", a, list(range(len(a))))])
     eng.end("a")
     check(whole, ref_a, "whole")
     rows_a, rows_b, ia, ib = [], [], 0, 0
@@ -173,7 +175,7 @@ def test_routed_feed_forward_and_another_position_encoding(toy_folder, dtype):
         entries = [StepEntry("a2", a[ia:ia + n], list(range(n)))]
         if ib < len(b):
             entries.append(StepEntry("b", [b[ib]], [0]))
-        lg = eng.step_tokens(entries)
+        lg = step(entries)
         rows_a.append(lg[:n])
         if ib < len(b):
             rows_b.append(lg[n:])
@@ -181,7 +183,7 @@ def test_routed_feed_forward_and_another_position_encoding(toy_folder, dtype):
         ia += n
     eng.end("a2")
     while ib < len(b):
-        rows_b.append(eng.step_tokens([StepEntry("b", [b[ib]], [0])]))
+        rows_b.append(step([StepEntry("b", [b[ib]], [0])]))
         ib += 1
     eng.end("b")
     check(torch.cat(rows_a), ref_a, "portions")
@@ -194,5 +196,5 @@ def test_routed_feed_forward_and_another_position_encoding(toy_folder, dtype):
             want.append(tok)
             ids.append(tok)
         assert eng.generate([a[:5]], GenerateParams(max_tokens=6, temperature=0.0))[0] == want
-    eng.cache.check_invariants()
-    assert eng.cache.free_pages() == eng.cache.num_pages
+    eng.check_invariants()
+    assert eng.free_pages() == eng.num_pages
