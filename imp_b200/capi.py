@@ -165,6 +165,8 @@ _SIGNATURES = {
     "imp_context_free": (None, [_H]),
     "imp_context_reset": (_E, [_H]),
     "imp_context_info_json": (c_char_p, [_H]),
+    "imp_context_timer_start": (_E, [_H]),
+    "imp_context_timer_stop": (_E, [_H, POINTER(c_float)]),
     "imp_context_set_eos": (_E, [_H, POINTER(c_int32), c_int]),
     "imp_context_check": (_E, [_H]),
     "imp_submit": (_E, [_H, POINTER(c_int32), c_int, POINTER(ImpGenerateParams), POINTER(c_int64)]),

@@ -243,6 +243,22 @@ IMP_EXPORT ImpError imp_context_check(ImpContext ctx) {
     IMP_CATCH
 }
 
+IMP_EXPORT ImpError imp_context_timer_start(ImpContext ctx) {
+    IMP_TRY
+    need_arg(ctx != nullptr, "imp_context_timer_start: ctx must not be null");
+    ctx->e->make_current();
+    ctx->e->timer_start();
+    IMP_CATCH
+}
+
+IMP_EXPORT ImpError imp_context_timer_stop(ImpContext ctx, float* out_ms) {
+    IMP_TRY
+    need_arg(ctx && out_ms, "imp_context_timer_stop: ctx and out_ms must not be null");
+    ctx->e->make_current();
+    *out_ms = ctx->e->timer_stop();
+    IMP_CATCH
+}
+
 IMP_EXPORT const char* imp_context_info_json(ImpContext ctx) {
     if (!ctx) return "";
     try {

@@ -148,6 +148,21 @@ void Arena::next_layer() {
     merge(layer_[cur_], hw_layer_);
 }
 
+Arena::Mark Arena::mark() const {
+    Mark m;
+    m.step_used = step_.used;
+    m.layer_used[0] = layer_[0].used;
+    m.layer_used[1] = layer_[1].used;
+    m.cur = cur_;
+    return m;
+}
+
+void Arena::restore(const Mark& m) {
+    step_.used = step_.need = m.step_used;
+    for (int i = 0; i < 2; ++i) layer_[i].used = layer_[i].need = m.layer_used[i];
+    cur_ = m.cur;
+}
+
 size_t Arena::capacity_bytes() const {
     size_t n = step_.main.bytes();
     for (const auto& r : layer_) n += r.main.bytes();

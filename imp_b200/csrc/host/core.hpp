@@ -143,6 +143,15 @@ public:
     void begin_step(cudaStream_t stream);      // reset everything; merge blocks if the last step grew
     void next_layer();                         // switch to the other layer region and empty it
     void freeze(bool on) { frozen_ = on; }     // while a graph is captured: growing is an error
+    // Where the allocation cursors stand.  A replayed graph does not allocate on the host, so whoever replays
+    // one puts the cursors where they stood when its capture ended: what is allocated after the replay must
+    // not land on memory the graph's kernels use.
+    struct Mark {
+        size_t step_used = 0, layer_used[2] = {0, 0};
+        int cur = 0;
+    };
+    Mark mark() const;
+    void restore(const Mark& m);
     uint64_t generation() const { return generation_; }
     size_t capacity_bytes() const;
     size_t high_water_bytes() const { return hw_step_ + 2 * hw_layer_; }

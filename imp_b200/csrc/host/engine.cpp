@@ -68,6 +68,23 @@ Engine::~Engine() {
     if (dev_) cudaStreamSynchronize(dev_->rt.stream);
     for (auto e : events_)
         if (e) cudaEventDestroy(e);
+    for (auto e : timer_)
+        if (e) cudaEventDestroy(e);
+}
+
+void Engine::timer_start() {
+    for (auto& e : timer_)
+        if (!e) IMP_CUDA(cudaEventCreate(&e));
+    IMP_CUDA(cudaEventRecord(timer_[0], dev_->rt.stream));
+}
+
+float Engine::timer_stop() {
+    if (!timer_[0]) fail(IMP_ERROR_INVALID_ARG, "the timer was not started");
+    IMP_CUDA(cudaEventRecord(timer_[1], dev_->rt.stream));
+    IMP_CUDA(cudaEventSynchronize(timer_[1]));
+    float ms = 0.f;
+    IMP_CUDA(cudaEventElapsedTime(&ms, timer_[0], timer_[1]));
+    return ms;
 }
 
 // Pages per cache group: explicit, or from a token count, or from free memory (the reference gives 80% of
@@ -256,6 +273,7 @@ Json Engine::info_json() const {
     j["launches"] = dev_->rt.launches;
     j["fallback_calls"] = dev_->rt.fallback_calls;
     j["split_norm_calls"] = dev_->rt.split_norm_calls;
+    j["h2d_bytes_last_step"] = stepper_->h2d_bytes_last_step;
     j["graph_replays"] = stepper_->graph_replays;
     j["graph_captures"] = stepper_->graph_captures;
     j["eager_steps"] = stepper_->eager_steps;

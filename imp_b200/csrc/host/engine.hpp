@@ -57,6 +57,9 @@ public:
     void make_current() const { dev_->make_current(); }
     void set_eos(const std::vector<int>& ids) { eos_ = ids; }      // for requests submitted from now on
     void check_invariants() const { cache_->check_invariants(); }
+    // Device time between two points of the context's stream (CUDA events): for measurement.
+    void timer_start();
+    float timer_stop();   // waits for the stream; milliseconds since timer_start
     // the reference's token-level pair (one request at a time)
     int64_t single_rid = -1;
     size_t single_read = 0;
@@ -91,6 +94,7 @@ private:
     std::vector<int> eos_;
     std::vector<int32_t> scratch_tokens_;
     int64_t steps_ = 0;
+    cudaEvent_t timer_[2] = {nullptr, nullptr};
 };
 
 }  // namespace imp

@@ -205,6 +205,7 @@ Step& Stepper::prepare(const StepEntryView* entries, int B) {
         }
     }
     buf_.upload(which, B, rt_->stream);
+    h2d_bytes_last_step = (int64_t)(buf_.small_words + buf_.off_bt.size() * (size_t)B * (size_t)buf_.max_pages) * 4;
 
     int32_t* d = buf_.dev();
     ImpBatchView& v = st.view;
@@ -300,6 +301,7 @@ Tensor Stepper::forward_decode_graph(Step& st) {
         IMP_CUDA(cudaStreamEndCapture(rt_->stream, &graph));
         Graph g;
         g.logits = logits;
+        g.mark = rt_->arena->mark();
         g.launches = rt_->launches - launches_before;   // launcher calls the graph stands for
         rt_->launches = launches_before;
         cudaError_t e = cudaGraphInstantiate(&g.exec, graph, 0);
@@ -309,6 +311,7 @@ Tensor Stepper::forward_decode_graph(Step& st) {
         ++graph_captures;
         hit = graphs_.emplace(B, g).first;
     }
+    rt_->arena->restore(hit->second.mark);
     IMP_CUDA(cudaGraphLaunch(hit->second.exec, rt_->stream));
     rt_->launches += hit->second.launches;
     ++graph_replays;

@@ -79,6 +79,7 @@ public:
     void check_device_status(const std::string& what);
     Step& current() { return step_; }
     int64_t graph_replays = 0, graph_captures = 0, eager_steps = 0;
+    int64_t h2d_bytes_last_step = 0;   // batch arrays copied from pinned memory by the last prepare()
 
 private:
     Tensor forward_decode_graph(Step& st);
@@ -96,6 +97,7 @@ private:
         cudaGraphExec_t exec = nullptr;
         Tensor logits{};
         int64_t launches = 0;
+        Arena::Mark mark;    // the workspace's cursors when the capture ended
     };
     std::map<int, Graph> graphs_;
     std::map<int, int> graph_uses_;

@@ -264,6 +264,16 @@ class Engine:
     def num_pages(self) -> int:
         return self.info()["cache"]["num_pages"]
 
+    def timer_start(self) -> None:
+        """Mark the start of a device-timed region on the engine's stream (a CUDA event)."""
+        capi.check(capi.load().imp_context_timer_start(self._ctx))
+
+    def timer_stop(self) -> float:
+        """Wait for the work queued since `timer_start`; its device time in milliseconds."""
+        ms = ctypes.c_float(0.0)
+        capi.check(capi.load().imp_context_timer_stop(self._ctx, ctypes.byref(ms)))
+        return float(ms.value)
+
     def check_invariants(self) -> None:
         """The cache manager's invariants (no page lost, held twice or freed twice)."""
         capi.check(capi.load().imp_context_check(self._ctx))

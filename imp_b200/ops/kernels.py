@@ -130,11 +130,11 @@ class SplitSum:
     summing kernel; `add_rmsnorm` takes one and adds the parts while it reads them.  Anyone else calls
     `summed()` first."""
 
-    __slots__ = ("out", "parts_ptr", "n_splits", "_parts")
+    __slots__ = ("out", "parts_ptr", "n_splits", "parts")
 
     def __init__(self, out: torch.Tensor, parts, n_splits: int):
         # parts: an address in the library's scratch, or a tensor [n_splits, M, N] float32 of the caller's
-        self._parts = parts
+        self.parts = parts if hasattr(parts, "data_ptr") else None
         self.out, self.n_splits = out, n_splits
         self.parts_ptr = parts.data_ptr() if hasattr(parts, "data_ptr") else int(parts)
 
@@ -373,6 +373,28 @@ def gemm_bf16_tc_swap(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
         return False
     L.check(rc, "gemm_bf16_tc_swap")
     return True
+
+
+def gemm_bf16_tc_swap_partials(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor,
+                               status: Optional[torch.Tensor] = None) -> Optional[SplitSum]:
+    """a[M,K] @ w[N,K]^T left as the partial results of the K splits of the swap-AB tcgen05 kernel; None where
+    that kernel would not split this shape (or cannot take it)."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and a.dtype == w.dtype == torch.bfloat16 and M <= TC_SWAP_MAX_M and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    lib = L.load()
+    n_splits = lib.imp_gemm_bf16_tc_swap_splits(M, N, K)
+    if n_splits < 2:
+        return None
+    parts = torch.empty((n_splits, M, N), dtype=torch.float32, device=a.device)
+    rc = lib.imp_gemm_bf16_tc_swap_partials(parts.data_ptr(), a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0),
+                                            M, N, K, _ptr(status), _stream())
+    if rc == -2:
+        return None
+    L.check(rc, "gemm_bf16_tc_swap_partials")
+    return SplitSum(out, parts, n_splits)
 
 
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, may_defer: bool = False):

@@ -115,6 +115,11 @@ IMP_EXPORT ImpError imp_context_set_eos(ImpContext ctx, const int32_t* ids, int 
 /* The cache manager's invariants (no page lost or held twice): IMP_ERROR_INTERNAL names a broken one. */
 IMP_EXPORT ImpError imp_context_check(ImpContext ctx);
 
+/* Device time, for measurement: CUDA events on the context's stream.  Work queued between the two calls
+ * lies between the two events; imp_context_timer_stop waits for it and gives the milliseconds. */
+IMP_EXPORT ImpError imp_context_timer_start(ImpContext ctx);
+IMP_EXPORT ImpError imp_context_timer_stop(ImpContext ctx, float* out_ms);
+
 /* State of the context as JSON (cache groups, free pages, run positions, counters, ...). */
 IMP_EXPORT const char* imp_context_info_json(ImpContext ctx);
 
