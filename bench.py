@@ -3,25 +3,34 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
 
-Prints ONE JSON line.  `value` is decoded tokens per second at the default batch (8) with every
-sequence's context ending at the configured context length (4096): K decode steps timed with CUDA
-events after W warm-up steps, through the engine's step function (cache, kernels, CUDA graph) with
-the batch arrays and the argmax on the device side of the clock.  `e2e` is the same workload through
-the public entry point (`Engine.submit` / `Engine.step`): host token lists in, sampled token ids out,
-every step with its host-to-device copy of the batch arrays from pinned memory and its
-device-to-host read of the tokens.  `prefill` is one 2,048-token prompt in one step; `points` holds
-decode at batch 1 and 64.  Roofline fractions use MEASURED_PEAKS.json when the driver wrote it,
-else the stated fallback.  Every decode step streams all weights (about 16 GB), far more than the
-126 MB L2, so no explicit L2 flush is needed between timed iterations ("inputs larger than L2").
+Prints ONE JSON line.  Everything goes through the engine's public entry point (imp_b200.Engine, a thin
+layer over the C API): host token lists in, sampled token ids out, every step with its host-to-device
+copy of the batch arrays from pinned memory and its device-to-host read of the tokens.
 
-For profiling and for other sizes one phase can be run alone; it prints its own short JSON line:
+`value` is decoded tokens per second at the default batch (8) with every sequence's context ending at
+the configured context length (4096): K decode steps after W warm-up steps, timed on the device with
+CUDA events on the engine's stream.  `e2e` is the same workload, K further steps, timed by the wall clock
+around the calls.  `prefill` is one 2,048-token prompt in one step (and in 512-token portions), from the
+upload of the batch to the last row's logits on the host.  `protocol` holds the full decode run of the
+benchmark configuration, 2,048 greedy steps from 2,048 cached tokens to 4,096, at batch 1, 8 and 64, with
+the first and last 256 steps and the spread over 256-step windows; `points` repeats its overall figures.
+`yardsticks` times cuBLASLt (torch.mm, what the reference's engine calls for its T>1 products,
+src/compute/gemm.cu:303-445) at the four prefill shapes beside this library's kernel, and the whole
+prefill with the products on the library arm.  Roofline fractions use MEASURED_PEAKS.json when the driver
+wrote it, else the stated fallback.  Every decode step streams all weights (about 16 GB), far more than
+the 126 MB L2, so no explicit L2 flush is needed between timed iterations ("inputs larger than L2").
+
+Other runs, each printing its own JSON line:
     python bench.py --only decode [--batch B] [--context C] [--page P] [--layers N] [--no-graphs]
-    python bench.py --only prefill [--tokens T] [--layers N]
+    python bench.py --only prefill [--tokens T] [--chunk C] [--layers N]
+    python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
+    python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
 import argparse
 import json
 import os
+import random
 import statistics
 import subprocess
 import sys
@@ -38,7 +47,14 @@ MODEL = {
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "torch_dtype": "bfloat16", "max_position_embeddings": 4096,
 }
+# The two other shapes of the baseline record, with their workloads (see run_workload).
+MODEL_06B = dict(MODEL, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True, max_position_embeddings=8192)
+MODEL_14B = dict(MODEL, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                 intermediate_size=17408, max_position_embeddings=16384)
 CONTEXT = 4096
+START = 2048
+STAGGER = 128      # prompts of a batch finish their prefill a step apart: room for the early ones to run all 2,048 steps
 PAGE = 16
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -128,211 +144,371 @@ def prefill_flops(cfg, n_layers, T):
     return linear + attn
 
 
-def fill_cache(eng, rid, n_tokens):
-    """Give request `rid` n_tokens of (random) keys and values without computing them."""
-    eng.cache.add_request(rid)
-    eng.cache.reserve(rid, n_tokens)
-    eng.cache.commit(rid, n_tokens)
+def spread(xs):
+    return {"min": round(min(xs), 4), "median": round(statistics.median(xs), 4), "max": round(max(xs), 4)}
 
 
-def time_decode(eng, B, ctx_end, steps, warmup, torch, K, StepEntry):
-    """Device time of `steps` decode steps at batch B whose contexts end at ctx_end.  Returns (ms/step, launches/step)."""
-    from imp_b200.ops import library
-    start = ctx_end - steps - warmup
-    rids = [f"d{B}_{i}" for i in range(B)]
-    for r in rids:
-        fill_cache(eng, r, start)
-    tok = torch.zeros(B, dtype=torch.int32, device=eng.model.rt.device)
-    host_tok = [1] * B
-
-    def one():
-        logits = eng.stepper.step([StepEntry(r, [t], [0]) for r, t in zip(rids, host_tok)])
-        K.argmax(logits, tok)
-
-    for _ in range(warmup):
-        one()
-    torch.cuda.synchronize()
-    before = library.launch_calls
-    graphs = len(eng.stepper._graphs)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        one()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    eng.stepper.check_device_status("decode bench")
-    calls = (library.launch_calls - before) / steps
-    for r in rids:
-        eng.stepper.finish(r)
-    return ms, calls
+def random_prompt(rng, vocab, n):
+    return [rng.randrange(vocab) for _ in range(n)]
 
 
-def count_forward_launches(eng, B, torch, StepEntry):
-    """Launcher calls of one eager decode forward of B sequences (what one graph replay stands for)."""
-    from imp_b200.ops import library
-    rids = [f"c{i}" for i in range(B)]
-    for r in rids:
-        fill_cache(eng, r, 32)
-    saved = eng.stepper.use_cuda_graphs
-    eng.stepper.use_cuda_graphs = False
-    before = library.launch_calls
-    eng.stepper.step([StepEntry(r, [1], [0]) for r in rids])
-    n = library.launch_calls - before
-    eng.stepper.use_cuda_graphs = saved
-    torch.cuda.synchronize()
-    for r in rids:
-        eng.stepper.finish(r)
-    return n
+def make_engine(cfgd, args, max_batch, max_ctx, budget=PREFILL_TOKENS, chunk=0, dtype="bfloat16", seed=0, pool_tokens=None):
+    from imp_b200 import Engine, EngineConfig
+    ecfg = EngineConfig(max_batch_size=max_batch, max_seq_len=max_ctx, kv_block_size=args.page or PAGE,
+                        kv_cache_tokens=pool_tokens or (max_batch * max_ctx + 2 * budget), max_batch_tokens=budget,
+                        prefill_chunk_size=chunk, compute_dtype=dtype, enable_cuda_graphs=not args.no_graphs)
+    t0 = time.time()
+    eng = Engine.from_random(cfgd, ecfg, seed=seed, std=0.02)
+    return eng, time.time() - t0
+
+
+def start_decoding(eng, rng, vocab, B, prompt_len, max_tokens):
+    """Submit B prompts and step until every one has its first token (real prefill fills the cache)."""
+    from imp_b200 import GenerateParams
+    gp = GenerateParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True)
+    reqs = [eng.submit(random_prompt(rng, vocab, prompt_len), gp) for _ in range(B)]
+    waiting = {r.rid for r in reqs}
+    while waiting:
+        for o in eng.step():
+            waiting.discard(o.rid)
+    return reqs
+
+
+def stop(eng, reqs):
+    for r in reqs:
+        eng.cancel(r)
+    eng.drain()
+    for r in reqs:
+        r.release()
+
+
+def timed_steps(eng, n, B):
+    """n decode steps of B sequences between two CUDA events on the engine's stream: device milliseconds."""
+    eng.timer_start()
+    for _ in range(n):
+        outs = eng.step()
+        assert len(outs) == B, f"{len(outs)} tokens from a step of {B} sequences: a request left the batch"
+    return eng.timer_stop()
+
+
+def time_prefill(eng, rng, vocab, n_prompt, chunk, reps=7):
+    """One prompt of n_prompt tokens, whole or in portions of `chunk`, to the last row's logits on the host."""
+    from imp_b200 import StepEntry
+    ms = []
+    for i in range(1 + reps):      # one warm-up; the products run at the power cap and vary by a few per cent
+        prompt = random_prompt(rng, vocab, n_prompt)
+        step = chunk or n_prompt
+        eng.timer_start()
+        for a in range(0, n_prompt, step):
+            part = prompt[a:a + step]
+            eng.step_tokens([StepEntry("pf", part, [len(part) - 1] if a + step >= n_prompt else [])])
+        t = eng.timer_stop()
+        eng.end("pf")
+        if i > 0:
+            ms.append(t)
+    return ms
+
+
+def decode_protocol(eng, rng, cfgd, n_layers, B, peaks, window=256):
+    """The benchmark configuration's decode run: B sequences with 2,048 cached tokens (real prefill) decode
+    greedily to 4,096; device time per 256-step window."""
+    _, weight_bytes, kv_per_tok = model_numbers(cfgd, n_layers)
+    total = CONTEXT - START
+    reqs = start_decoding(eng, rng, cfgd["vocab_size"], B, START, total + STAGGER)
+    eng.step()                                       # the first decode step of a batch size runs eagerly, the second is captured
+    eng.step()
+    done, win_ms = 0, []       # the two steps above are not counted: the stagger leaves room for them
+    while done + window <= total:
+        win_ms.append(timed_steps(eng, window, B) / window)
+        done += window
+    stop(eng, reqs)
+
+    def point(ms, ctx):
+        gbs = (weight_bytes + B * ctx * kv_per_tok) / (ms * 1e-3) / 1e9
+        return {"tok_s": round(B / ms * 1e3, 1), "ms": round(ms, 4), "context": int(ctx), "gbs": round(gbs, 1),
+                "frac": round(gbs / peaks["hbm_gbs"], 4)}
+
+    n = len(win_ms)
+    all_ms = sum(win_ms) / n
+    return {"batch": B, "steps": n * window, "first256": point(win_ms[0], START + 2 + window / 2),
+            "last256": point(win_ms[-1], START + 2 + (n - 0.5) * window),
+            "all": point(all_ms, START + 2 + n * window / 2), "ms_per_step_over_windows": spread(win_ms)}
+
+
+def yardsticks(peaks, reps=20):
+    """cuBLASLt (through torch.mm) at the four prefill products of the benchmark shape beside this library's own
+    choice of kernel for the same product, each timed with CUDA events over `reps` launches on one stream."""
+    import torch
+
+    from imp_b200.ops import kernels as K
+    d, f, T = MODEL["hidden_size"], MODEL["intermediate_size"], PREFILL_TOKENS
+    qkv = (MODEL["num_attention_heads"] + 2 * MODEL["num_key_value_heads"]) * MODEL["head_dim"]
+    shapes = {"qkv": (T, qkv, d), "o": (T, d, MODEL["num_attention_heads"] * MODEL["head_dim"]), "gate_up": (T, 2 * f, d),
+              "down": (T, d, f)}
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for name, (M, N, Kd) in shapes.items():
+        a = torch.randn(M, Kd, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        w = (torch.randn(N, Kd, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        wt = w.t()
+        lib_ms = timed(lambda: torch.mm(a, wt, out=c))
+        own_ms = timed(lambda: K.linear(c, a, w))
+        flops = 2.0 * M * N * Kd
+        out[name] = {"shape": f"{M}x{N}x{Kd}", "cublaslt_ms": round(lib_ms, 4), "own_ms": round(own_ms, 4),
+                     "cublaslt_tflops": round(flops / lib_ms / 1e9, 1), "own_tflops": round(flops / own_ms / 1e9, 1),
+                     "own_over_cublaslt": round(lib_ms / own_ms, 3)}
+    return out
+
+
+def library_arm_prefill(args):
+    """The whole 2,048-token prefill with the products of more than 16 rows on cuBLASLt (IMP_B200_GEMM=cublas is
+    read once per process, so this is a run of its own)."""
+    env = dict(os.environ, IMP_B200_GEMM="cublas")
+    cmd = [sys.executable, os.path.abspath(__file__), "--only", "prefill"] + (["--layers", str(args.layers)] if args.layers else [])
+    try:
+        p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        line = [l for l in p.stdout.splitlines() if l.startswith("{")][-1]
+        d = json.loads(line)
+        return {"ms": d["ms"], "launches": d.get("launches"), "fallback_calls": d.get("fallback_calls")}
+    except Exception as e:   # the yardstick is extra: its absence must not take the line with it
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
 def run_ours(args):
-    import torch
-
-    from imp_b200 import Engine, EngineConfig, GenerateParams, StepEntry, config_from_dict
-    from imp_b200.ops import kernels as K
-    from imp_b200.ops import library
-
     peaks, peak_src = read_peaks()
     cfgd = dict(MODEL)
     n_layers = args.layers or MODEL["num_hidden_layers"]
     cfgd["num_hidden_layers"] = n_layers
     if args.only == "decode" and args.context > cfgd["max_position_embeddings"]:
         cfgd["max_position_embeddings"] = args.context
-    mc = config_from_dict(cfgd)
-    torch.cuda.set_device(0)
     B = args.batch
-    maxB = max(B, 64) if not args.only else B
-    _, _, kv_per_tok = model_numbers(cfgd, n_layers)
-    max_ctx = max(CONTEXT, args.context) if args.only == "decode" else CONTEXT
-    ecfg = EngineConfig(max_batch_size=maxB, max_seq_len=max_ctx, kv_block_size=args.page or PAGE,
-                        kv_cache_tokens=maxB * max_ctx + 4 * CONTEXT, max_batch_tokens=PREFILL_TOKENS,
-                        compute_dtype="bfloat16", enable_cuda_graphs=not args.no_graphs)
-    t0 = time.time()
-    eng = Engine.from_random(mc, ecfg, seed=0, std=0.02)
-    for g in eng.cache.paged:          # stand-in cache contents for sequences that are not really prefilled
-        g.storage.normal_(0.0, 0.5)
-    torch.cuda.synchronize()
-    setup_s = time.time() - t0
-    _, weight_bytes, _ = model_numbers(cfgd, n_layers)
+    rng = random.Random(0)
+    _, weight_bytes, kv_per_tok = model_numbers(cfgd, n_layers)
+    V = cfgd["vocab_size"]
 
-    gen = torch.Generator().manual_seed(0)
     if args.only == "decode":
-        ctx = max(args.context or CONTEXT, args.steps + args.warmup + 1)
-        ms, calls = time_decode(eng, B, ctx, args.steps, args.warmup, torch, K, StepEntry)
+        ctx = max(args.context or CONTEXT, args.steps + args.warmup + 64)
+        eng, _ = make_engine(cfgd, args, B, ctx)
+        reqs = start_decoding(eng, rng, V, B, ctx - args.steps - args.warmup - 4 * B - 2, args.steps + args.warmup + 4 * B + 8)
+        for _ in range(args.warmup):
+            eng.step()
+        before = eng.info()
+        ms = timed_steps(eng, args.steps, B) / args.steps
+        info = eng.info()
         print(json.dumps({"only": "decode", "batch": B, "layers": n_layers, "context": ctx, "ms_per_step": round(ms, 4),
-                          "launcher_calls_per_step": calls}))
+                          "launches_per_step": (info["launches"] - before["launches"]) / args.steps,
+                          "graph_replays": info["graph_replays"] - before["graph_replays"], "fallback_calls": info["fallback_calls"]}))
+        stop(eng, reqs)
         return 0
-    # ---- prefill: one prompt of 2,048 tokens in one step --------------------------------------------
-    n_prompt = PREFILL_TOKENS
-    if args.only == "prefill" and 0 < args.tokens <= PREFILL_TOKENS:
-        n_prompt = args.tokens
-    prompt = torch.randint(0, mc.vocab_size, (n_prompt,), generator=gen).tolist()
-    pf_ms = []
-    for i in range(1 + 7):      # one warm-up, seven timed: the products run at the power cap and vary by a few per cent
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        eng.stepper.step([StepEntry("pf", prompt, [n_prompt - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        eng.stepper.finish("pf")
-        if i > 0:
-            pf_ms.append(e0.elapsed_time(e1))
-    eng.stepper.check_device_status("prefill bench")
+
+    maxB = max(B, 64) if not args.only else 1
+    # the position table and the longest sequence leave room for the stagger of a batch's prompts
+    cfgd["max_position_embeddings"] = CONTEXT + STAGGER
+    eng, setup_s = make_engine(cfgd, args, maxB, CONTEXT + STAGGER)
+
+    # ---- prefill: one prompt of 2,048 tokens, whole and in 512-token portions ------------------------
+    n_prompt = args.tokens if (args.only == "prefill" and 0 < args.tokens <= PREFILL_TOKENS) else PREFILL_TOKENS
+    pf_ms = time_prefill(eng, rng, V, n_prompt, args.chunk if args.only == "prefill" else 0)
     pf = statistics.median(pf_ms)
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": n_prompt, "ms": round(pf, 3)}))
+        info = eng.info()
+        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": n_prompt, "chunk": args.chunk, "ms": round(pf, 3),
+                          "spread_ms": spread(pf_ms), "launches": info["launches"], "fallback_calls": info["fallback_calls"],
+                          "gemm": os.environ.get("IMP_B200_GEMM", "tcgen05")}))
         return 0
     pf_flops = prefill_flops(cfgd, n_layers, PREFILL_TOKENS)
+    pf512 = time_prefill(eng, rng, V, PREFILL_TOKENS, 512, reps=5)
     prefill = {"value": round(PREFILL_TOKENS / pf * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
-               "frac": round(pf_flops / (pf * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pf_flops / (pf * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+               "frac_of_sustained": round(pf_flops / (pf * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
+               "spread_ms": spread(pf_ms),
+               "in_512_portions": {"value": round(PREFILL_TOKENS / statistics.median(pf512) * 1e3, 1),
+                                   "ms": round(statistics.median(pf512), 3), "spread_ms": spread(pf512)}}
 
-    # ---- decode at the headline batch, device-timed, with clocks sampled ---------------------------------
-    per_forward = count_forward_launches(eng, B, torch, StepEntry)
+    # ---- the headline: K decode steps at batch B with contexts ending at 4096, device-timed, then K more by the
+    # ---- wall clock through the same calls (the end-to-end figure), clocks sampled throughout ----------------
+    K_, W = args.steps, args.warmup
+    slack = 4 * B            # prompts finish their prefill at different steps: the early ones decode a few tokens first
+    plen = CONTEXT - 2 * (K_ + W) - slack - 2
     with ClockSampler(0) as clocks:
-        ms, calls = time_decode(eng, B, CONTEXT, args.steps, args.warmup, torch, K, StepEntry)
+        reqs = start_decoding(eng, rng, V, B, plen, 2 * (K_ + W) + slack + 2)
+        for _ in range(W):
+            eng.step()
+        before = eng.info()
+        ms = timed_steps(eng, K_, B) / K_
+        after = eng.info()
+        for _ in range(W):
+            eng.step()
+        t0 = time.perf_counter()
+        for _ in range(K_):
+            outs = eng.step()
+            assert len(outs) == B
+        e2e_ms = (time.perf_counter() - t0) / K_ * 1e3
+        h2d = eng.info()["h2d_bytes_last_step"]
+        stop(eng, reqs)
     value = B / ms * 1e3
-    mean_ctx = CONTEXT - args.steps / 2.0
+    mean_ctx = CONTEXT - (K_ + W) - K_ / 2.0 - slack / 2.0
     step_bytes = weight_bytes + B * mean_ctx * kv_per_tok
     achieved = step_bytes / (ms * 1e-3) / 1e9
-    # A graph replay stands for `per_forward` kernel launches of this library; the argmax adds one.
-    launches = int(args.steps * (per_forward + 1)) if eng.stepper._graphs else int(calls * args.steps)
+    launches = after["launches"] - before["launches"]
 
-    # ---- other batch sizes -------------------------------------------------------------------------
-    points = {}
-    for b in (1, 64):
-        steps_b = max(8, min(args.steps, 32))
-        ms_b, _ = time_decode(eng, b, CONTEXT, steps_b, args.warmup, torch, K, StepEntry)
-        points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
-        points[f"decode_b{b}_ms"] = round(ms_b, 3)
-
-    # ---- end to end through the entry point: real prompts, host tokens in and out -----------------------
-    e2e_steps, e2e_warm = args.steps, args.warmup
-    # Prompts finish their prefill at different steps (they share the token budget), so the early ones
-    # decode a few tokens before the timed region starts: leave room for that, so that all B requests
-    # are still decoding at its end.
-    slack = 4 * B
-    plen = CONTEXT - e2e_steps - e2e_warm - 1 - slack
-    gp = GenerateParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + 1 + slack, ignore_eos=True)
-    reqs = [eng.submit(torch.randint(0, mc.vocab_size, (plen,), generator=gen).tolist(), gp) for _ in range(B)]
-    while any(not r.output for r in reqs):
-        eng.step()
-    for _ in range(e2e_warm):
-        eng.step()
-    torch.cuda.synchronize()
-    t_e2e = time.perf_counter()
-    step_ms = []
-    for _ in range(e2e_steps):
-        t_s = time.perf_counter()
-        eng.step()
-        step_ms.append((time.perf_counter() - t_s) * 1e3)
-    torch.cuda.synchronize()
-    if os.environ.get("IMP_BENCH_DEBUG"):
-        print("e2e step ms:", [round(x, 2) for x in step_ms], "graphs", sorted(eng.stepper._graphs),
-              "running", len(eng.scheduler.running), file=sys.stderr)
-    e2e_ms = (time.perf_counter() - t_e2e) / e2e_steps * 1e3
-    assert all(not r.done and len(r.output) >= 1 + e2e_warm + e2e_steps for r in reqs), "a request left the batch"
-    for r in reqs:
-        eng.scheduler.cancel(r.rid)
-    buf = eng.stepper.buffers
-    h2d = 4 * (buf.small_words + len(buf.bt_off) * B * buf.max_pages)
-    d2h = 4 * B + 4
+    # ---- the configuration's own protocol: 2,048 -> 4,096 at batch 1, 8 and 64 ------------------------------
+    protocol, points = {}, {}
+    if not args.quick:
+        for b in (1, 8, 64):
+            r = decode_protocol(eng, rng, cfgd, n_layers, b, peaks)
+            protocol[f"b{b}"] = r
+            points[f"decode_b{b}"] = r["all"]["tok_s"]
+            points[f"decode_b{b}_ms"] = r["all"]["ms"]
+            points[f"decode_b{b}_frac"] = r["all"]["frac"]
+    info = eng.info()
+    eng.close()
 
     line = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, context 4096); prefill tok/s at 2,048 tokens",
-        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K_, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": "Qwen3-8B-shaped", "layers": n_layers, "layers_of_config": MODEL["num_hidden_layers"],
                    "hidden": cfgd["hidden_size"], "q_heads": cfgd["num_attention_heads"],
                    "kv_heads": cfgd["num_key_value_heads"], "head_dim": cfgd["head_dim"],
                    "intermediate": cfgd["intermediate_size"], "vocab": cfgd["vocab_size"],
-                   "global_batch": B, "seq_len": CONTEXT, "page_size": args.page or PAGE, "weights": "random N(0,0.02) seed 0",
+                   "global_batch": B, "seq_len": CONTEXT, "max_positions": CONTEXT + STAGGER, "page_size": args.page or PAGE,
+                   "weights": "random N(0,0.02) seed 0",
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (16 GB of weights per step)",
-                   "cache_fill": "random pages for value/points, real prefill for e2e",
-                   "peaks": peak_src},
+                   "cache_fill": "real prefill", "api": "C API through the Python entry point", "peaks": peak_src},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "protocol": protocol,
         "e2e": {"value": round(B / e2e_ms * 1e3, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B + 4},
         "gpu_launches": launches,
+        "fallback_calls": info["fallback_calls"],
         "clocks": clocks.summary(),
         "setup_s": round(setup_s, 1),
-        "library": os.path.basename(library.loaded_library_path() or ""),
+        "workspace_mb": round(info["workspace_bytes"] / 2 ** 20, 1),
     }
+    if not args.quick:
+        try:
+            line["yardsticks"] = yardsticks(peaks)
+            line["yardsticks"]["prefill_2048_on_cublaslt"] = library_arm_prefill(args)
+            line["yardsticks"]["prefill_2048_own_ms"] = prefill["ms"]
+        except Exception as e:
+            line["yardsticks"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    from imp_b200 import capi
+    line["library"] = os.path.basename(capi.loaded_library_path() or "")
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------- workloads
+def run_workload(args):
+    """The two other workloads of the baseline record, through Engine.submit / Engine.step.  Protocol of the
+    reference's own bench loop (tools/imp-cli/main.cpp:142-215): synthetic ids, one discarded warm-up, wall clock."""
+    from imp_b200 import GenerateParams
+    peaks, peak_src = read_peaks()
+    rng = random.Random(1)
+    if args.workload == "0.6b":
+        cfgd = dict(MODEL_06B)
+        n_req, chunk, ctx, gen = 64, 512, 8192, 256
+        lens = [rng.randint(16, 1024) for _ in range(n_req)]
+        gp = GenerateParams(temperature=0.0, max_tokens=gen, ignore_eos=True)
+        seed, budget, max_batch = 2, 2048, 64
+    else:
+        cfgd = dict(MODEL_14B)
+        n_req, chunk, ctx, gen = 8, 2048, 16384, 512
+        lens = [8192] * n_req
+        gp = GenerateParams(temperature=0.7, top_k=40, top_p=0.9, seed=7, max_tokens=gen, ignore_eos=True)
+        seed, budget, max_batch = 3, 2048 + 8, 8
+    if args.layers:
+        cfgd["num_hidden_layers"] = args.layers
+    n_layers = cfgd["num_hidden_layers"]
+    dtype = args.dtype
+    if dtype == "float32":
+        cfgd["torch_dtype"] = "float32"
+    eng, setup_s = make_engine(cfgd, args, max_batch, ctx, budget=budget, chunk=chunk, dtype=dtype, seed=seed,
+                               pool_tokens=sum(lens) + n_req * (gen + 2 * (args.page or PAGE)))
+    V = cfgd["vocab_size"]
+    warm = eng.generate([random_prompt(rng, V, 40)], GenerateParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert len(warm[0]) == 4
+    prompts = [random_prompt(rng, V, n) for n in lens]
+    reqs = [eng.submit(p, gp) for p in prompts]
+    t0 = time.perf_counter()
+    n_steps = decode_only_steps = 0
+    decode_s = 0.0
+    live = {r.rid for r in reqs}
+    first_token_at = {}
+    while live:
+        all_decoding = len(first_token_at) == n_req      # every prompt has been read: this step only decodes
+        t_s = time.perf_counter()
+        outs = eng.step()
+        dt = time.perf_counter() - t_s
+        n_steps += 1
+        if all_decoding:
+            decode_only_steps += 1
+            decode_s += dt
+        for o in outs:
+            first_token_at.setdefault(o.rid, time.perf_counter() - t0)
+            if o.finished:
+                live.discard(o.rid)
+    eng.drain()
+    total_s = time.perf_counter() - t0
+    n_out = sum(len(r.output) for r in reqs)
+    assert n_out == n_req * gen, f"{n_out} tokens generated, {n_req * gen} expected"
+    info = eng.info()
+    _, weight_bytes, kv_per_tok = model_numbers(cfgd, n_layers)
+    elem = 2 if dtype == "bfloat16" else 4
+    line = {"workload": args.workload, "dtype": dtype, "layers": n_layers, "requests": n_req, "prompt_tokens": sum(lens),
+            "generated_tokens": n_out, "seconds": round(total_s, 3), "steps": n_steps,
+            "generated_tok_s": round(n_out / total_s, 1), "total_tok_s": round((n_out + sum(lens)) / total_s, 1),
+            "time_to_last_first_token_s": round(max(first_token_at.values()), 3),
+            "prefill_tok_s": round(sum(lens) / max(first_token_at.values()), 1),
+            "decode_only_steps": decode_only_steps,
+            "decode_ms_per_step": round(decode_s / decode_only_steps * 1e3, 3) if decode_only_steps else None,
+            "preemptions": info["scheduler"]["preemptions"], "fallback_calls": info["fallback_calls"],
+            "graph_replays": info["graph_replays"], "setup_s": round(setup_s, 1), "peaks": peak_src}
+    if decode_only_steps:
+        mean_ctx = sum(lens) / n_req + gen / 2
+        gbs = (weight_bytes * elem / 2 + n_req * mean_ctx * kv_per_tok * elem / 2) / (decode_s / decode_only_steps) / 1e9
+        line["decode_roofline_frac"] = round(gbs / peaks["hbm_gbs"], 4)
     print(json.dumps(line))
     return 0
 
 
 def run_reference(args):
-    # The reference is a CMake C++/CUDA project (no setup.py or pyproject.toml; CUDA >= 13.1 and
-    # network fetches at configure time), so the one offline install attempt fails before any build.
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "kekzl/imp is not pip-installable (no setup.py/pyproject.toml; CMake needs "
-                                     "CUDA >= 13.1 and network fetches): pip install --target baseline/_ref failed"}))
+    """The one offline install the contract describes is attempted once (it cannot succeed: the reference is a
+    CMake C++/CUDA project without setup.py or pyproject.toml, it needs CUDA >= 13.1 where this image has 12.9,
+    and its configure step fetches googletest, CUTLASS and two more projects from the network)."""
+    why = "kekzl/imp is not pip-installable (no setup.py/pyproject.toml; CMake needs CUDA >= 13.1 and network fetches)"
+    target = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(target) or not os.listdir(target):
+        if os.path.isdir("/root/reference") and os.path.isdir("/opt/wheelhouse"):
+            try:
+                p = subprocess.run([sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--find-links",
+                                    "/opt/wheelhouse", "--target", target, "/root/reference"], capture_output=True, text=True, timeout=300)
+                tail = (p.stderr or p.stdout).strip().splitlines()
+                why += f": pip install --target baseline/_ref exited {p.returncode}" + (f" ({tail[-1][:160]})" if tail else "")
+            except Exception as e:
+                why += f": pip install could not run ({type(e).__name__})"
+        else:
+            why += ": no reference tree or wheelhouse on this machine, nothing was attempted"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
@@ -346,9 +522,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one phase only and print its timing (for profiling small cases)")
+    ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
+    ap.add_argument("--quick", action="store_true", help="skip the 2,048-step protocol runs and the yardsticks")
     ap.add_argument("--context", type=int, default=0,
                     help="with --only decode: the contexts end here instead of at the configured length (may be longer)")
     ap.add_argument("--tokens", type=int, default=0, help="with --only prefill: tokens of the prompt (at most 2048)")
+    ap.add_argument("--chunk", type=int, default=0, help="with --only prefill: portions of this many tokens (0 = whole)")
     ap.add_argument("--page", type=int, default=0, help="tokens per cache page (0 = the default of the engine's configuration)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = ap.parse_args()
@@ -359,6 +539,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload:
+        return run_workload(args)
     return run_ours(args)
 
 
