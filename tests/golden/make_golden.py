@@ -1,9 +1,9 @@
 """Writes tests/golden/plain_tiny.json: logits of the plain implementation on two tiny random models.
 
-The plain implementation (tests/plain/qwen3_plain.py) rests on kekzl/imp's formulas, not on its
-code, which cannot be built or run here (CUDA-only model code, CUDA >= 13.1, network fetches).
-These numbers therefore pin the plain implementation against accidental change; they are not
-outputs of the reference.  Run from the repository root:  python tests/golden/make_golden.py
+These numbers pin the whole plain model (tests/plain/qwen3_plain.py) against accidental change; they
+are not outputs of the reference, whose whole model cannot be built or run here (CUDA-only model
+code, CUDA >= 13.1, network fetches).  What the reference's own kernels compute, part by part, is
+stored in reference_anchor.json (see make_reference_anchor.py).  Run from the repository root:  python tests/golden/make_golden.py
 """
 import json
 import os

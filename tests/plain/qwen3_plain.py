@@ -1,10 +1,15 @@
 """A plain, slow implementation of the Qwen3 dense decoder: whole sequences, no cache.
 
 It rests on the formulas of kekzl/imp's sources (cited per function by the
-file's path within that project), not on running its code: the reference's
-model code is CUDA-only and cannot be built here (it needs CUDA >= 13.1,
-CMakeLists.txt:15, and fetches dependencies from the network, :44-68), so there
-is no golden output of the reference to compare with.
+file's path within that project).  The reference's model code is CUDA-only and
+cannot be built as a project here (it needs CUDA >= 13.1, CMakeLists.txt:15, and
+fetches dependencies from the network, :44-68), so no whole-model output of the
+reference exists; but its kernel files compile one by one, and
+tests/golden/reference_anchor.json holds what they gave on a B200 for tiny
+inputs.  tests/test_reference_anchor.py pins the per-part functions below
+(rmsnorm, rope, the q/k norm before the rotation, the SwiGLU activation,
+embedding, attention, the greedy tie rule) on those outputs; the order of the
+parts inside a layer and the tied head rest on reading.
 
 One function per part.  Nothing here is shared with the engine: this file
 reads config.json and model.safetensors by itself and computes on the CPU in
