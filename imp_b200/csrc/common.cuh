@@ -26,6 +26,9 @@ enum ImpStatus : int {
 #define IMP_ERR_UNSUPPORTED (-2)
 
 void imp_set_error(const char* fmt, ...);
+// Streaming multiprocessors of the current device (asked once per device); launch heuristics size their
+// grids by it.  1 when the device cannot be asked: the launch that follows reports the real error.
+int imp_sm_count();
 
 #define IMP_CHECK_ARG(cond, ...)            \
     do {                                    \

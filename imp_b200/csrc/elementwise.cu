@@ -96,10 +96,11 @@ IMP_API int imp_swiglu(void* out, const void* gate_up, int n_tokens, int F, int 
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t total = (int64_t)n_tokens * F;
     const int threads = 256;
-    const int grid = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const int64_t sms = imp_sm_count();
+    const int grid = (int)((total + threads - 1) / threads < sms * 16 ? (total + threads - 1) / threads : sms * 16);
     if (dtype == IMP_BF16 && F % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
         const int64_t work = total >> 3;
-        const int g8 = (int)((work + threads - 1) / threads < 148 * 32 ? (work + threads - 1) / threads : 148 * 32);
+        const int g8 = (int)((work + threads - 1) / threads < sms * 32 ? (work + threads - 1) / threads : sms * 32);
         swiglu_bf16_vec_kernel<<<g8, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n_tokens, F, block);
     } else if (dtype == IMP_F32)
         swiglu_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)gate_up, n_tokens, F, block);
@@ -124,7 +125,8 @@ IMP_API int imp_cast(void* dst, int dst_dtype, const void* src, int src_dtype, i
     cudaStream_t s = (cudaStream_t)stream;
     const int block = 256;
     const int64_t want = (n + block - 1) / block;
-    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int64_t cap = (int64_t)imp_sm_count() * 16;
+    const int grid = (int)(want < cap ? want : cap);
     if (src_dtype == IMP_F32 && dst_dtype == IMP_BF16)
         cast_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>((__nv_bfloat16*)dst, (const float*)src, n);
     else if (src_dtype == IMP_BF16 && dst_dtype == IMP_F32)

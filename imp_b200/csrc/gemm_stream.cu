@@ -213,7 +213,7 @@ static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, 
                       A, lda, W, ldw, M, N, K);
 }
 
-// Ring depth.  Five stages let three CTAs share an SM (444 resident CTAs on 148 SMs).  A product with
+// Ring depth.  Five stages let three CTAs share an SM (444 resident CTAs on a B200's 148 SMs).  A product with
 // so few tiles that two CTAs per SM hold them all runs eight stages instead: every CTA then keeps
 // 56 KiB of weight reads in flight, which the memory needs when only a few hundred CTAs pull on it.
 // IMP_B200_GS_STAGES=4|5|6|8 forces one depth (for measurements).
@@ -231,17 +231,18 @@ static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, 
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
     int stages = gs_env_stages();
     // Up to 8 tokens: two row groups per CTA where 32-row tiles still give about one CTA per SM or more.
-    // With at least 148 such tiles, four stages of 21 KiB (two CTAs per SM); with 96..147 tiles, six stages
-    // (one CTA per SM, 80 KiB of weight reads in flight each).  IMP_B200_GS_RG=1 keeps 16-row tiles
+    // With at least one such tile per SM, four stages of 21 KiB (two CTAs per SM); with two thirds of that
+    // and more (96..147 tiles on 148 SMs), six stages (one CTA per SM, 80 KiB of weight reads in flight each).  IMP_B200_GS_RG=1 keeps 16-row tiles
     // everywhere, =2 uses 32-row tiles only in the first case.
     static int rg_env = -1;
     if (rg_env < 0) { const char* e = getenv("IMP_B200_GS_RG"); rg_env = e ? atoi(e) : 3; }
     // (With one or two tokens the activations are a small share of the traffic and more, smaller CTAs win.)
-    if (NT == 1 && M >= 3 && rg_env >= 2 && stages == 0 && (N + 31) / 32 >= 148)
+    const int sms = imp_sm_count();
+    if (NT == 1 && M >= 3 && rg_env >= 2 && stages == 0 && (N + 31) / 32 >= sms)
         return launch_stream_st<1, TO, SWIGLU, 4, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
-    if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= 96 && (N + 31) / 32 < 148)
+    if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= (sms * 2 + 2) / 3 && (N + 31) / 32 < sms)
         return launch_stream_st<1, TO, SWIGLU, 6, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
-    if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * 148) ? 8 : 5;
+    if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * sms) ? 8 : 5;
     switch (stages) {
         case 4: return launch_stream_st<NT, TO, SWIGLU, 4, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
         case 6: return launch_stream_st<NT, TO, SWIGLU, 6, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);

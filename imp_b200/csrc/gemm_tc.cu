@@ -646,6 +646,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
 // splits == 1) lanes r and r + 8 of every 16 hold gate and up of one output column.
 constexpr int TCS_W_BYTES = 128 * TC_BK * 2;   // 16 KiB
 
+// For the test of the give-up paths only (imp_gemm_tc_test_hooks): the K block whose stage the producer of
+// gemm_tc_swap_kernel leaves unfilled, so that the waits behind it cannot succeed.  -1 in every other run.
+static __constant__ int tcs_test_skip_kb = -1;
+
 // Ring depth.  Up to 32 tokens: five stages of 20 KiB; up to 64: four of 24 KiB; both so that two CTAs share an SM
 // (and its memory pipes).  More tokens: six stages of 32 KiB, one CTA per SM.  (Five stages measured 0.7 % faster
 // than four on the whole decode step at 8 to 32 rows; six would leave room for one CTA only.)
@@ -717,6 +721,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
             const int s = i % TCS_STAGES;
             ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status);
             if (!ok) break;
+            if (i == tcs_test_skip_kb) { issued = i + 1; continue; }
             const uint32_t w_dst = smem_u32(tiles + s * STAGE), x_dst = w_dst + TCS_W_BYTES;
             mbar_expect_tx(full0 + 8 * s, stage_tx);
             tma_load_2d(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * s);
@@ -852,9 +857,7 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
     static int mode = -1, sms = 0;   // IMP_B200_TC_SIMPLE=1 selects the one-tile-per-CTA kernel
     if (mode < 0) {
         mode = getenv("IMP_B200_TC_SIMPLE") ? 1 : 0;
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
+        sms = imp_sm_count();
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); mode = -1; return (int)e; }
     }
@@ -917,12 +920,7 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
 #ifndef TCS_MIN_KB_PER_SPLIT
 #define TCS_MIN_KB_PER_SPLIT 6     // blocks of K a split has at least
 #endif
-static int tcs_sms() {
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        sms = 148;
-    return sms;
-}
+static int tcs_sms() { return imp_sm_count(); }
 
 // Weight rows of a CTA's tile when K is not split.  All CTAs are resident at once (two per SM up to 64 tokens),
 // handed out round robin, so the SM with the most CTAs sets the time: 192 tiles of 128 rows put two tiles on 44 SMs
@@ -1012,7 +1010,8 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
         if (rc) return rc;
         if (partials_only) IMP_RETURN_LAUNCH();
         const int64_t total = (int64_t)M * N;
-        const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        const int64_t cap = (int64_t)imp_sm_count() * 8;
+        const int grid = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
         cudaError_t e;
         if (epilogue == TC_OUT_F32)
             e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, (const float*)scratch,
@@ -1036,6 +1035,22 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
     }
     if (rc) return rc;
     IMP_RETURN_LAUNCH();
+}
+
+// Test hooks of the bounded waits.  `wait_limit` polls (0: the regular limit) bound every mbarrier wait of the
+// kernels in this file from the next launch on, and the producer of the few-rows kernel leaves the stage of K
+// block `skip_kb` unfilled (-1: none; blocks inside the first ring depth are never skipped), so that the MMA
+// thread's wait for it, the producer's later wait for the slot and its wait for its own copies all run out.
+// The kernel then reports IMP_WAIT_TIMEOUT through the status word, frees its tensor memory and returns.
+// A test lowers the limit to a few thousand polls for one CTA and restores both values afterwards.
+IMP_API int imp_gemm_tc_test_hooks(unsigned wait_limit, int skip_kb) {
+    const uint32_t limit = wait_limit ? wait_limit : TC_WAIT_LIMIT;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(tc_wait_limit, &limit, sizeof limit);
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(tcs_test_skip_kb, &skip_kb, sizeof skip_kb);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { imp_set_error("imp_gemm_tc_test_hooks: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
 }
 
 IMP_API int imp_gemm_bf16_tc_swap(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
@@ -1065,7 +1080,8 @@ IMP_API int imp_gemm_bf16_tc_swap_sum(void* C, int64_t ldc, int epilogue, const 
                   "imp_gemm_bf16_tc_swap_sum: bad argument");
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t total = (int64_t)M * N;
-    const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    const int64_t cap = (int64_t)imp_sm_count() * 8;
+    const int grid = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
     cudaError_t e;
     if (epilogue == TC_OUT_F32)
         e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, scratch, total, M, N, splits);
@@ -1097,14 +1113,12 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     if (K % 8 || lda % 8 || ldw % 8 || q_stride % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)q_out % 16 ||
         (uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16)
         return IMP_ERR_UNSUPPORTED;
-    static int ready = -1, sms = 148;
+    static int ready = -1, sms = 2;
     if (ready < 0) {
         const char* e = getenv("IMP_B200_TC_PAIR");
         ready = (e == nullptr || atoi(e) != 0) && getenv("IMP_B200_TC_SIMPLE") == nullptr ? 1 : 0;
         if (ready) {
-            int dev = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 1)
-                sms = 148;
+            sms = imp_sm_count() < 2 ? 2 : imp_sm_count();
             cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   TC2_SMEM_BYTES);
             if (e2 != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e2)); ready = -1; return (int)e2; }

@@ -177,11 +177,13 @@ std::vector<TilingSpec> attention_tilings() {
 // The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with fewer
 // (token, kv head) pairs than such slots the keys are split until the slots are full.  With more, the
 // split count with the least modelled time is taken.  The model (fitted to measurements at 40 to 128
-// sequences on 148 SMs): a CTA alone streams about 1/150 of what the device can, so a wave of CTAs runs
+// sequences on a B200): a CTA alone streams about 1/150 of what its 148 SMs can, so a wave of CTAs runs
 // at full speed from about one CTA per SM up, and a last wave of fewer runs as slowly as each of its
 // CTAs; splitting costs the merge kernel and the partial results, about a tenth of one CTA's work.
+constexpr double B200_SMS = 148.0;   // the part the model's constant was fitted on
+
 int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count) {
-    const int sms = sm_count > 0 ? sm_count : 148;
+    const int sms = sm_count > 0 ? sm_count : std::max(1, imp_device_sm_count());
     const int base = std::max(1, n_tokens * n_kv_heads * ((group + 15) / 16));
     if (page_size % 16) return std::max(1, std::min(DECODE_MAX_SPLITS, sms * 3 / base));
     const int slots = 2 * sms;
@@ -193,7 +195,7 @@ int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm
         while (p * 2 <= s) p *= 2;
         return p;
     }
-    const double saturating = 150.0 / 148.0 * sms;
+    const double saturating = sms * (150.0 / B200_SMS);   // scaled with the SMs the device has
     int best = 1;
     double best_t = 0;
     for (int s = 1; s <= 8; ++s) {

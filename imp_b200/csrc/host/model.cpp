@@ -193,6 +193,10 @@ void stage(Step& st, const char* name, const Tensor& t) {
     st.diag->stage(st, st.layer >= 0 ? "layer" + std::to_string(st.layer) + "." + name : std::string(name), t);
 }
 
+void stage(Step& st, const char* name, const Branch& b) {
+    if (st.diag) stage(st, name, b.split() ? Tensor{} : b.t);
+}
+
 // -------------------------------------------------------------------------------- device model
 DeviceModel::DeviceModel(const HostModel& host, Runtime* rt) : plan_(host.plan), rt_(rt), factory_(rt, &store_) {
     std::vector<std::pair<std::string, Tensor>> placed;

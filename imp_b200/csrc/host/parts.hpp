@@ -102,6 +102,8 @@ struct LayerCache {
 // A named point of the forward pass: with IMP_B200_PROFILE a timer stops here, with
 // IMP_B200_DEBUG_FORWARD the tensor's statistics are printed.  Does nothing otherwise.
 void stage(Step& st, const char* name, const Tensor& t);
+struct Branch;
+void stage(Step& st, const char* name, const Branch& b);   // an unsummed branch stops the timer and has no statistics
 
 // A branch output: nothing, a tensor, or the unsummed parts of one ([n_splits, M, N] float32 whose
 // sum in split order, rounded to `t`'s type, is the value that belongs into `t`).

@@ -266,9 +266,12 @@ struct PreNormBlock : Block {
     Branch forward(Step& st, Tensor h, const Branch& pending, LayerCache* cache) override {
         Tensor x = norm1->add_norm(st, h, pending);
         Branch a = mixer_->forward(st, x, cache);
+        stage(st, "mixer", a);                  // time since the stage before: first norm and mixer
         x = norm2->add_norm(st, h, a);
         ffn->defer_out = defer_pending;
-        return ffn->forward(st, x);
+        Branch f = ffn->forward(st, x);
+        stage(st, "feed_forward", f);           // second norm and feed-forward
+        return f;
     }
 };
 

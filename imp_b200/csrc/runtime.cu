@@ -45,6 +45,17 @@ IMP_API int imp_device_sm_count(void) {
     return n;
 }
 
+int imp_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 1;
+    if (dev < 64 && cached[dev] > 0) return cached[dev];
+    const int n = imp_device_sm_count();
+    if (n <= 0) return 1;
+    if (dev < 64) cached[dev] = n;
+    return n;
+}
+
 const char* imp_status_name(int code) {
     switch (code) {
         case IMP_OK: return "ok";

@@ -8,6 +8,9 @@
 #include <cuda.h>
 
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;   // polls of mbarrier.try_wait (each suspends for a while): about a second
+// The limit the waits read (one copy per translation unit).  It only ever differs from TC_WAIT_LIMIT while a test
+// of the give-up paths has lowered it, so that a wait which cannot succeed runs out in milliseconds.
+static __constant__ uint32_t tc_wait_limit = TC_WAIT_LIMIT;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -19,7 +22,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 // Bounded wait for the phase with the given parity; false (and a status report) when it runs out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+    const uint32_t limit = tc_wait_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n"

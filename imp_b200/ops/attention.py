@@ -118,9 +118,10 @@ def _check(lib, rc: int, what: str) -> None:
         raise L.KernelError(f"{what} failed ({rc}): {lib.imp_last_error().decode(errors='replace')}")
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16, sm_count: int = 148) -> int:
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16, sm_count: int = 0) -> int:
     """Key splits of the decode kernel as the library chooses them (csrc/host/attention.cpp `decode_splits`):
-    a function of the batch size alone, since a captured graph must not depend on the context length."""
+    a function of the batch size alone, since a captured graph must not depend on the context length.
+    `sm_count` 0 asks the device."""
     return int(L.load().imp_op_decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count))
 
 

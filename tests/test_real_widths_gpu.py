@@ -1,8 +1,16 @@
-"""The engine at the layer widths of the benchmark model (hidden 4096, 32 query / 8 kv heads of 128,
-inner 12288), two layers and a reduced, odd vocabulary, against the plain implementation: the shapes
-at which the tensor-memory GEMMs (single CTAs, CTA pairs, swap-AB), the weight-streaming GEMM with
-32-row tiles and the tensor-memory attention run in the benchmark, here checked for their numbers.
+"""The engine at the layer widths of three real models, two layers each and a reduced, odd vocabulary,
+against the plain implementation: the shapes at which the tensor-memory GEMMs (single CTAs, CTA pairs,
+swap-AB), the weight-streaming GEMM with 32-row tiles and the tensor-memory attention run in the
+benchmarks, here checked for their numbers.
+
+  8b    hidden 4096, 32 query / 8 kv heads of 128, inner 12288, separate head
+  0.6b  hidden 1024 (not heads x head size), 16 / 8 heads of 128: two query heads a kv head, inner 3072, tied head
+  14b   hidden 5120, 40 / 8 heads of 128: FIVE query heads a kv head (an odd group for the attention kernels
+        that take one or two heads of a group per CTA), inner 17408 = 68 x 256 (a ragged last tile column
+        for the CTA-pair product)
 """
+import shutil
+
 import numpy as np
 import pytest
 import torch
@@ -17,20 +25,30 @@ WIDE = {
     "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
     "max_position_embeddings": 1024,
 }
+SHAPES = {
+    "8b": WIDE,
+    "0.6b": dict(WIDE, vocab_size=30011, hidden_size=1024, num_attention_heads=16, intermediate_size=3072, tie_word_embeddings=True),
+    "14b": dict(WIDE, vocab_size=15013, hidden_size=5120, num_attention_heads=40, intermediate_size=17408),
+}
+ALL_SHAPES = pytest.mark.parametrize("wide", list(SHAPES), indirect=True)
+ONLY_8B = pytest.mark.parametrize("wide", ["8b"], indirect=True)
 
 
 @pytest.fixture(scope="module")
-def wide(tmp_path_factory):
+def wide(request, tmp_path_factory):
     from imp_b200.config.registry import config_from_dict
     from imp_b200.weights.random_init import write_model_folder
+    config = SHAPES[request.param]
     folder = str(tmp_path_factory.mktemp("wide"))
-    write_model_folder(folder, config_from_dict(WIDE), seed=3, std=0.02)
+    write_model_folder(folder, config_from_dict(config), seed=3, std=0.02)
     g = torch.Generator().manual_seed(8)
-    ids = {name: torch.randint(0, WIDE["vocab_size"], (n,), generator=g).tolist()
+    ids = {name: torch.randint(0, config["vocab_size"], (n,), generator=g).tolist()
            for name, n in (("a", 300), ("b", 140), ("c", 33))}
     plain = PlainModel(folder)
     ref = {name: plain.logits(v) for name, v in ids.items()}
-    return folder, ids, ref
+    del plain
+    yield folder, ids, ref
+    shutil.rmtree(folder, ignore_errors=True)
 
 
 def run(eng, ids, plan):
@@ -59,6 +77,7 @@ def engine(folder, dtype):
                                                    kv_cache_tokens=24 * 512, max_batch_tokens=640))
 
 
+@ALL_SHAPES
 def test_bfloat16_at_real_widths(wide):
     folder, ids, ref = wide
     eng = engine(folder, "bfloat16")
@@ -81,6 +100,9 @@ def test_bfloat16_at_real_widths(wide):
     plan += [[("a", 1), ("b", 1)] for _ in range(20)]
     plan += [[("a", 49), ("b", 48)]]
     check(run(eng, ids, plan), "portions and decode")
+    # one step of 320 tokens over three sequences, then the rest: the fused q,k,v epilogue (norm, rotation, page write)
+    # of the wide products in a mixed batch, where a tile of rows holds the end of one sequence and the start of another
+    check(run(eng, ids, [[("a", 200), ("b", 100), ("c", 20)], [("c", 13), ("a", 100), ("b", 40)]]), "a mixed step of 320 tokens")
     # twenty sequences decoding together (the swap-AB kernel's shape in decode): twenty copies of c, last 3 tokens
     many = {f"c{i}": ids["c"] for i in range(20)}
     from imp_b200 import StepEntry
@@ -99,6 +121,7 @@ def test_bfloat16_at_real_widths(wide):
     assert eng.info()["fallback_calls"] == 0, "a matrix product fell back to the plain kernel"
 
 
+@ALL_SHAPES
 def test_float32_at_real_widths_is_exact_under_cutting(wide):
     folder, ids, ref = wide
     eng = engine(folder, "float32")
@@ -112,6 +135,7 @@ def test_float32_at_real_widths_is_exact_under_cutting(wide):
         assert np.array_equal(whole[r].numpy(), cut[r].numpy()), f"request {r}: logits depend on the cut"
 
 
+@ONLY_8B
 def test_a_norm_that_knows_nothing_of_unsummed_branches_gets_tensors(wide, tmp_path, monkeypatch):
     """Products of few rows leave their K-split partial sums to the norm that reads them next, but only to a norm
     that says it takes them.  Here the second norm of layer 1 and the final norm are a norm defined in this test

@@ -1,9 +1,15 @@
 """Key splits of the decode attention: chosen from the batch alone, within bounds, and as measured."""
-from imp_b200.ops.attention import DECODE_MAX_SPLITS, decode_splits
+from functools import partial
+
+from imp_b200.ops.attention import DECODE_MAX_SPLITS
+from imp_b200.ops.attention import decode_splits as device_splits
+
+SMS = 148                                               # a B200; another count is tried below
+decode_splits = partial(device_splits, sm_count=SMS)
 
 
 def test_splits_fill_the_device_for_small_batches_and_stop_for_large_ones():
-    slots = 2 * 148
+    slots = 2 * SMS
     for batch in range(1, 300):
         s = decode_splits(batch, 8, 4, 16)
         assert 1 <= s <= DECODE_MAX_SPLITS
@@ -25,3 +31,14 @@ def test_groups_above_sixteen_count_as_several_row_tiles():
 def test_other_page_sizes_use_the_direct_kernel_rule():
     assert decode_splits(1, 8, 4, 3) >= 1
     assert decode_splits(1000, 8, 4, 3) == 1
+
+
+def test_the_rule_scales_with_the_number_of_sms():
+    for sms in (132, 74, 20):
+        slots = 2 * sms
+        for batch in (1, 3, 8, 17):
+            s = device_splits(batch, 8, 4, 16, sm_count=sms)
+            base = batch * 8
+            if base <= slots:
+                assert base * s <= slots and (base * s * 2 > slots or s == DECODE_MAX_SPLITS)
+    assert device_splits(8, 8, 4, 16, sm_count=74) == 2
