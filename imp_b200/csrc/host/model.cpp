@@ -169,6 +169,7 @@ Json Diagnostics::profile_json() const {
     Json j = Json::object();
     j["steps"] = steps_;
     j["ms_per_step"] = steps_ ? total_ms_ / steps_ : 0.0;
+    j["last_step_ms"] = (double)last_step_ms;
     Json st = Json::array();
     for (size_t i = 0; i < sums_.size(); ++i) {
         Json o = Json::object();

@@ -65,13 +65,32 @@ def test_profile_timers_name_every_stage_and_add_up_to_the_step(model_folders):
     assert all(s["ms"] > 0 for s in prof["stages"])
     total = sum(s["ms"] for s in prof["stages"])
     assert abs(total - prof["ms_per_step"]) <= 1e-3 * prof["ms_per_step"]
-    # the step's own device time (events around batch upload, forward pass and the copy of the logits) holds the
-    # timed stages and little else
-    step_ms = sum(out["timed_ms"]) / len(out["timed_ms"])
-    assert total <= step_ms * 1.001 and total >= 0.9 * step_ms, f"stages {total:.4f} ms of a step of {step_ms:.4f} ms"
+    # the stages lie inside the step's own device time (events around batch upload, forward pass and the copy of the logits)
+    assert prof["last_step_ms"] <= out["timed_ms"][-1] * 1.001
     # a model that is not asked to profile reports nothing and prints nothing
     plain_out, plain_err = run(folder, page, ids)
     assert "profile" not in plain_out["model"] and "[profile]" not in plain_err
+
+
+def test_profile_timers_cover_the_step_where_the_device_is_the_limit(tmp_path):
+    """On the tiny model a step is a few launches long and the time around the forward pass (batch upload, copy of the
+    logits) is a third of it.  At a width where the device works for milliseconds the stages must hold the step's time
+    to within a tenth."""
+    from imp_b200.config.registry import config_from_dict
+    from imp_b200.weights.random_init import write_model_folder
+    cd = {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 2003, "hidden_size": 1024, "num_hidden_layers": 3,
+          "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 3072, "rms_norm_eps": 1e-6,
+          "rope_theta": 1000000.0, "tie_word_embeddings": True, "torch_dtype": "bfloat16", "max_position_embeddings": 512}
+    folder = str(tmp_path / "medium")
+    write_model_folder(folder, config_from_dict(cd), seed=4, std=0.02)
+    ids = torch.randint(0, cd["vocab_size"], (512,), generator=torch.Generator().manual_seed(3)).tolist()
+    out, _ = run(folder, 16, ids, IMP_B200_PROFILE="1")
+    prof = out["model"]["profile"]
+    assert [s["stage"] for s in prof["stages"]] == stage_names(3)
+    step_ms, staged_ms = out["timed_ms"][-1], prof["last_step_ms"]
+    assert staged_ms <= step_ms * 1.001 and staged_ms >= 0.9 * step_ms, f"stages {staged_ms:.4f} ms of a step of {step_ms:.4f} ms"
+    layers = [s["ms"] for s in prof["stages"] if s["stage"].startswith("layer")]
+    assert sum(layers) >= 0.8 * prof["ms_per_step"]                   # the time is in the layers, not in the head of 2003 rows
 
 
 def test_debug_forward_statistics_are_those_of_the_plain_computation(model_folders):
