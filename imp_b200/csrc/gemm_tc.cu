@@ -340,6 +340,14 @@ struct QkvRopeArgs {
     int bt_stride, n_seqs, max_pos, Hq, Hkv, Dh, page_size, num_pages;
 };
 
+// The product as the other paths see it: rounded to bfloat16 before the per-head norm and the rotation, so that a
+// token's cached key has the same bits whether its q,k,v came from this epilogue or from a product that wrote
+// bfloat16 and a separate norm-and-rotation kernel.
+__device__ __forceinline__ void round32_bf16(float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+}
+
 __device__ __forceinline__ void store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -404,6 +412,7 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
             for (int c = 0; c < chunks; ++c) {
                 float v[32];
                 tc_ld32(thead + (uint32_t)(c * 32), v);
+                round32_bf16(v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) ss = fmaf(v[i], v[i], ss);
             }
@@ -419,6 +428,8 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
             tc_ld32(thead + (uint32_t)(c * 32), x);
             tc_ld32(thead + (uint32_t)(half + c * 32), y);
             if (dst == nullptr) continue;
+            round32_bf16(x);
+            round32_bf16(y);
             // the table row of this token is read 16 bytes at a time: 32 rows touch 32 sectors per load either
             // way, so fewer, wider loads keep the L1 out of the way
 #pragma unroll

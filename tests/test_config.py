@@ -34,6 +34,15 @@ def test_layer_types_choose_window_per_layer():
     assert [l.mixer.params["window"] for l in plan.layers] == [9, 0, 9, 0]
 
 
+def test_end_tokens_are_kept_as_a_list(tmp_path):
+    assert config_from_dict(TINY_A).eos_token_ids == ()
+    assert config_from_dict(dict(TINY_A, eos_token_id=9)).eos_token_ids == (9,)
+    c = config_from_dict(dict(TINY_A, eos_token_id=[9, 200]))
+    assert c.eos_token_ids == (9, 200)
+    c.save(str(tmp_path))
+    assert load_config(str(tmp_path)).eos_token_ids == (9, 200)
+
+
 def test_round_trip_through_folder(tmp_path):
     c = config_from_dict(TINY_C)
     c.save(str(tmp_path))

@@ -225,3 +225,32 @@ def test_lookahead_overlaps_only_when_it_may(model_folders):
     while not pen.done:
         eng.step()
         assert not eng.info()["inflight"]              # the penalty reads the tokens on the host
+
+
+def test_a_second_end_token_in_config_json_ends_generation(model_folders, tmp_path):
+    """`eos_token_id` may be a list; every id of it ends a request.  The model folder is copied with a list whose
+    SECOND entry is a token that a seeded run samples a few steps in: generation stops there, and runs on with ignore_eos."""
+    import json
+    import shutil
+
+    from imp_b200 import GenerateParams
+    from imp_b200.engine.scheduler import FinishReason
+    folder, cd, page = model_folders["A"]
+    prompt = prompts_for(cd["vocab_size"], [11], seed=33)[0]
+    sampled = dict(max_tokens=12, temperature=1.0, seed=3)            # the same seed gives the same tokens every time
+    free_run = engine(folder, "float32", page).generate([prompt], GenerateParams(**sampled))[0]
+    at = next(i for i in range(2, 12) if free_run[i] not in free_run[:i])   # a token that has not appeared before it
+    stop = free_run[at]
+    never = next(t for t in range(cd["vocab_size"]) if t not in free_run)
+    copy = tmp_path / "with_eos"
+    shutil.copytree(folder, copy)
+    config = json.load(open(copy / "config.json"))
+    config["eos_token_id"] = [never, stop]
+    json.dump(config, open(copy / "config.json", "w"))
+    eng = engine(str(copy), "float32", page)
+    assert eng.eos_token_ids == (never, stop)
+    r = eng.submit(prompt, GenerateParams(**sampled))
+    while not r.done:
+        eng.step()
+    assert list(r.output) == free_run[:at + 1] and r.finish_reason == FinishReason.EOS
+    assert eng.generate([prompt], GenerateParams(ignore_eos=True, **sampled))[0] == free_run

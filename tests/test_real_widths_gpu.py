@@ -121,6 +121,36 @@ def test_bfloat16_at_real_widths(wide):
     assert eng.info()["fallback_calls"] == 0, "a matrix product fell back to the plain kernel"
 
 
+@ONLY_8B
+def test_keys_do_not_depend_on_which_product_kernel_wrote_them(wide):
+    """512 tokens whole (q,k,v with norm, rotation and page write in the epilogue of the CTA-pair product), as two
+    portions of 256 (the same kernel, the second portion over cached keys) and as four of 128 (a product that writes
+    bfloat16, then the separate norm-and-rotation kernel).  All three round the product to bfloat16 before the norm,
+    so the logits of the last rows differ by accumulation order only."""
+    folder, ids, ref = wide
+    from imp_b200 import StepEntry
+    eng = engine(folder, "bfloat16")
+    g = torch.Generator().manual_seed(21)
+    d = torch.randint(0, SHAPES["8b"]["vocab_size"], (512,), generator=g).tolist()
+    want = PlainModel(folder).logits(d)[-8:]
+    scale = float(want.abs().max())
+    got = {}
+    for name, cut in (("whole", [512]), ("halves", [256, 256]), ("quarters", [128] * 4)):
+        at = 0
+        for n in cut:
+            last = at + n == 512
+            lg = eng.step_tokens([StepEntry(name, d[at:at + n], list(range(n - 8, n)) if last else [])])
+            at += n
+        got[name] = torch.from_numpy(lg)
+        eng.end(name)
+        err = (got[name] - want).abs()
+        assert (err <= 0.03 * scale + 0.03 * want.abs()).all(), f"{name}: max error {float(err.max()):.3g} of {scale:.3g}"
+    for name in ("halves", "quarters"):
+        diff = float((got[name] - got["whole"]).abs().max())
+        assert diff <= 0.01 * scale, f"{name} against whole: {diff:.3g} of {scale:.3g}"
+    assert eng.info()["fallback_calls"] == 0
+
+
 @ALL_SHAPES
 def test_float32_at_real_widths_is_exact_under_cutting(wide):
     folder, ids, ref = wide

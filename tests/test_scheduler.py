@@ -102,6 +102,20 @@ def test_eos_and_ignore_eos_and_context_limit():
     assert fin[0].rid == "b" and fin[0].finish_reason == FinishReason.CONTEXT and fin[0].n_total == 8
 
 
+def test_any_of_several_end_tokens_finishes_a_request():
+    cache, s = make(max_seq=64)
+    s.add(req("first", 3, 50, eos_token_ids=(7, 11)))
+    s.add(req("second", 3, 50, eos_token_ids=(7, 11)))
+    s.add(req("other", 3, 50, eos_token_ids=(5,)))
+    _, fin = run_step(cache, s, token=11)               # the second id of the list ends both; 11 is no end token of "other"
+    assert sorted(r.rid for r in fin) == ["first", "second"]
+    assert all(r.finish_reason == FinishReason.EOS for r in fin)
+    _, fin = run_step(cache, s, token=7)
+    assert fin == []
+    _, fin = run_step(cache, s, token=5)
+    assert [r.rid for r in fin] == ["other"] and fin[0].finish_reason == FinishReason.EOS
+
+
 def test_request_that_can_never_fit_is_refused_when_added():
     cache, s = make(num_pages=4, page=4)          # 16 tokens in all
     r = s.add(req("big", 10, 10))
