@@ -1,15 +1,19 @@
 // Paged prefill attention on the fifth-generation tensor cores (tcgen05 + tensor memory), bfloat16,
 // compiled once per head size: -DIMP_ATTN_DH=64 or 128.
 //
-// A CTA owns one tile of up to 128 consecutive query tokens of one sequence and NQ (1 or 2) query
-// heads that share a kv head, and walks the cached keys of the sequence in tiles of 128 from the
+// A work item is one tile of up to 128 consecutive query tokens of one sequence and NQ (1 or 2) query
+// heads that share a kv head; it walks the cached keys of the sequence in tiles of 128 from the
 // window's start to the last token's position (keys come from the pages only; the new tokens'
-// keys are already there).  Roles:
-//   warp 0           producer.  Q tiles once, then per key tile the K pages and the V pages of the
+// keys are already there).  One CTA per SM (a CTA holds all of an SM's tensor memory) works through
+// several items: the list has the heavy tiles first and the CTAs walk it forth and back, so that the
+// sums per CTA come out nearly equal, and barriers, tensor memory and the pipeline are set up once.
+// While the softmax warps store one item's result, the Q tiles of the next are already loaded and its
+// first S is on the tensor cores.  Roles:
+//   warp 0           producer.  Per item the Q tiles, then per key tile the K pages and the V pages of the
 //                    kv head with TMA (cp.async.bulk.tensor, 128-byte swizzle), one box per page
 //                    and 64 head dimensions, into shared-memory rings; page ids come from the block
 //                    table, pages that do not exist are fetched from beyond the tensor (zeros).
-//   warp 1, lane 0   MMA issuer.  S_w = Q_w K^T (M=128 tokens, N=128 keys, K=head size) into tensor
+//   warp 1           MMA issuer.  S_w = Q_w K^T (M=128 tokens, N=128 keys, K=head size) into tensor
 //                    memory, and O_w += P_w V (M=128, N=head size, K=128 keys; P from tensor memory), V being read as an
 //                    MN-major operand straight from its [key, dim] layout.  After P_w V of tile i
 //                    it issues Q_w K^T of tile i+1, so while one head's softmax runs the tensor
@@ -53,7 +57,7 @@ template <int NQ> struct FaCfg {
     static constexpr int THREADS = 128 + 128 * NQ;        // warps 0-3: producer, MMA issuer, two idle; then 4 per head
     static constexpr int TMEM_COLS = 256 * NQ;
     static constexpr int TILE_BYTES = NQ * FA_Q_BYTES + (K_STAGES + V_STAGES) * FA_KV_BYTES;
-    static constexpr int N_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 3 * NQ;
+    static constexpr int N_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 3 * NQ;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
 };
 
@@ -81,6 +85,55 @@ __device__ __forceinline__ void fa_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         : "memory");
 }
 
+// The MMAs of one S tile (S = Q K^T over the whole head size) and of one O update (O += P V over 128 keys) as one
+// block of instructions each: descriptors advance by constants inside the block, one lane of the (converged) warp is
+// elected once and issues all of them.  Written out because the issuing thread is on the critical path of every tile:
+// with the descriptors built per MMA in C++ a tile's sixteen MMAs took about 1,500 cycles to issue, more than the 1,024
+// the tensor cores need to run them.
+// Q and K tiles: 64-wide blocks of the head dimension 16 KiB apart (descriptor units of 16 bytes: 1024), K steps of
+// 16 elements = 32 bytes (2 units).
+#define FA_QK_STEP(a_off, b_off, pred)                                         \
+    "add.u64 a, %1, " #a_off ";\n"                                             \
+    "add.u64 b, %2, " #b_off ";\n"                                             \
+    "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, " #pred ";\n"
+__device__ __forceinline__ void fa_issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred e, yes, no;\n"
+        ".reg .b64 a, b;\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "setp.eq.u32 yes, 0, 0;\n"
+        "setp.ne.u32 no, 0, 0;\n"
+        FA_QK_STEP(0, 0, no) FA_QK_STEP(2, 2, yes) FA_QK_STEP(4, 4, yes) FA_QK_STEP(6, 6, yes)
+#if IMP_ATTN_DH == 128
+        FA_QK_STEP(1024, 1024, yes) FA_QK_STEP(1026, 1026, yes) FA_QK_STEP(1028, 1028, yes) FA_QK_STEP(1030, 1030, yes)
+#endif
+        "}\n" ::"r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
+        : "memory");
+}
+#undef FA_QK_STEP
+// P (tensor memory, 8 columns of bfloat16 pairs per 16 keys) times V (16 keys = 2 swizzle groups of 1024 bytes: 128
+// descriptor units per step); the first MMA overwrites O unless `accumulate`.
+#define FA_PV_STEP(t, pred)                                                    \
+    "add.u32 pa, %1, " #t " * 8;\n"                                            \
+    "add.u64 b, %2, " #t " * 128;\n"                                           \
+    "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], b, %3, " #pred ";\n"
+__device__ __forceinline__ void fa_issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred e, yes, first;\n"
+        ".reg .b64 b;\n"
+        ".reg .b32 pa;\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "setp.eq.u32 yes, 0, 0;\n"
+        "setp.ne.u32 first, %4, 0;\n"
+        FA_PV_STEP(0, first) FA_PV_STEP(1, yes) FA_PV_STEP(2, yes) FA_PV_STEP(3, yes)
+        FA_PV_STEP(4, yes) FA_PV_STEP(5, yes) FA_PV_STEP(6, yes) FA_PV_STEP(7, yes)
+        "}\n" ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+#undef FA_PV_STEP
+
 __device__ __forceinline__ float fa_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -92,6 +145,24 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// -DFA_TRACE: CTA 0 records SM clock values at the hand-overs of its pipeline (for reading a timeline; never in a
+// product build).  Slot layout: role * 1024 + event index; roles 0: MMA issuer, 1: softmax head 0, 2: softmax head 1.
+#ifdef FA_TRACE
+__device__ long long fa_trace_buf[3 * 1024];
+#define FA_TR(role, idx) do { if (blockIdx.x == 0 && (idx) < 1024) fa_trace_buf[(role) * 1024 + (idx)] = clock64(); } while (0)
+IMP_API int imp_attn_tc_trace(long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, fa_trace_buf, sizeof(long long) * (size_t)(n < 3072 ? n : 3072));
+}
+#else
+#define FA_TR(role, idx) do {} while (0)
+#endif
+
+// Geometry of one work item: one tile of query tokens and NQ query heads of one kv head.
+struct FaItem {
+    int hk, head0, tok0, rows, seq, pos0, pos_last, first_key, kt_lo, n_kt;
+    bool geometry_ok;
+};
+
 template <int NQ>
 __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -101,8 +172,6 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2, int window, int* status) {
     using Cfg = FaCfg<NQ>;
     constexpr int KS = Cfg::K_STAGES, VS = Cfg::V_STAGES;
-    pdl_wait();
-    pdl_launch_dependents();
     extern __shared__ unsigned char fa_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = tiles;                                   // [NQ][FA_Q_BYTES]
@@ -110,35 +179,19 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     unsigned char* v_s = k_s + KS * FA_KV_BYTES;                  // [VS][FA_KV_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::TILE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BARS);
-    const uint32_t q_full = smem_u32(bars);
-    const uint32_t k_full0 = q_full + 8, k_empty0 = k_full0 + 8 * KS;
+    const uint32_t q_full = smem_u32(bars), q_empty = q_full + 8;
+    const uint32_t k_full0 = q_empty + 8, k_empty0 = k_full0 + 8 * KS;
     const uint32_t v_full0 = k_empty0 + 8 * KS, v_empty0 = v_full0 + 8 * VS;
     const uint32_t s_full0 = v_empty0 + 8 * VS, p_ready0 = s_full0 + 8 * NQ, o_done0 = p_ready0 + 8 * NQ;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = Hq / Hkv, units_per_kv = G / NQ, units = Hkv * units_per_kv;
-    // heavy tiles first: within a sequence later tiles see more keys
-    const int tile = n_tiles - 1 - (int)(blockIdx.x / units);
-    const int unit = blockIdx.x % units;
-    const int hk = unit / units_per_kv;
-    const int head0 = hk * G + (unit % units_per_kv) * NQ;
-    const int tok0 = tile_tok0[tile];
-    const int rows = tile_rows[tile];
-    const int seq = seq_of_token[tok0];
-    const int pos0 = positions[tok0];
-    const int pos_last = pos0 + rows - 1;
-    const bool geometry_ok = seq >= 0 && seq < n_seqs && pos0 >= 0 && rows >= 1 && rows <= FA_BM &&
-                             pos_last / P < bt_stride;
-    if (!geometry_ok && threadIdx.x == 0)
-        imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
-    // key tiles [kt_lo, kt_hi]: from the window's start of the first row to the last row's own key
-    const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int kt_lo = first_key / FA_BN;
-    const int kt_hi = geometry_ok ? pos_last / FA_BN : kt_lo - 1;
-    const int n_kt = kt_hi - kt_lo + 1;
+    const int n_items = n_tiles * units;
 
+    // Nothing up to pdl_wait() touches what an earlier kernel of the stream may still write.
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int s = 0; s < KS; ++s) { mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); }
         for (int s = 0; s < VS; ++s) { mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1); }
         for (int w = 0; w < NQ; ++w) {
@@ -158,39 +211,65 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // The CTA's item in pass p.  The list has the heavy tiles first (within a sequence later tiles see more keys), and
+    // the passes walk it forth and back: the CTA that got the heaviest item of one pass gets the lightest of the next.
+    // Every role walks the same items in the same order; an item without keys (or with a broken geometry) is skipped by
+    // all of them.
+    auto load_item = [&](int pass, FaItem& it) -> bool {
+        const int grid = (int)gridDim.x;
+        const int k = pass * grid + ((pass & 1) ? grid - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (k >= n_items) return false;
+        const int tile = n_tiles - 1 - k / units, unit = k % units;
+        it.hk = unit / units_per_kv;
+        it.head0 = it.hk * G + (unit % units_per_kv) * NQ;
+        it.tok0 = tile_tok0[tile];
+        it.rows = tile_rows[tile];
+        it.seq = seq_of_token[it.tok0];
+        it.pos0 = positions[it.tok0];
+        it.pos_last = it.pos0 + it.rows - 1;
+        it.geometry_ok = it.seq >= 0 && it.seq < n_seqs && it.pos0 >= 0 && it.rows >= 1 && it.rows <= FA_BM &&
+                         it.pos_last / P < bt_stride;
+        // key tiles [kt_lo, kt_hi]: from the window's start of the first row to the last row's own key
+        it.first_key = (window > 0 && it.pos0 - window + 1 > 0) ? it.pos0 - window + 1 : 0;
+        it.kt_lo = it.first_key / FA_BN;
+        const int kt_hi = it.geometry_ok ? it.pos_last / FA_BN : it.kt_lo - 1;
+        it.n_kt = kt_hi - it.kt_lo + 1;
+        return true;
+    };
 
     // With two heads the 384 threads start with 168 registers each; the softmax threads hold a whole row of S
     // (128 values) and take registers over from the first warpgroup, which needs few.
     if (warp < 4) {
     if (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == 0) {
-        if (n_kt > 0) {
-            // ------------------------------------------------------------------ producer (whole warp)
-            // Lane 0 waits for a free stage and announces the bytes; then every lane fetches boxes: box b of a tile is
-            // page b / FA_KB, head-dimension block b % FA_KB.  Page ids are read before the wait, so the table lookup
-            // overlaps it.
-            if (lane == 0) {
-                mbar_expect_tx(q_full, NQ * FA_Q_BYTES);
-                for (int w = 0; w < NQ; ++w)
-                    for (int kb = 0; kb < FA_KB; ++kb)
-                        tma_load_2d(smem_u32(q_s + w * FA_Q_BYTES + kb * FA_BLOCK_BYTES), &map_q, (head0 + w) * DH + kb * 64,
-                                    tok0, q_full);
-            }
-            const int* bt = block_table + (int64_t)seq * bt_stride;
-            const int pages_per_tile = FA_BN / P;
-            const int boxes = pages_per_tile * FA_KB;         // at most 32: page sizes start at 8
-            const int oob_row = num_pages * Hkv * P;          // a box that starts here is all zeros
-            const int my_pg = lane / FA_KB, my_kb = lane % FA_KB;
-            bool ok = true;
-            int k_issued = 0, v_issued = 0;
-            for (int i = 0; i < n_kt && ok; ++i) {
+        // ------------------------------------------------------------------ producer (whole warp)
+        // Lane 0 waits for a free stage and announces the bytes; then every lane fetches boxes: box b of a tile is
+        // page b / FA_KB, head-dimension block b % FA_KB.  Page ids are read before the wait, so the table lookup
+        // overlaps it.  K and V tiles are numbered through all items of the CTA (kv_n); an item's Q tiles follow its
+        // first K tile, once the MMAs of the item before have read theirs (q_empty).
+        const int pages_per_tile = FA_BN / P;
+        const int boxes = pages_per_tile * FA_KB;         // at most 32: page sizes start at 8
+        const int oob_row = num_pages * Hkv * P;          // a box that starts here is all zeros
+        const int my_pg = lane / FA_KB, my_kb = lane % FA_KB;
+        bool ok = true;
+        int k_n = 0, v_n = 0, q_n = 0;                    // K tiles, V tiles and Q loads issued so far
+        FaItem it;
+        for (int pass = 0; ok && load_item(pass, it); ++pass) {
+            if (!it.geometry_ok && lane == 0)
+                imp_report(status, it.seq < 0 || it.seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+            if (it.n_kt <= 0) continue;
+            const int* bt = block_table + (int64_t)it.seq * bt_stride;
+            for (int i = 0; i < it.n_kt && ok; ++i) {
                 int y = oob_row;
                 if (lane < boxes) {
-                    const int idx = (kt_lo + i) * pages_per_tile + my_pg;
+                    const int idx = (it.kt_lo + i) * pages_per_tile + my_pg;
                     const int page = idx < bt_stride ? bt[idx] : -1;
                     if (page >= 0 && page < num_pages) {
-                        y = (page * Hkv + hk) * P;
-                    } else if (idx * P <= pos_last && idx * P + P - 1 >= first_key) {
+                        y = (page * Hkv + it.hk) * P;
+                    } else if (idx * P <= it.pos_last && idx * P + P - 1 >= it.first_key) {
                         // some row of this tile reads the page: it starts at or before the last position and ends inside
                         // the first row's window
                         imp_report(status, IMP_BAD_PAGE);
@@ -198,11 +277,12 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 }
                 for (int kv = 0; kv < 2 && ok; ++kv) {
                     const int stages = kv == 0 ? KS : VS;
-                    const int s = i % stages;
+                    const int n = kv == 0 ? k_n : v_n;
+                    const int s = n % stages;
                     const uint32_t full = (kv == 0 ? k_full0 : v_full0) + 8 * s;
                     const uint32_t empty = (kv == 0 ? k_empty0 : v_empty0) + 8 * s;
                     if (lane == 0) {
-                        ok = mbar_wait(empty, ((uint32_t)(i / stages) & 1u) ^ 1u, status);
+                        ok = mbar_wait(empty, ((uint32_t)(n / stages) & 1u) ^ 1u, status);
                         if (ok) mbar_expect_tx(full, FA_KV_BYTES);
                     }
                     ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -211,64 +291,115 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     if (lane < boxes)
                         tma_load_2d(smem_u32(dst + my_kb * FA_BLOCK_BYTES + my_pg * P * 128), kv == 0 ? &map_k : &map_v,
                                     my_kb * 64, y, full);
-                    if (kv == 0) k_issued = i + 1; else v_issued = i + 1;
-                }
-            }
-            if (!ok && lane == 0) {   // let the copies in flight land before the CTA's shared memory is released
-                mbar_wait(q_full, 0, nullptr);
-                for (int i = k_issued > KS ? k_issued - KS : 0; i < k_issued; ++i)
-                    mbar_wait(k_full0 + 8 * (i % KS), (uint32_t)(i / KS) & 1u, nullptr);
-                for (int i = v_issued > VS ? v_issued - VS : 0; i < v_issued; ++i)
-                    mbar_wait(v_full0 + 8 * (i % VS), (uint32_t)(i / VS) & 1u, nullptr);
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && n_kt > 0) {
-            // ---------------------------------------------------------------- MMA issuer
-            const uint32_t idesc_s = tc_instr_desc(FA_BM, FA_BN);
-            const uint32_t idesc_o = tc_instr_desc(FA_BM, DH) | (1u << 16);   // B (= V) is MN-major
-            bool ok = mbar_wait(q_full, 0, status);
-            auto issue_qk = [&](int w, int i) {
-                const uint32_t q_addr = smem_u32(q_s + w * FA_Q_BYTES), k_addr = smem_u32(k_s + (i % KS) * FA_KV_BYTES);
-#pragma unroll
-                for (int kb = 0; kb < FA_KB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc_mma(tmem_base + (uint32_t)(w * 256), tc_smem_desc(q_addr + kb * FA_BLOCK_BYTES + kk * 32),
-                               tc_smem_desc(k_addr + kb * FA_BLOCK_BYTES + kk * 32), idesc_s, (kb > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(s_full0 + 8 * w);
-            };
-            if (ok) ok = mbar_wait(k_full0, 0, status);
-            if (ok) {
-                tc_fence_after_sync();
-                for (int w = 0; w < NQ; ++w) issue_qk(w, 0);
-                tc_commit(k_empty0);
-            }
-            for (int i = 0; i < n_kt && ok; ++i) {
-                for (int w = 0; w < NQ && ok; ++w) {
-                    ok = mbar_wait(p_ready0 + 8 * w, (uint32_t)i & 1u, status);
-                    if (ok && w == 0) ok = mbar_wait(v_full0 + 8 * (i % VS), (uint32_t)(i / VS) & 1u, status);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    const uint32_t v_addr = smem_u32(v_s + (i % VS) * FA_KV_BYTES);
-                    // P is the A operand straight from tensor memory: 16 keys = 8 columns of bfloat16 pairs per step
-#pragma unroll
-                    for (int t = 0; t < FA_BN / 16; ++t)
-                        fa_mma_ts(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256 + t * 8),
-                                  fa_v_desc(v_addr + t * 2048), idesc_o, (i > 0 || t > 0) ? 1u : 0u);
-                    tc_commit(o_done0 + 8 * w);
-                    if (w == NQ - 1) tc_commit(v_empty0 + 8 * (i % VS));
-                    if (i + 1 < n_kt) {
-                        if (w == 0) {
-                            ok = mbar_wait(k_full0 + 8 * ((i + 1) % KS), (uint32_t)((i + 1) / KS) & 1u, status);
-                            if (!ok) break;
-                            tc_fence_after_sync();
+                    if (kv == 0) ++k_n; else ++v_n;
+                    if (kv == 0 && i == 0) {
+                        if (lane == 0) {
+                            if (q_n > 0) ok = mbar_wait(q_empty, (uint32_t)(q_n - 1) & 1u, status);
+                            if (ok) {
+                                mbar_expect_tx(q_full, NQ * FA_Q_BYTES);
+                                for (int w = 0; w < NQ; ++w)
+                                    for (int kb = 0; kb < FA_KB; ++kb)
+                                        tma_load_2d(smem_u32(q_s + w * FA_Q_BYTES + kb * FA_BLOCK_BYTES), &map_q,
+                                                    (it.head0 + w) * DH + kb * 64, it.tok0, q_full);
+                            }
                         }
-                        issue_qk(w, i + 1);
-                        if (w == NQ - 1) tc_commit(k_empty0 + 8 * ((i + 1) % KS));
+                        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                        if (ok) ++q_n;
                     }
                 }
             }
+        }
+        if (!ok && lane == 0) {   // let the copies in flight land before the CTA's shared memory is released
+            if (q_n > 0) mbar_wait(q_full, (uint32_t)(q_n - 1) & 1u, nullptr);
+            for (int n = k_n > KS ? k_n - KS : 0; n < k_n; ++n)
+                mbar_wait(k_full0 + 8 * (n % KS), (uint32_t)(n / KS) & 1u, nullptr);
+            for (int n = v_n > VS ? v_n - VS : 0; n < v_n; ++n)
+                mbar_wait(v_full0 + 8 * (n % VS), (uint32_t)(n / VS) & 1u, nullptr);
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (whole warp)
+        // All lanes run this code with the same values, so that addresses and descriptors stay in uniform registers;
+        // each MMA and each commit is then issued by one elected lane.  (A single lane running the loop alone spent
+        // about 100 cycles per MMA, more than the 64 the tensor cores need for it.)
+        // Per key tile and head: O_w += P_w V once the softmax has written P_w, then S_w = Q_w K^T of the next tile,
+        // so while one head's softmax runs the tensor cores work on the other head.  After the last tile of an item
+        // both heads' S of the next item's first tile follow at once: the softmax warps find them ready when they
+        // come back from storing the item's result.
+#ifdef FA_EXP_N64   // timing experiment only (wrong results): S tiles of 64 keys, to see whether issue or execution sets the pace
+        const uint32_t idesc_s = tc_instr_desc(FA_BM, 64);
+#else
+        const uint32_t idesc_s = tc_instr_desc(FA_BM, FA_BN);
+#endif
+        const uint32_t idesc_o = tc_instr_desc(FA_BM, DH) | (1u << 16);   // B (= V) is MN-major
+        bool ok = true;
+        int kv_n = 0;                 // number of the current K / V tile among all of the CTA's
+        int t_n = 0;                  // tiles finished: the phase of s_full, p_ready, o_done
+        int item_n = 0;               // items started: the phase of q_full
+        int pass = 0;
+        auto wait_all = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, status)) != 0; };
+        auto next_n_kt = [&]() -> int {   // key tiles of the CTA's next item with work; 0: none left
+            FaItem it;
+            while (load_item(pass++, it))
+                if (it.n_kt > 0) return it.n_kt;
+            return 0;
+        };
+        static_assert(FA_BN == 128, "fa_issue_pv is written for tiles of 128 keys");
+        const uint64_t q_desc0 = tc_smem_desc(smem_u32(q_s)), k_desc0 = tc_smem_desc(smem_u32(k_s)), v_desc0 = fa_v_desc(smem_u32(v_s));
+        auto issue_qk = [&](int w, int n) {      // S_w = Q_w K^T with K tile number n
+            fa_issue_qk(tmem_base + (uint32_t)(w * 256), q_desc0 + (uint64_t)(w * (FA_Q_BYTES >> 4)),
+                        k_desc0 + (uint64_t)((n % KS) * (FA_KV_BYTES >> 4)), idesc_s);
+            if (tc_elect_one()) tc_commit(s_full0 + 8 * w);
+        };
+        // S of an item's first tile, both heads: its Q tiles and K tile number n
+        auto first_qk = [&](int n, int n_kt) {
+            ok = wait_all(q_full, (uint32_t)item_n & 1u);
+            if (ok) ok = wait_all(k_full0 + 8 * (n % KS), (uint32_t)(n / KS) & 1u);
+            if (!ok) return;
+            tc_fence_after_sync();
+            for (int w = 0; w < NQ; ++w) issue_qk(w, n);
+            if (tc_elect_one()) {
+                tc_commit(k_empty0 + 8 * (n % KS));
+                if (n_kt == 1) tc_commit(q_empty);      // the item's only use of Q
+            }
+            ++item_n;
+        };
+        int n_kt = next_n_kt();
+        if (n_kt > 0) first_qk(0, n_kt);
+        while (n_kt > 0 && ok) {
+            const int n_kt_next = next_n_kt();
+            for (int i = 0; i < n_kt && ok; ++i, ++kv_n, ++t_n) {
+                const bool last = i + 1 == n_kt;
+                for (int w = 0; w < NQ && ok; ++w) {
+                    if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 0);
+                    ok = wait_all(p_ready0 + 8 * w, (uint32_t)t_n & 1u);
+                    if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 1);
+                    if (ok && w == 0) ok = wait_all(v_full0 + 8 * (kv_n % VS), (uint32_t)(kv_n / VS) & 1u);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    fa_issue_pv(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256),
+                                v_desc0 + (uint64_t)((kv_n % VS) * (FA_KV_BYTES >> 4)), idesc_o, i > 0 ? 1u : 0u);
+                    if (tc_elect_one()) {
+                        tc_commit(o_done0 + 8 * w);
+                        if (w == NQ - 1) tc_commit(v_empty0 + 8 * (kv_n % VS));
+                    }
+                    if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 2);
+                    if (!last) {
+                        if (w == 0) {
+                            ok = wait_all(k_full0 + 8 * ((kv_n + 1) % KS), (uint32_t)((kv_n + 1) / KS) & 1u);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                        }
+                        issue_qk(w, kv_n + 1);
+                        if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 3);
+                        if (w == NQ - 1 && tc_elect_one()) {
+                            tc_commit(k_empty0 + 8 * ((kv_n + 1) % KS));
+                            if (i + 2 == n_kt) tc_commit(q_empty);   // that was the item's last use of Q
+                        }
+                    }
+                }
+                if (last && ok && n_kt_next > 0) first_qk(kv_n + 1, n_kt_next);
+            }
+            n_kt = n_kt_next;
         }
     }
     } else {
@@ -278,14 +409,21 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         const int row = (warp & 3) * 32 + lane;              // tensor-memory lane = query row of the tile
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_tmem = lane_base + (uint32_t)(w * 256), o_tmem = s_tmem + 128u;
+        bool ok = true;
+        int t_n = 0;                                         // tiles finished: the phase of s_full and o_done
+        FaItem it;
+        for (int pass = 0; ok && load_item(pass, it); ++pass) {
+        if (it.n_kt <= 0) continue;
+        const int n_kt = it.n_kt, pos0 = it.pos0, rows = it.rows;
         const int p = pos0 + (row < rows ? row : rows - 1);  // padding rows repeat the last real row
         float m_used = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int i = 0; i < n_kt && ok; ++i) {
-            const int k0 = (kt_lo + i) * FA_BN;
-            ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * w, (uint32_t)i & 1u, status));
+        for (int i = 0; i < n_kt && ok; ++i, ++t_n) {
+            const int k0 = (it.kt_lo + i) * FA_BN;
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 0);
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * w, (uint32_t)t_n & 1u, status));
             if (!ok) break;
             tc_fence_after_sync();
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 1);
             // a tile needs the mask when a key of it lies behind the first row's position or before the last row's window
             const bool masked = (k0 + FA_BN - 1 > pos0) || (window > 0 && pos0 + FA_BM - 1 - k0 >= window);
             const int hi = p - k0;                                        // columns <= hi are not in the future
@@ -297,6 +435,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             tc_wait_ld_pin<true>(sr[0]);
 #pragma unroll
             for (int c = 1; c < FA_BN / 32; ++c) tc_wait_ld_pin<false>(sr[c]);
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 2);
             // four independent maxima: one chain of 128 dependent comparisons would sit on the critical path
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (masked) {
@@ -335,6 +474,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 }
                 m_used = m_new;
             }
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 3);
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;    // a row with nothing visible yet
             float ls[4] = {0.f, 0.f, 0.f, 0.f};                             // four partial sums, added in a fixed order
             // P = exp2(s - m) as bfloat16 pairs, written over the first 64 columns of S (this thread's own row):
@@ -356,16 +496,20 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 tc_st32(s_tmem + (uint32_t)(hlf * 32), pk);
             }
             l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 4);
             tc_wait_st();
             tc_fence_before_sync();                                       // this row's reads and writes of tensor memory
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready0 + 8 * w);
+            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 5);
         }
-        if (ok && n_kt > 0) ok = __all_sync(0xffffffffu, mbar_wait(o_done0 + 8 * w, (uint32_t)(n_kt - 1) & 1u, status));
-        if (ok && n_kt > 0) {
+        // The item's result.  The loads of O are complete (tc_ld32 waits) before this warp signals its next P, and the
+        // first P V of the next item, which overwrites O, waits for that signal of all four warps.
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done0 + 8 * w, (uint32_t)(t_n - 1) & 1u, status));
+        if (ok) {
             tc_fence_after_sync();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* o_row = out + (int64_t)(tok0 + row) * out_stride + (int64_t)(head0 + w) * DH;
+            __nv_bfloat16* o_row = out + (int64_t)(it.tok0 + row) * out_stride + (int64_t)(it.head0 + w) * DH;
 #pragma unroll 1
             for (int c = 0; c < DH / 32; ++c) {
                 float o[32];
@@ -382,6 +526,8 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     }
                 }
             }
+            tc_fence_before_sync();
+        }
         }
     }
     tc_fence_before_sync();
@@ -439,8 +585,15 @@ static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) { imp_set_error("imp_attn_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
-    const int64_t grid = (int64_t)n_tiles * Hkv * ((Hq / Hkv) / NQ);
-    IMP_CHECK_ARG(grid <= 0x7fffffff, "imp_attn_prefill_tc: too many tiles");
+    const int64_t items = (int64_t)n_tiles * Hkv * ((Hq / Hkv) / NQ);
+    IMP_CHECK_ARG(items <= 0x7fffffff, "imp_attn_prefill_tc: too many tiles");
+    static int sms = 0;                 // one CTA fits an SM (all of its tensor memory); the CTAs share out the items
+    if (sms <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 1;
+    }
+    const int64_t grid = items < sms ? items : sms;
     cudaError_t e = imp_launch(attn_prefill_tc_kernel<NQ>, dim3((unsigned)grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, s, mq, mk,
                                mv, out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows,
                                n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status);
