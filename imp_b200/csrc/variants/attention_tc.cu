@@ -140,6 +140,40 @@ __device__ __forceinline__ float fa_exp2(float x) {
     return y;
 }
 
+// The softmax warps are bound by the number of instructions they issue (a share of the exponentials computed on the
+// FMA pipe instead of the special-function unit made them slower), so the arithmetic around the exponentials uses
+// the two-wide 32-bit instructions and the three-input maximum of this architecture.
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (x0, x1) = (a0, a1) * s + t
+__device__ __forceinline__ void fa_fma2(float& x0, float& x1, float a0, float a1, float s, float t) {
+    asm("{\n"
+        ".reg .b64 a, b, c, d;\n"
+        "mov.b64 a, {%2, %3};\n"
+        "mov.b64 b, {%4, %4};\n"
+        "mov.b64 c, {%5, %5};\n"
+        "fma.rn.f32x2 d, a, b, c;\n"
+        "mov.b64 {%0, %1}, d;\n"
+        "}\n"
+        : "=f"(x0), "=f"(x1)
+        : "f"(a0), "f"(a1), "f"(s), "f"(t));
+}
+// (s0, s1) += (a0, a1)
+__device__ __forceinline__ void fa_add2(float& s0, float& s1, float a0, float a1) {
+    asm("{\n"
+        ".reg .b64 a, b, d;\n"
+        "mov.b64 a, {%0, %1};\n"
+        "mov.b64 b, {%2, %3};\n"
+        "add.rn.f32x2 d, a, b;\n"
+        "mov.b64 {%0, %1}, d;\n"
+        "}\n"
+        : "+f"(s0), "+f"(s1)
+        : "f"(a0), "f"(a1));
+}
+
 __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -451,7 +485,8 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
 #pragma unroll
                 for (int c = 0; c < FA_BN / 32; ++c)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) tm[j & 3] = fmaxf(tm[j & 3], __uint_as_float(sr[c][j]));
+                    for (int j = 0; j < 32; j += 2)
+                        tm[(j >> 1) & 3] = fa_max3(tm[(j >> 1) & 3], __uint_as_float(sr[c][j]), __uint_as_float(sr[c][j + 1]));
             }
             float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
             tmax *= scale_log2;                                           // scale > 0: the order is kept
@@ -476,7 +511,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             }
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 3);
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;    // a row with nothing visible yet
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};                             // four partial sums, added in a fixed order
+            float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};         // eight partial sums, added in a fixed order
             // P = exp2(s - m) as bfloat16 pairs, written over the first 64 columns of S (this thread's own row):
             // keys 2j, 2j+1 share column j, the lower key in the lower half
 #pragma unroll
@@ -487,15 +522,16 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     const int c = 2 * hlf + cc;
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[c][j]), scale_log2, -m_sub));   // exp2(-inf) = 0: masked
-                        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[c][j + 1]), scale_log2, -m_sub));
-                        ls[(j >> 1) & 3] += e0 + e1;
+                        float x0, x1;
+                        fa_fma2(x0, x1, __uint_as_float(sr[c][j]), __uint_as_float(sr[c][j + 1]), scale_log2, -m_sub);
+                        const float e0 = fa_exp2(x0), e1 = fa_exp2(x1);                  // exp2(-inf) = 0: masked
+                        fa_add2(ls[j & 6], ls[(j & 6) + 1], e0, e1);
                         pk[cc * 16 + (j >> 1)] = __uint_as_float(fa_pack(e0, e1));
                     }
                 }
                 tc_st32(s_tmem + (uint32_t)(hlf * 32), pk);
             }
-            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            l += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 4);
             tc_wait_st();
             tc_fence_before_sync();                                       // this row's reads and writes of tensor memory
