@@ -57,7 +57,7 @@ template <int NQ> struct FaCfg {
     static constexpr int THREADS = 128 + 128 * NQ;        // warps 0-3: producer, MMA issuer, two idle; then 4 per head
     static constexpr int TMEM_COLS = 256 * NQ;
     static constexpr int TILE_BYTES = NQ * FA_Q_BYTES + (K_STAGES + V_STAGES) * FA_KV_BYTES;
-    static constexpr int N_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 3 * NQ;
+    static constexpr int N_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 4 * NQ;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
 };
 
@@ -113,7 +113,7 @@ __device__ __forceinline__ void fa_issue_qk(uint32_t d_tmem, uint64_t q_desc, ui
 }
 #undef FA_QK_STEP
 // P (tensor memory, 8 columns of bfloat16 pairs per 16 keys) times V (16 keys = 2 swizzle groups of 1024 bytes: 128
-// descriptor units per step); the first MMA overwrites O unless `accumulate`.
+// descriptor units per step) for one half of a tile (64 keys); the first MMA overwrites O unless `accumulate`.
 #define FA_PV_STEP(t, pred)                                                    \
     "add.u32 pa, %1, " #t " * 8;\n"                                            \
     "add.u64 b, %2, " #t " * 128;\n"                                           \
@@ -128,7 +128,6 @@ __device__ __forceinline__ void fa_issue_pv(uint32_t o_tmem, uint32_t p_tmem, ui
         "setp.eq.u32 yes, 0, 0;\n"
         "setp.ne.u32 first, %4, 0;\n"
         FA_PV_STEP(0, first) FA_PV_STEP(1, yes) FA_PV_STEP(2, yes) FA_PV_STEP(3, yes)
-        FA_PV_STEP(4, yes) FA_PV_STEP(5, yes) FA_PV_STEP(6, yes) FA_PV_STEP(7, yes)
         "}\n" ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -216,7 +215,8 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     const uint32_t q_full = smem_u32(bars), q_empty = q_full + 8;
     const uint32_t k_full0 = q_empty + 8, k_empty0 = k_full0 + 8 * KS;
     const uint32_t v_full0 = k_empty0 + 8 * KS, v_empty0 = v_full0 + 8 * VS;
-    const uint32_t s_full0 = v_empty0 + 8 * VS, p_ready0 = s_full0 + 8 * NQ, o_done0 = p_ready0 + 8 * NQ;
+    // p_ready: per head two barriers, one for each half (64 keys) of P
+    const uint32_t s_full0 = v_empty0 + 8 * VS, p_ready0 = s_full0 + 8 * NQ, o_done0 = p_ready0 + 16 * NQ;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = Hq / Hkv, units_per_kv = G / NQ, units = Hkv * units_per_kv;
@@ -230,7 +230,8 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         for (int s = 0; s < VS; ++s) { mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1); }
         for (int w = 0; w < NQ; ++w) {
             mbar_init(s_full0 + 8 * w, 1);
-            mbar_init(p_ready0 + 8 * w, 4);      // one arrival per softmax warp
+            mbar_init(p_ready0 + 16 * w, 4);     // one arrival per softmax warp
+            mbar_init(p_ready0 + 16 * w + 8, 4);
             mbar_init(o_done0 + 8 * w, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -377,7 +378,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 if (it.n_kt > 0) return it.n_kt;
             return 0;
         };
-        static_assert(FA_BN == 128, "fa_issue_pv is written for tiles of 128 keys");
+        static_assert(FA_BN == 128, "fa_issue_pv is written for halves of tiles of 128 keys");
         const uint64_t q_desc0 = tc_smem_desc(smem_u32(q_s)), k_desc0 = tc_smem_desc(smem_u32(k_s)), v_desc0 = fa_v_desc(smem_u32(v_s));
         auto issue_qk = [&](int w, int n) {      // S_w = Q_w K^T with K tile number n
             fa_issue_qk(tmem_base + (uint32_t)(w * 256), q_desc0 + (uint64_t)(w * (FA_Q_BYTES >> 4)),
@@ -405,13 +406,18 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                 const bool last = i + 1 == n_kt;
                 for (int w = 0; w < NQ && ok; ++w) {
                     if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 0);
-                    ok = wait_all(p_ready0 + 8 * w, (uint32_t)t_n & 1u);
+                    // the first 64 keys of P are there while the softmax still works on the other 64
+                    ok = wait_all(p_ready0 + 16 * w, (uint32_t)t_n & 1u);
                     if (lane == 0) FA_TR(0, (t_n * 2 + w) * 4 + 1);
                     if (ok && w == 0) ok = wait_all(v_full0 + 8 * (kv_n % VS), (uint32_t)(kv_n / VS) & 1u);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    fa_issue_pv(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256),
-                                v_desc0 + (uint64_t)((kv_n % VS) * (FA_KV_BYTES >> 4)), idesc_o, i > 0 ? 1u : 0u);
+                    const uint64_t v_desc = v_desc0 + (uint64_t)((kv_n % VS) * (FA_KV_BYTES >> 4));
+                    fa_issue_pv(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256), v_desc, idesc_o, i > 0 ? 1u : 0u);
+                    ok = wait_all(p_ready0 + 16 * w + 8, (uint32_t)t_n & 1u);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    fa_issue_pv(tmem_base + (uint32_t)(w * 256 + 128), tmem_base + (uint32_t)(w * 256 + 32), v_desc + 4 * 128, idesc_o, 1u);
                     if (tc_elect_one()) {
                         tc_commit(o_done0 + 8 * w);
                         if (w == NQ - 1) tc_commit(v_empty0 + 8 * (kv_n % VS));
@@ -530,13 +536,16 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
                     }
                 }
                 tc_st32(s_tmem + (uint32_t)(hlf * 32), pk);
+                // each half is handed over by itself: the MMAs of the first run while the second is computed
+                if (hlf == 1) {
+                    l += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
+                    if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 4);
+                }
+                tc_wait_st();
+                tc_fence_before_sync();                                   // this row's reads and writes of tensor memory
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready0 + 16 * w + 8 * hlf);
             }
-            l += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
-            if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 4);
-            tc_wait_st();
-            tc_fence_before_sync();                                       // this row's reads and writes of tensor memory
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready0 + 8 * w);
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 5);
         }
         // The item's result.  The loads of O are complete (tc_ld32 waits) before this warp signals its next P, and the
