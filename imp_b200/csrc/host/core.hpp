@@ -187,6 +187,12 @@ struct Runtime {
     int64_t fallback_calls = 0;     // matrix products that ran on the plain fallback kernel
     int64_t launches = 0;           // launcher calls of this library
     int64_t split_norm_calls = 0;   // norms that added the unsummed parts of a product themselves
+    // IMP_B200_TIME_WITHOUT: letters of built-in operations that are NOT launched (q: q,k,v product, a: decode
+    // attention, o: output product, g: gate/up product, d: down product, n: the blocks' norms).  The results are then
+    // meaningless; the step's time against the full step's is what the operation costs inside the step.  A
+    // measurement aid only: the context warns when it is set.
+    std::string time_without;
+    bool without(char op) const { return !time_without.empty() && time_without.find(op) != std::string::npos; }
     bool is_f32() const { return dtype == F32; }
     Tensor empty(int64_t rows, int64_t cols, int dt = -1, bool step = false) {
         const int d = dt < 0 ? dtype : dt;

@@ -30,6 +30,10 @@ DeviceContext::DeviceContext(int device_id, int dtype, size_t step_bytes, size_t
     arena = std::make_unique<Arena>(step_bytes, layer_bytes);
     rt.arena = arena.get();
     rt.sm_count = imp_device_sm_count();
+    rt.time_without = env_string("IMP_B200_TIME_WITHOUT", "");
+    if (!rt.time_without.empty())
+        log_line(LOG_WARN, "IMP_B200_TIME_WITHOUT=%s: these operations are not launched, every result of this context is meaningless",
+                 rt.time_without.c_str());
 }
 
 DeviceContext::~DeviceContext() {

@@ -31,6 +31,7 @@ struct RMSNorm : Norm {
     Tensor add_norm(Step& st, Tensor h, const Branch& branch, const int32_t* rows_idx, int n_rows) override {
         const int64_t n = rows_idx ? n_rows : rows(h);
         Tensor out = st.rt->empty(n, cols(h), -1, /*step=*/rows_idx != nullptr);
+        if (st.rt->without('n') && !rows_idx) return out;
         add_rmsnorm(*st.rt, h, branch, weight, out, eps, offset, rows_idx, n_rows);
         return out;
     }
@@ -172,13 +173,15 @@ struct GQAAttention : Mixer {
             }
         }
         Tensor qkv = rt.empty(T, qd + 2 * kd);
-        linear(rt, qkv, x, w_qkv);
+        if (!rt.without('q')) linear(rt, qkv, x, w_qkv);
         if (fusable && st.decode_only()) {
             // decode steps: the attention kernel normalises and rotates q and the new key itself and writes the new
             // key and value into their pages (no rotary kernel)
             Tensor attn = rt.empty(T, qd);
-            if (decode_attention_fused(st, attn, qkv, g, *cache, qk, rot))
+            if (rt.without('a') || decode_attention_fused(st, attn, qkv, g, *cache, qk, rot)) {
+                if (rt.without('o')) return Branch::of(rt.empty(T, rows(w_o)));
                 return linear(rt, rt.empty(T, rows(w_o)), attn, w_o, defer_out);
+            }
         }
         if (position && !rotary) {
             // An encoding the fused kernel does not know: norm, then let the part rewrite q and k, then a plain write.
@@ -232,12 +235,13 @@ struct SwiGLU : FeedForward {
         const int64_t T = rows(x);
         Tensor act = rt.empty(T, f);
         if (interleaved) {
-            linear_swiglu(rt, act, x, w_gu);
+            if (!rt.without('g')) linear_swiglu(rt, act, x, w_gu);
         } else {
             Tensor gu = rt.empty(T, 2 * f);
             linear(rt, gu, x, w_gu);
             swiglu(rt, act, gu, 0);
         }
+        if (rt.without('d')) return Branch::of(rt.empty(T, rows(w_down)));
         return linear(rt, rt.empty(T, rows(w_down)), act, w_down, defer_out);
     }
 };
