@@ -231,7 +231,7 @@ static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, 
                                     int64_t ldw, int M, int N, int K, cudaStream_t s) {
     int stages = gs_env_stages();
     // Up to 8 tokens: two row groups per CTA where 32-row tiles still give about one CTA per SM or more.
-    // With at least one such tile per SM, four stages of 21 KiB (two CTAs per SM); with two thirds of that
+    // With at least one such tile per SM, four stages of 21 KiB (two CTAs per SM); with 96/148 of that
     // and more (96..147 tiles on 148 SMs), six stages (one CTA per SM, 80 KiB of weight reads in flight each).  IMP_B200_GS_RG=1 keeps 16-row tiles
     // everywhere, =2 uses 32-row tiles only in the first case.
     static int rg_env = -1;
@@ -240,7 +240,7 @@ static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, 
     const int sms = imp_sm_count();
     if (NT == 1 && M >= 3 && rg_env >= 2 && stages == 0 && (N + 31) / 32 >= sms)
         return launch_stream_st<1, TO, SWIGLU, 4, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
-    if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= (sms * 2 + 2) / 3 && (N + 31) / 32 < sms)
+    if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= (sms * 96 + 147) / 148 && (N + 31) / 32 < sms)
         return launch_stream_st<1, TO, SWIGLU, 6, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
     if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * sms) ? 8 : 5;
     switch (stages) {

@@ -657,9 +657,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
 // splits == 1) lanes r and r + 8 of every 16 hold gate and up of one output column.
 constexpr int TCS_W_BYTES = 128 * TC_BK * 2;   // 16 KiB
 
-// For the test of the give-up paths only (imp_gemm_tc_test_hooks): the K block whose stage the producer of
-// gemm_tc_swap_kernel leaves unfilled, so that the waits behind it cannot succeed.  -1 in every other run.
-static __constant__ int tcs_test_skip_kb = -1;
+// For the test of the give-up paths only (imp_gemm_tc_test_hooks), handed to gemm_tc_swap_kernel with its parameters:
+// the poll limit of its waits, and the K block whose stage the producer leaves unfilled, so that the waits behind it
+// cannot succeed.  TC_WAIT_LIMIT and -1 in every other run.
+static uint32_t g_tcs_wait_limit = TC_WAIT_LIMIT;
+static int g_tcs_skip_kb = -1;
 
 // Ring depth.  Up to 32 tokens: five stages of 20 KiB; up to 64: four of 24 KiB; both so that two CTAs share an SM
 // (and its memory pipes).  More tokens: six stages of 32 KiB, one CTA per SM.  (Five stages measured 0.7 % faster
@@ -676,7 +678,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w,
                                                               const __grid_constant__ CUtensorMap map_x, void* __restrict__ Cv,
                                                               int64_t ldc, int64_t split_stride, int M, int N, int K,
-                                                              int kb_per_split, int tile_rows, int* status) {
+                                                              int kb_per_split, int tile_rows, int* status,
+                                                              uint32_t wait_limit, int skip_kb) {
     constexpr int TCS_STAGES = tcs_stages<BN>();
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -730,9 +733,9 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         issued = early;
         for (int i = early; i < k_blocks; ++i) {
             const int s = i % TCS_STAGES;
-            ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status);
+            ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / TCS_STAGES) & 1u) ^ 1u, status, wait_limit);
             if (!ok) break;
-            if (i == tcs_test_skip_kb) { issued = i + 1; continue; }
+            if (i == skip_kb) { issued = i + 1; continue; }
             const uint32_t w_dst = smem_u32(tiles + s * STAGE), x_dst = w_dst + TCS_W_BYTES;
             mbar_expect_tx(full0 + 8 * s, stage_tx);
             tma_load_2d(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * s);
@@ -741,7 +744,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         }
         if (!ok)
             for (int i = issued > TCS_STAGES ? issued - TCS_STAGES : 0; i < issued; ++i)
-                mbar_wait(full0 + 8 * (i % TCS_STAGES), (uint32_t)(i / TCS_STAGES) & 1u, nullptr);
+                mbar_wait(full0 + 8 * (i % TCS_STAGES), (uint32_t)(i / TCS_STAGES) & 1u, nullptr, wait_limit);
     } else {
         pdl_wait();
     }
@@ -750,7 +753,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         bool ok = true;
         for (int i = 0; i < k_blocks && ok; ++i) {
             const int s = i % TCS_STAGES;
-            ok = mbar_wait(full0 + 8 * s, (uint32_t)(i / TCS_STAGES) & 1u, status);
+            ok = mbar_wait(full0 + 8 * s, (uint32_t)(i / TCS_STAGES) & 1u, status, wait_limit);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t w_addr = smem_u32(tiles + s * STAGE), x_addr = w_addr + TCS_W_BYTES;
@@ -764,7 +767,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     }
     __syncwarp();
 
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, status));
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, status, wait_limit));
     tc_fence_after_sync();
     if (acc_ok) {
         const int r = warp * 32 + lane;             // accumulator lane = weight row of the tile
@@ -984,7 +987,7 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
     }
     dim3 grid((N + tile_rows - 1) / tile_rows, 1, splits);
     cudaError_t e = imp_launch(gemm_tc_swap_kernel<BN, EPI>, grid, dim3(128), (size_t)tcs_smem_bytes<BN>(), s, mw, mx, C, ldc,
-                               split_stride, M, N, K, kb_per_split, tile_rows, status);
+                               split_stride, M, N, K, kb_per_split, tile_rows, status, g_tcs_wait_limit, g_tcs_skip_kb);
     if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1049,18 +1052,14 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
 }
 
 // Test hooks of the bounded waits.  `wait_limit` polls (0: the regular limit) bound every mbarrier wait of the
-// kernels in this file from the next launch on, and the producer of the few-rows kernel leaves the stage of K
-// block `skip_kb` unfilled (-1: none; blocks inside the first ring depth are never skipped), so that the MMA
-// thread's wait for it, the producer's later wait for the slot and its wait for its own copies all run out.
-// The kernel then reports IMP_WAIT_TIMEOUT through the status word, frees its tensor memory and returns.
-// A test lowers the limit to a few thousand polls for one CTA and restores both values afterwards.
+// few-rows kernel from its next launch on, and its producer leaves the stage of K block `skip_kb` unfilled (-1:
+// none; blocks inside the first ring depth are never skipped), so that the MMA thread's wait for it, the producer's
+// later wait for the slot and its wait for its own copies all run out.  The kernel then reports IMP_WAIT_TIMEOUT
+// through the status word, frees its tensor memory and returns.  A test lowers the limit to a few thousand polls for
+// one CTA and restores both values afterwards.  (Both travel as kernel parameters.)
 IMP_API int imp_gemm_tc_test_hooks(unsigned wait_limit, int skip_kb) {
-    const uint32_t limit = wait_limit ? wait_limit : TC_WAIT_LIMIT;
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(tc_wait_limit, &limit, sizeof limit);
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(tcs_test_skip_kb, &skip_kb, sizeof skip_kb);
-    if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) { imp_set_error("imp_gemm_tc_test_hooks: %s", cudaGetErrorString(e)); return (int)e; }
+    g_tcs_wait_limit = wait_limit ? wait_limit : TC_WAIT_LIMIT;
+    g_tcs_skip_kb = skip_kb;
     return 0;
 }
 

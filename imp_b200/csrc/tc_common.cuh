@@ -8,9 +8,8 @@
 #include <cuda.h>
 
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;   // polls of mbarrier.try_wait (each suspends for a while): about a second
-// The limit the waits read (one copy per translation unit).  It only ever differs from TC_WAIT_LIMIT while a test
-// of the give-up paths has lowered it, so that a wait which cannot succeed runs out in milliseconds.
-static __constant__ uint32_t tc_wait_limit = TC_WAIT_LIMIT;
+// (Module-level __constant__ or __device__ variables are kept out of the files whose kernels run in the decode step:
+// their mere presence cost every launch of the step's CUDA graph about a third of a microsecond, 2.3 % of the step.)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -20,9 +19,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity; false (and a status report) when it runs out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    const uint32_t limit = tc_wait_limit;
+// Bounded wait for the phase with the given parity; false (and a status report) when it runs out.  `limit` differs
+// from TC_WAIT_LIMIT only where a test of the give-up paths passes a small one through a kernel's parameters.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, uint32_t limit = TC_WAIT_LIMIT) {
     for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
