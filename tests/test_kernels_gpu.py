@@ -591,6 +591,22 @@ def test_attention_tc_prefill_shapes_pages_windows(K, Dh, Hq, Hkv, page, window)
     run_prefill_tc(K, [257, 64], [257, 64], Hq, Hkv, Dh, page, window, seed=13)
 
 
+@pytest.mark.parametrize("Dh,Hq,Hkv,window", [(64, 8, 8, 0), (128, 16, 4, 0), (64, 16, 8, 200)])
+def test_attention_tc_prefill_more_items_than_sms(K, Dh, Hq, Hkv, window):
+    """22 query tiles x 8 (tile, head group) units = 176 work items: more than the device has SMs, so CTAs of the
+    persistent kernel work through two items each (heavy first, forth and back), with barrier phases, ring slots and
+    tensor memory carried from one item to the next."""
+    from imp_b200.ops import library as L
+    units = Hkv * max(1, (Hq // Hkv) // 2) if (Hq // Hkv) % 2 == 0 else Hq
+    assert 22 * units > L.load().imp_device_sm_count()
+    run_prefill_tc(K, [1500, 1200], [1500, 1200], Hq, Hkv, Dh, 16, window, seed=21)
+    # the same with a far key that the last query of each sequence must find among a thousand
+    out, want = run_prefill_tc(K, [1500, 1200], [1500, 1200], Hq, Hkv, Dh, 16, 0, seed=22, spike=lambda n: n // 9)
+    G = Hq // Hkv
+    for last in (1499, 2699):
+        assert (want.view(-1, Hkv, G, Dh)[last, :, 0, :] > 4.5).all() and (out.view(-1, Hkv, G, Dh)[last, :, 0, :].float() > 4.5).all()
+
+
 @pytest.mark.parametrize("where", ["first", "page_edge", "tile_edge", "far"])
 def test_attention_tc_prefill_finds_one_far_key(K, where):
     """One key's score stands out in every sequence; its value (5.0 everywhere) must dominate head 0 of each group."""
