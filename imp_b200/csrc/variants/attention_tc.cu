@@ -36,6 +36,8 @@
 #include "../common.cuh"
 #include "../tc_common.cuh"
 
+#include <cstdlib>
+
 #ifndef IMP_ATTN_DH
 #error "compile with -DIMP_ATTN_DH=<head size>"
 #endif
@@ -674,7 +676,18 @@ IMP_API int imp_attn_prefill_tc(void* out, int64_t out_stride, const void* q, in
     cudaStream_t s = (cudaStream_t)stream;
 #define FA_ARGS mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, \
                 n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status, s
-    if ((Hq / Hkv) % 2 == 0) return fa_launch<2>(FA_ARGS);
+    // Two heads per item halve the K / V traffic; one head per item gives twice as many, half as long items.  With
+    // fewer two-head items than half the SMs (a portion of a prompt late in a long sequence: few tiles, each with many
+    // keys) the longest item sets the time, so the heads are shared out one by one.
+    static int pair_min_items = -1;       // IMP_B200_ATTN_PAIR_MIN: two heads per item from this many items on
+    if (pair_min_items < 0) {
+        const char* e = getenv("IMP_B200_ATTN_PAIR_MIN");
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+        pair_min_items = e ? atoi(e) : sms / 2 + 1;
+    }
+    const int64_t pair_items = (int64_t)n_tiles * Hkv * ((Hq / Hkv) / 2);
+    if ((Hq / Hkv) % 2 == 0 && pair_items >= pair_min_items) return fa_launch<2>(FA_ARGS);
     return fa_launch<1>(FA_ARGS);
 #undef FA_ARGS
 }
