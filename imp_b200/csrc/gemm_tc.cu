@@ -516,7 +516,9 @@ template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status,
-                        const __grid_constant__ QkvRopeArgs qkv) {
+                        const __grid_constant__ QkvRopeArgs qkv, int splits, int kb_per_split, int64_t split_stride) {
+    // splits > 1 (32-bit output only): the K range is cut into `splits` parts, each (tile, part) is a unit of work of its
+    // own and writes its partial product split_stride elements after the part before; the caller adds the parts in order.
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * TC2_STAGE_BYTES);
@@ -527,7 +529,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
     const int num_m = (M + TC2_BM - 1) / TC2_BM, num_n = (N + TC2_BN - 1) / TC2_BN;
-    const int total = num_m * num_n;
+    const int n_tiles = num_m * num_n;
+    const int total = n_tiles * splits;            // units: all tiles of part 0, then all of part 1, ...
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC2_STAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * TC2_STAGES), acce0 = smem_u32(bars + 2 * TC2_STAGES + 2);
 
@@ -562,9 +565,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             // ------------------------------------------------ producer (one per CTA, for its own halves)
             uint32_t it = 0;
             bool ok = true;
-            for (int t = pair; t < total && ok; t += n_pairs) {
+            for (int u = pair; u < total && ok; u += n_pairs) {
+                const int t = u % n_tiles, z = u / n_tiles;
+                const int kb_lo = z * kb_per_split, kb_hi = min(k_blocks, kb_lo + kb_per_split);
                 const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN + (int)rank * 128;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const uint32_t s = it % TC2_STAGES;
                     ok = mbar_wait(empty0 + 8 * s, ((it / TC2_STAGES) & 1u) ^ 1u, status);
                     if (!ok) break;
@@ -586,13 +591,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             const uint32_t idesc = tc_instr_desc(TC2_BM, TC2_BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int t = pair; t < total && ok; t += n_pairs, ++local) {
+            for (int u = pair; u < total && ok; u += n_pairs, ++local) {
+                const int z = u / n_tiles;
+                const int kb_lo = z * kb_per_split, kb_hi = min(k_blocks, kb_lo + kb_per_split);
                 const uint32_t buf = local & 1u;
                 ok = mbar_wait(acce0 + 8 * buf, ((local >> 1) & 1u) ^ 1u, status);   // both epilogues have drained it
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * TC2_BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const uint32_t s = it % TC2_STAGES;
                     ok = mbar_wait(full0 + 8 * s, (it / TC2_STAGES) & 1u, status);
                     if (!ok) break;
@@ -601,7 +608,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
 #pragma unroll
                     for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
                         tc_mma_pair(d_tmem, tc_smem_desc(a_addr + k * TC_UMMA_K * 2), tc_smem_desc(b_addr + k * TC_UMMA_K * 2),
-                                    idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                                    idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
                     tc_commit_pair(empty0 + 8 * s);
                 }
                 if (ok) tc_commit_pair(accf0 + 8 * buf);
@@ -612,12 +619,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
         const int quarter = warp & 3;
         const uint32_t acce_even0 = cluster_map(acce0, 0);
         uint32_t local = 0;
-        for (int t = pair; t < total; t += n_pairs, ++local) {
+        for (int u = pair; u < total; u += n_pairs, ++local) {
+            const int t = u % n_tiles, z = u / n_tiles;
             const uint32_t buf = local & 1u;
             const bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
             if (!ok) break;
             tc_fence_after_sync();
             const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN;
+            void* Cz = EPI == TC_OUT_F32 ? (void*)(reinterpret_cast<float*>(Cv) + (int64_t)z * split_stride) : Cv;
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
             if (EPI == TC_OUT_QKV_ROPE) {
@@ -627,7 +636,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
                 for (int c = 0; c < TC2_BN / 32; ++c) {
                     float v[32];
                     tc_ld32(taddr + (uint32_t)(c * 32), v);
-                    tc_store32<EPI == TC_OUT_QKV_ROPE ? TC_OUT_BF16 : EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+                    tc_store32<EPI == TC_OUT_QKV_ROPE ? TC_OUT_BF16 : EPI>(Cz, ldc, row, n0 + c * 32, M, N, v);
                 }
             }
             tc_fence_before_sync();
@@ -836,6 +845,36 @@ __global__ void gemm_tc_reduce_kernel(TO* __restrict__ out, int64_t ldc, const f
     }
 }
 
+// The same sums (each element in split order) four columns at a time, for the partial products of many rows.
+template <typename TO>
+__global__ void gemm_tc_reduce4_kernel(TO* __restrict__ out, int64_t ldc, const float* __restrict__ part, int64_t split_stride,
+                                       int M, int N, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n4 = N >> 2;
+    const int64_t total = (int64_t)M * n4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / n4;
+        const int n = (int)(i - m * n4) << 2;
+        const float* src = part + m * N + n;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(src + s * split_stride);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        TO* dst = out + m * ldc + n;
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(dst) = acc;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst) = o;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------- host
 // A [rows, K] bfloat16 matrix with row stride ld elements, fetched in boxes of box_rows x 64 elements.
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld, int box_rows) {
@@ -889,7 +928,7 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
         const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
         const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
         cudaError_t e = imp_launch(gemm_tc_pair_kernel<EPI>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES, s, ma, mw128,
-                                   C, ldc, M, N, K, status, QkvRopeArgs{});
+                                   C, ldc, M, N, K, status, QkvRopeArgs{}, 1, (K + TC_BK - 1) / TC_BK, (int64_t)0);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
         return 0;
     }
@@ -927,6 +966,58 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
     if (epilogue == TC_OUT_BF16) return launch_tc<TC_OUT_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
     if (epilogue == TC_OUT_F32) return launch_tc<TC_OUT_F32>(C, ldc, ma, mw, mw128, M, N, K, status, s);
     return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
+}
+
+// ---- many rows, few tiles: the K range in parts ------------------------------------------------------
+// A portion of a prompt (256 to about a thousand rows) times a weight of a few thousand rows makes fewer 256 x 256
+// tiles than the device has CTA pairs (512 x 4096: 32 tiles on 74 pairs).  Then the K range is cut so that
+// tiles x parts fills the pairs, each part leaves a 32-bit partial product, and gemm_tc_reduce_kernel adds them in order.
+#ifndef TC2_MIN_KB_PER_SPLIT
+#define TC2_MIN_KB_PER_SPLIT 48    // blocks of K (3072 elements) a part has at least: a launch of the pair kernel costs about
+#endif                             // 12 us before and after its MMAs, so parts of a short K gain less than their sum costs
+#ifndef TC2_MAX_SPLITS
+#define TC2_MAX_SPLITS 4
+#endif
+IMP_API int imp_gemm_bf16_tc_splits(int M, int N, int K) {
+    static int enabled = -1;       // IMP_B200_TC_SPLIT=0: never
+    if (enabled < 0) { const char* e = getenv("IMP_B200_TC_SPLIT"); enabled = e ? atoi(e) : 1; }
+    const char* pair_env = getenv("IMP_B200_TC_PAIR");
+    if (!enabled || M < 256 || getenv("IMP_B200_TC_SIMPLE") || (pair_env && atoi(pair_env) == 0)) return 1;
+    const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
+    const int pairs = imp_sm_count() / 2;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    int splits = pairs / (tiles2 > 0 ? tiles2 : 1);
+    if (splits > k_blocks / TC2_MIN_KB_PER_SPLIT) splits = k_blocks / TC2_MIN_KB_PER_SPLIT;
+    if (splits > TC2_MAX_SPLITS) splits = TC2_MAX_SPLITS;
+    return splits < 1 ? 1 : splits;
+}
+
+// scratch[s][M, N] (32-bit, M * N floats apart) for s < imp_gemm_bf16_tc_splits(M, N, K): the parts of A W^T.
+IMP_API int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N,
+                                      int K, int* status, void* stream) {
+    IMP_CHECK_ARG(scratch && A && W && M > 0 && N > 0 && K > 0 && lda >= K && ldw >= K, "imp_gemm_bf16_tc_partials: bad argument");
+    const int splits = imp_gemm_bf16_tc_splits(M, N, K);
+    if (splits < 2) return IMP_ERR_UNSUPPORTED;
+    if (K % 8 || lda % 8 || ldw % 8 || N % 4 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)scratch % 16) return IMP_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TC_OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM_BYTES);
+        if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_partials: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    CUtensorMap ma, mw128;
+    if (int rc = make_map(&ma, A, M, K, lda, TC_BM)) return rc;
+    if (int rc = make_map(&mw128, W, N, K, ldw, 128)) return rc;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    const int kb_per_split = (k_blocks + splits - 1) / splits;
+    const int units = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN) * splits;
+    const int sms = imp_sm_count();
+    const int pairs = units < sms / 2 ? units : sms / 2;
+    cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_F32>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
+                               (cudaStream_t)stream, ma, mw128, (void*)scratch, (int64_t)N, M, N, K, status, QkvRopeArgs{}, splits,
+                               kb_per_split, (int64_t)M * N);
+    if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_partials: %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
 }
 
 // ---- few rows (M <= 128) ----------------------------------------------------------------------------
@@ -1091,13 +1182,24 @@ IMP_API int imp_gemm_bf16_tc_swap_sum(void* C, int64_t ldc, int epilogue, const 
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t total = (int64_t)M * N;
     const int64_t cap = (int64_t)imp_sm_count() * 8;
-    const int grid = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
     cudaError_t e;
-    if (epilogue == TC_OUT_F32)
-        e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, scratch, total, M, N, splits);
-    else
-        e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc, scratch,
-                       total, M, N, splits);
+    if (M > 128 && N % 4 == 0 && ldc % 4 == 0 && (uintptr_t)C % 16 == 0 && (uintptr_t)scratch % 16 == 0) {
+        // many rows (the parts of a portion's product): four columns a thread
+        const int64_t work = total / 4;
+        const int grid = (int)((work + 255) / 256 < cap ? (work + 255) / 256 : cap);
+        if (epilogue == TC_OUT_F32)
+            e = imp_launch(gemm_tc_reduce4_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, scratch, total, M, N, splits);
+        else
+            e = imp_launch(gemm_tc_reduce4_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc, scratch,
+                           total, M, N, splits);
+    } else {
+        const int grid = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+        if (epilogue == TC_OUT_F32)
+            e = imp_launch(gemm_tc_reduce_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)C, ldc, scratch, total, M, N, splits);
+        else
+            e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc, scratch,
+                           total, M, N, splits);
+    }
     if (e != cudaSuccess) { imp_set_error("gemm_tc_swap_sum: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1147,7 +1249,8 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
     const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
-                               (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a);
+                               (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a, 1,
+                               (K + TC_BK - 1) / TC_BK, (int64_t)0);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }

@@ -49,6 +49,9 @@ int imp_gemm_bf16_stream(void* C, int64_t ldc, int out_dtype, const void* A, int
                          int N, int K, void* stream);
 int imp_gemm_bf16_stream_swiglu(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N,
                                 int K, void* stream);
+int imp_gemm_bf16_tc_splits(int M, int N, int K);
+int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, int* status,
+                              void* stream);
 int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw, int M,
                      int N, int K, int* status, void* stream);
 int64_t imp_gemm_bf16_tc_swap_scratch_floats(int M, int N, int K, int epilogue);

@@ -91,6 +91,23 @@ static void gemm_stream(Runtime& rt, Tensor out, const Tensor& a, const Tensor& 
 
 static bool gemm_tc(Runtime& rt, Tensor out, const Tensor& a, const Tensor& w, int epilogue = -1) {
     if (epilogue < 0) epilogue = out.dtype == F32 ? TC_OUT_F32 : TC_OUT_BF16;
+    if (epilogue != TC_OUT_SWIGLU) {
+        // few 256 x 256 tiles for the device's CTA pairs (a portion of a prompt): the K range in parts, then their sum
+        const int M = (int)rows(a), N = (int)rows(w), K = (int)cols(a);
+        const int n_splits = imp_gemm_bf16_tc_splits(M, N, K);
+        if (n_splits > 1) {
+            const Arena::Mark mark = rt.arena->mark();
+            float* parts = (float*)rt.arena->alloc((size_t)n_splits * M * N * 4);
+            const int rc = imp_gemm_bf16_tc_partials(parts, a.data, a.stride0, w.data, w.stride0, M, N, K, rt.status, rt.stream);
+            if (rc != -2) {
+                check_launch(rc, "gemm_bf16_tc_partials");
+                check_launch(imp_gemm_bf16_tc_swap_sum(out.data, out.stride0, epilogue, parts, M, N, n_splits, rt.stream), "gemm_bf16_tc_sum");
+                rt.launches += 2;
+                return true;
+            }
+            rt.arena->restore(mark);
+        }
+    }
     const int rc = imp_gemm_bf16_tc(out.data, out.stride0, epilogue, a.data, a.stride0, w.data, w.stride0, (int)rows(a),
                                     (int)rows(w), (int)cols(a), rt.status, rt.stream);
     if (rc == -2) return false;
