@@ -182,13 +182,18 @@ def stop(eng, reqs):
         r.release()
 
 
-def timed_steps(eng, n, B):
-    """n decode steps of B sequences between two CUDA events on the engine's stream: device milliseconds."""
+def timed_steps(eng, n, B, wall=None):
+    """n decode steps of B sequences between two CUDA events on the engine's stream: device milliseconds.  `wall`
+    (a list) also gets the host's milliseconds around the same calls, tokens read on the host after every step."""
+    t0 = time.perf_counter()
     eng.timer_start()
     for _ in range(n):
         outs = eng.step()
         assert len(outs) == B, f"{len(outs)} tokens from a step of {B} sequences: a request left the batch"
-    return eng.timer_stop()
+    ms = eng.timer_stop()
+    if wall is not None:
+        wall.append((time.perf_counter() - t0) * 1e3)
+    return ms
 
 
 def time_prefill(eng, rng, vocab, n_prompt, chunk, reps=7):
@@ -217,9 +222,9 @@ def decode_protocol(eng, rng, cfgd, n_layers, B, peaks, window=256):
     reqs = start_decoding(eng, rng, cfgd["vocab_size"], B, START, total + STAGGER)
     eng.step()                                       # the first decode step of a batch size runs eagerly, the second is captured
     eng.step()
-    done, win_ms = 0, []       # the two steps above are not counted: the stagger leaves room for them
+    done, win_ms, wall_ms = 0, [], []       # the two steps above are not counted: the stagger leaves room for them
     while done + window <= total:
-        win_ms.append(timed_steps(eng, window, B) / window)
+        win_ms.append(timed_steps(eng, window, B, wall_ms) / window)
         done += window
     stop(eng, reqs)
 
@@ -230,9 +235,11 @@ def decode_protocol(eng, rng, cfgd, n_layers, B, peaks, window=256):
 
     n = len(win_ms)
     all_ms = sum(win_ms) / n
+    e2e_ms = sum(wall_ms) / (n * window)       # the same steps by the host's clock, through the entry point
     return {"batch": B, "steps": n * window, "first256": point(win_ms[0], START + 2 + window / 2),
             "last256": point(win_ms[-1], START + 2 + (n - 0.5) * window),
-            "all": point(all_ms, START + 2 + n * window / 2), "ms_per_step_over_windows": spread(win_ms)}
+            "all": point(all_ms, START + 2 + n * window / 2), "ms_per_step_over_windows": spread(win_ms),
+            "e2e": {"tok_s": round(B / e2e_ms * 1e3, 1), "ms": round(e2e_ms, 4), "over_device": round(e2e_ms / all_ms, 4)}}
 
 
 def yardsticks(peaks, reps=20):
