@@ -59,6 +59,7 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p]),
     "imp_gemm_bf16_tc_swap_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
     "imp_gemm_bf16_tc_swap_splits": (c_int, [c_int, c_int, c_int]),
+    "imp_gemm_bf16_tc_splits": (c_int, [c_int, c_int, c_int]),
     "imp_gemm_tc_test_hooks": (c_int, [ctypes.c_uint, c_int]),
     "imp_gemm_bf16_tc_swap_partials": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
                                                c_void_p, c_void_p]),

@@ -280,6 +280,29 @@ def test_gemm_bf16_tcgen05_fused_swiglu(K, M, F, K_):
     close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
 
 
+@pytest.mark.parametrize("M,N,K_", [(512, 4096, 12288), (300, 1024, 6144), (256, 520, 9224), (1000, 2048, 6208)])
+@pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
+def test_linear_with_the_k_range_in_parts(K, M, N, K_, odtype):
+    """A portion of a prompt times a weight with few rows and a long K: fewer 256 x 256 tiles than half the CTA pairs,
+    so the library cuts K into parts that are units of work of their own and adds the partial products in order.  The
+    ragged cases: rows and columns that do not fill tiles, a K that the parts do not divide."""
+    from imp_b200.ops import library as L
+    assert L.load().imp_gemm_bf16_tc_splits(M, N, K_) >= 2
+    a, w = rnd(M, K_, dtype=torch.bfloat16, seed=60).to(DEV), (rnd(N, K_, dtype=torch.bfloat16, seed=61) * 0.05).to(DEV)
+    out = K.linear(torch.full((M, N), float("nan"), dtype=odtype, device=DEV), a, w)
+    want = a.double().cpu() @ w.double().cpu().T
+    if odtype == torch.float32:
+        close(out, want, torch.float32, scale=float(want.abs().max()) * 8)
+    else:
+        close(out, want, torch.bfloat16)
+    before = K.fallback_calls()
+    K.linear(out, a, w)
+    assert K.fallback_calls() == before
+    # the same product the same way twice: the same bits (the parts are added in a fixed order)
+    again = K.linear(torch.empty_like(out), a, w)
+    assert torch.equal(out, again)
+
+
 def test_linear_dispatch(K):
     x = rnd(40, 96, dtype=torch.bfloat16, seed=12).to(DEV)
     w = rnd(50, 96, dtype=torch.bfloat16, seed=13).to(DEV)
