@@ -281,6 +281,75 @@ def yardsticks(peaks, reps=20):
     return out
 
 
+def attention_yardsticks(reps=20):
+    """The prefill attention of the benchmark shape (2,048 tokens, one sequence, paged cache) three ways: this
+    library's tcgen05 kernel, its plain mma.sync kernel (the class of kernel the reference runs on this architecture:
+    4-warp WMMA, src/compute/attention_dispatch.cu:27-57), and the library attention behind torch's
+    scaled_dot_product_attention on the same dense q, k, v.  CUDA events over `reps` launches each."""
+    import math
+
+    import torch
+
+    from imp_b200.ops import attention as A
+    from imp_b200.ops import kernels as K
+    T, Hq, Hkv, Dh, P = PREFILL_TOKENS, MODEL["num_attention_heads"], MODEL["num_key_value_heads"], MODEL["head_dim"], PAGE
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(T, Hq * Dh, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, Dh, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, Dh, generator=g, device=dev).to(torch.bfloat16)
+    n_pages = T // P
+    perm = torch.randperm(n_pages, generator=g, device=dev)
+    kc = torch.zeros(n_pages, Hkv, P, Dh, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    pos = torch.arange(T, device=dev)
+    kc[perm[pos // P], :, pos % P] = k
+    vc[perm[pos // P], :, pos % P] = v
+    bt = perm.to(torch.int32).view(1, n_pages).contiguous()
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    positions = pos.to(torch.int32)
+    status = K.new_status(dev)
+    scale = 1.0 / math.sqrt(Dh)
+
+    def tiles(n):
+        t0 = torch.arange(0, T, n, dtype=torch.int32, device=dev)
+        return t0, torch.full_like(t0, n)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    out = torch.empty(T, Hq * Dh, dtype=torch.bfloat16, device=dev)
+    t128, r128 = tiles(128)
+    t32, r32 = tiles(32)
+    res = {"shape": f"{T} tokens, {Hq}/{Hkv} heads x {Dh}, causal"}
+    res["own_tcgen05_us"] = round(timed(lambda: A.prefill_attention_tc(out, q, Hq, Hkv, Dh, kc, vc, bt, seq, positions, t128, r128,
+                                                                       scale, 0, status)), 1)
+    res["own_mma_sync_us"] = round(timed(lambda: A.prefill_attention(out, q, Hq, Hkv, Dh, kc, vc, bt, seq, positions, t32, r32,
+                                                                     scale, 0, status)), 1)
+    K.check_status(status)
+    try:
+        qd = q.view(T, Hq, Dh).transpose(0, 1).unsqueeze(0).contiguous()
+        kd = k.transpose(0, 1).unsqueeze(0).repeat_interleave(Hq // Hkv, dim=1).contiguous()
+        vd = v.transpose(0, 1).unsqueeze(0).repeat_interleave(Hq // Hkv, dim=1).contiguous()
+        sdpa = torch.nn.functional.scaled_dot_product_attention
+        res["torch_sdpa_us"] = round(timed(lambda: sdpa(qd, kd, vd, is_causal=True, scale=scale)), 1)
+    except Exception as e:
+        res["torch_sdpa_us"] = None
+        res["torch_sdpa_error"] = f"{type(e).__name__}: {e}"[:120]
+    flops = 4.0 * Hq * Dh * T * (T + 1) / 2
+    res["own_tcgen05_tflops"] = round(flops / res["own_tcgen05_us"] / 1e6, 1)
+    return res
+
+
 def library_arm_prefill(args):
     """The whole 2,048-token prefill with the products of more than 16 rows on cuBLASLt (IMP_B200_GEMM=cublas is
     read once per process, so this is a run of its own)."""
@@ -414,6 +483,10 @@ def run_ours(args):
     if not args.quick:
         try:
             line["yardsticks"] = yardsticks(peaks)
+            try:
+                line["yardsticks"]["attention_prefill_2048"] = attention_yardsticks()
+            except Exception as e:     # a yardstick is extra: its absence must not take the line with it
+                line["yardsticks"]["attention_prefill_2048"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
             line["yardsticks"]["prefill_2048_on_cublaslt"] = library_arm_prefill(args)
             line["yardsticks"]["prefill_2048_own_ms"] = prefill["ms"]
         except Exception as e:
