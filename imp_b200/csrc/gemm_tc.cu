@@ -468,7 +468,26 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
 constexpr int TC2_STAGES = 6;
 constexpr int TC2_HALF_BYTES = 128 * TC_BK * 2;                 // 16 KiB: 128 rows of A, or of W
 constexpr int TC2_STAGE_BYTES = 2 * TC2_HALF_BYTES;
-constexpr int TC2_SMEM_BYTES = TC2_STAGES * TC2_STAGE_BYTES + 1024 + 256;
+// Output staging for the bfloat16 epilogues: two buffers of 128 rows x 128 bytes (64 output columns), written row by
+// row with the 128-byte swizzle and handed to TMA stores.  (Each thread storing 16 bytes to its own row of C cost a
+// 2,048 x 4,096 x 4,096 product 8 % of its time and one of 512 rows 12 %.)
+constexpr int TC2_OUT_BYTES = 128 * 128;
+constexpr int TC2_RING_BYTES = TC2_STAGES * TC2_STAGE_BYTES;
+constexpr int TC2_SMEM_BYTES = TC2_RING_BYTES + 2 * TC2_OUT_BYTES + 1024 + 256;
+static_assert(TC2_SMEM_BYTES <= 227 * 1024, "the pair kernel's shared memory");
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 tc2_pack8(const float* v) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    return o;
+}
 constexpr int TC2_BM = 256, TC2_BN = 256;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -516,12 +535,16 @@ template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status,
-                        const __grid_constant__ QkvRopeArgs qkv, int splits, int kb_per_split, int64_t split_stride) {
+                        const __grid_constant__ QkvRopeArgs qkv, int splits, int kb_per_split, int64_t split_stride,
+                        const __grid_constant__ CUtensorMap map_c, int tma_store) {
+    // tma_store (bfloat16 and SwiGLU epilogues): C goes out through shared memory and TMA stores described by map_c
+    // (boxes of 128 rows x 64 columns, clipped at the matrix edges) instead of 16-byte stores from every thread.
     // splits > 1 (32-bit output only): the K range is cut into `splits` parts, each (tile, part) is a unit of work of its
     // own and writes its partial product split_stride elements after the part before; the caller adds the parts in order.
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * TC2_STAGE_BYTES);
+    unsigned char* out_stage = tiles + TC2_RING_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + 2 * TC2_OUT_BYTES);
     // bars: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC2_STAGES + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -618,11 +641,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int quarter = warp & 3;
         const uint32_t acce_even0 = cluster_map(acce0, 0);
+        const bool storer = warp == 2 && lane == 0;      // issues the TMA stores and waits for them
+        uint32_t out_n = 0;                              // staging buffers used so far
         uint32_t local = 0;
         for (int u = pair; u < total; u += n_pairs, ++local) {
             const int t = u % n_tiles, z = u / n_tiles;
             const uint32_t buf = local & 1u;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
+            bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
+            if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store) {
+                // the four warps meet at barriers below: they go on, or give up, together
+                uint32_t all;
+                asm volatile(
+                    "{\n"
+                    ".reg .pred p, q;\n"
+                    "setp.ne.u32 p, %1, 0;\n"
+                    "bar.red.and.pred q, 2, 128, p;\n"
+                    "selp.u32 %0, 1, 0, q;\n"
+                    "}\n"
+                    : "=r"(all)
+                    : "r"((uint32_t)ok)
+                    : "memory");
+                ok = all != 0;
+            }
             if (!ok) break;
             tc_fence_after_sync();
             const int m0 = (t % num_m) * TC2_BM + (int)rank * 128, n0 = (t / num_m) * TC2_BN;
@@ -631,6 +671,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
             if (EPI == TC_OUT_QKV_ROPE) {
                 qkv_rope_row(qkv, taddr, row, n0, N, row < M, status);
+            } else if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store) {
+                constexpr int SUBS = EPI == TC_OUT_SWIGLU_BF16 ? 2 : 4;     // sub-tiles of 64 output columns
+                const int x0 = EPI == TC_OUT_SWIGLU_BF16 ? n0 >> 1 : n0;
+                const int r = quarter * 32 + lane;                          // row in the CTA's half of the tile
+#pragma unroll 1
+                for (int j = 0; j < SUBS; ++j, ++out_n) {
+                    unsigned char* buf = out_stage + (out_n & 1u) * TC2_OUT_BYTES;
+                    // the store that read this buffer two sub-tiles ago has finished reading it
+                    if (storer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    uint4 q[8];
+                    if (EPI == TC_OUT_BF16) {
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) {
+                            float v[32];
+                            tc_ld32(taddr + (uint32_t)((2 * j + cc) * 32), v);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) q[4 * cc + i] = tc2_pack8(v + 8 * i);
+                        }
+                    } else {
+                        // 32 accumulator columns = gate (8), up (8), gate (8), up (8): 16 outputs
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) {
+                            float v[32], o[16];
+                            tc_ld32(taddr + (uint32_t)((4 * j + cc) * 32), v);
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
+                                    o[8 * h + i] = gate / (1.f + expf(-gate)) * up;
+                                }
+                            q[2 * cc] = tc2_pack8(o);
+                            q[2 * cc + 1] = tc2_pack8(o + 8);
+                        }
+                    }
+                    unsigned char* rowp = buf + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = q[c];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (storer) {
+                        tma_store_2d(&map_c, smem_u32(buf), x0 + j * 64, m0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < TC2_BN / 32; ++c) {
@@ -643,6 +729,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acce_even0 + 8 * buf);
         }
+        if (storer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // C is written before the CTA leaves
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -927,8 +1014,15 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
     if (mode == 0 && pair_mode == 1 && M >= 256) {
         const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
         const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+        // bfloat16 outputs leave through TMA stores where C's rows allow them (16-byte strides)
+        static int tma_out = -1;       // IMP_B200_TC_TMA_STORE=0: every thread stores its own row
+        if (tma_out < 0) { const char* e = getenv("IMP_B200_TC_TMA_STORE"); tma_out = e ? atoi(e) : 1; }
+        CUtensorMap mc{};
+        int tma_store = 0;
+        if (EPI != TC_OUT_F32 && tma_out && ldc % 8 == 0)
+            tma_store = make_map(&mc, C, M, EPI == TC_OUT_SWIGLU_BF16 ? N / 2 : N, ldc, 128) == 0 ? 1 : 0;
         cudaError_t e = imp_launch(gemm_tc_pair_kernel<EPI>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES, s, ma, mw128,
-                                   C, ldc, M, N, K, status, QkvRopeArgs{}, 1, (K + TC_BK - 1) / TC_BK, (int64_t)0);
+                                   C, ldc, M, N, K, status, QkvRopeArgs{}, 1, (K + TC_BK - 1) / TC_BK, (int64_t)0, mc, tma_store);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
         return 0;
     }
@@ -1015,7 +1109,7 @@ IMP_API int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda
     const int pairs = units < sms / 2 ? units : sms / 2;
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_F32>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)scratch, (int64_t)N, M, N, K, status, QkvRopeArgs{}, splits,
-                               kb_per_split, (int64_t)M * N);
+                               kb_per_split, (int64_t)M * N, CUtensorMap{}, 0);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_partials: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1250,7 +1344,7 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a, 1,
-                               (K + TC_BK - 1) / TC_BK, (int64_t)0);
+                               (K + TC_BK - 1) / TC_BK, (int64_t)0, CUtensorMap{}, 0);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
