@@ -362,11 +362,36 @@ __device__ __forceinline__ void store32_bf16(__nv_bfloat16* dst, const float (&v
     }
 }
 
+// Output staging of the CTA-pair kernel: buffers of 128 rows x 128 bytes (64 bfloat16 columns), written row by row with
+// the 128-byte swizzle and handed to TMA stores.
+constexpr int TC2_OUT_BYTES = 128 * 128;
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 tc2_pack8(const float* v) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    return o;
+}
+// Where the q part of the fused epilogue goes when it leaves through TMA stores (bufs == nullptr: every thread stores
+// its own row): the two staging buffers, q's tensor map, whether this thread issues the stores, the thread's row in
+// the CTA's half tile and that half tile's first row in q.
+struct QkvStage {
+    unsigned char* bufs;
+    const CUtensorMap* map;
+    bool storer;
+    int r, m0;
+};
+
 // One accumulator row (token `row`, tensor-memory address `taddr` of its first column) of the tile that
 // starts at column n0.  All 32 lanes of the warp call it together (the tensor-memory loads are collective);
 // `live` says whether this lane's row exists.
 __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t taddr, int row, int n0, int N, bool live,
-                                             int* status) {
+                                             int* status, const QkvStage& stg) {
     const int Dh = a.Dh, half = Dh >> 1, chunks = Dh >> 5;          // 32-column chunks per head: 2 or 4
     int pos = 0;
     int64_t page_row = -1;
@@ -418,16 +443,22 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
             }
             inv = rsqrtf(ss / (float)Dh + a.eps);
         }
+        const bool staged = is_q && stg.bufs != nullptr;            // uniform over the CTA's epilogue warps
         __nv_bfloat16* dst = nullptr;
         if (live) {
             if (is_q) dst = a.q_out + (int64_t)row * a.q_stride + (int64_t)hh * Dh;
             else if (page_row >= 0) dst = a.k_cache + (page_row + (int64_t)(hh - a.Hq) * a.page_size) * Dh;
         }
+        if (staged) {
+            // both buffers are free once the stores of the head before have read them
+            if (stg.storer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         for (int c = 0; c < chunks / 2; ++c) {                      // dims [32c, 32c+32) pair with [half + 32c, ...)
             float x[32], y[32];
             tc_ld32(thead + (uint32_t)(c * 32), x);
             tc_ld32(thead + (uint32_t)(half + c * 32), y);
-            if (dst == nullptr) continue;
+            if (dst == nullptr && !staged) continue;                // (a staged row without a token writes what TMA clips)
             round32_bf16(x);
             round32_bf16(y);
             // the table row of this token is read 16 bytes at a time: 32 rows touch 32 sectors per load either
@@ -446,8 +477,29 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
                     y[i] = xa * si[j] + yb * co[j];
                 }
             }
-            store32_bf16(dst + c * 32, x);
-            store32_bf16(dst + half + c * 32, y);
+            if (staged) {
+                // 32 dims = four 16-byte pieces of the row of the 64-column buffer they fall into
+                const int dx = c * 32, dy = half + c * 32;
+                unsigned char* rx = stg.bufs + (dx >> 6) * TC2_OUT_BYTES + stg.r * 128;
+                unsigned char* ry = stg.bufs + (dy >> 6) * TC2_OUT_BYTES + stg.r * 128;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    *reinterpret_cast<uint4*>(rx + (((((dx & 63) >> 3) + i) ^ (stg.r & 7)) << 4)) = tc2_pack8(x + 8 * i);
+                    *reinterpret_cast<uint4*>(ry + (((((dy & 63) >> 3) + i) ^ (stg.r & 7)) << 4)) = tc2_pack8(y + 8 * i);
+                }
+            } else {
+                store32_bf16(dst + c * 32, x);
+                store32_bf16(dst + half + c * 32, y);
+            }
+        }
+        if (staged) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (stg.storer) {
+                for (int sub = 0; sub < Dh / 64; ++sub)
+                    tma_store_2d(stg.map, smem_u32(stg.bufs + sub * TC2_OUT_BYTES), hh * Dh + sub * 64, stg.m0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         }
     }
 }
@@ -471,23 +523,11 @@ constexpr int TC2_STAGE_BYTES = 2 * TC2_HALF_BYTES;
 // Output staging for the bfloat16 epilogues: two buffers of 128 rows x 128 bytes (64 output columns), written row by
 // row with the 128-byte swizzle and handed to TMA stores.  (Each thread storing 16 bytes to its own row of C cost a
 // 2,048 x 4,096 x 4,096 product 8 % of its time and one of 512 rows 12 %.)
-constexpr int TC2_OUT_BYTES = 128 * 128;
 constexpr int TC2_RING_BYTES = TC2_STAGES * TC2_STAGE_BYTES;
 constexpr int TC2_SMEM_BYTES = TC2_RING_BYTES + 2 * TC2_OUT_BYTES + 1024 + 256;
 static_assert(TC2_SMEM_BYTES <= 227 * 1024, "the pair kernel's shared memory");
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src)
-                 : "memory");
-}
-__device__ __forceinline__ uint4 tc2_pack8(const float* v) {
-    uint4 o;
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
-    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-    return o;
-}
+
 constexpr int TC2_BM = 256, TC2_BN = 256;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -648,7 +688,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             const int t = u % n_tiles, z = u / n_tiles;
             const uint32_t buf = local & 1u;
             bool ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (local >> 1) & 1u, status));
-            if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store) {
+            if (EPI != TC_OUT_F32 && tma_store) {
                 // the four warps meet at barriers below: they go on, or give up, together
                 uint32_t all;
                 asm volatile(
@@ -670,7 +710,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
             if (EPI == TC_OUT_QKV_ROPE) {
-                qkv_rope_row(qkv, taddr, row, n0, N, row < M, status);
+                const QkvStage stg{tma_store ? out_stage : nullptr, &map_c, storer, quarter * 32 + lane, m0};
+                qkv_rope_row(qkv, taddr, row, n0, N, row < M, status, stg);
             } else if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store) {
                 constexpr int SUBS = EPI == TC_OUT_SWIGLU_BF16 ? 2 : 4;     // sub-tiles of 64 output columns
                 const int x0 = EPI == TC_OUT_SWIGLU_BF16 ? n0 >> 1 : n0;
@@ -1342,9 +1383,16 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     a.Hq = Hq; a.Hkv = Hkv; a.Dh = Dh; a.page_size = page_size; a.num_pages = num_pages;
     const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
     const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+    // q leaves through TMA stores (k and v go to their pages row by row)
+    CUtensorMap mq{};
+    int q_tma = 0;
+    {
+        const char* env = getenv("IMP_B200_TC_TMA_STORE");
+        if (!(env && atoi(env) == 0) && q_stride % 8 == 0) q_tma = make_map(&mq, q_out, M, Hq * Dh, q_stride, 128) == 0 ? 1 : 0;
+    }
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a, 1,
-                               (K + TC_BK - 1) / TC_BK, (int64_t)0, CUtensorMap{}, 0);
+                               (K + TC_BK - 1) / TC_BK, (int64_t)0, mq, q_tma);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
