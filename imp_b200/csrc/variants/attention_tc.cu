@@ -58,7 +58,8 @@ template <int NQ> struct FaCfg {
     static constexpr int V_STAGES = 2;
     static constexpr int THREADS = 128 + 128 * NQ;        // warps 0-3: producer, MMA issuer, two idle; then 4 per head
     static constexpr int TMEM_COLS = 256 * NQ;
-    static constexpr int TILE_BYTES = NQ * FA_Q_BYTES + (K_STAGES + V_STAGES) * FA_KV_BYTES;
+    static constexpr int OUT_BYTES = 128 * 128;           // per head: 128 rows x 64 dims of O on their way to a TMA store
+    static constexpr int TILE_BYTES = NQ * FA_Q_BYTES + (K_STAGES + V_STAGES) * FA_KV_BYTES + NQ * OUT_BYTES;
     static constexpr int N_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 4 * NQ;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
 };
@@ -201,7 +202,8 @@ struct FaItem {
 template <int NQ>
 __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int64_t out_stride,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, int out_tma,
+    __nv_bfloat16* __restrict__ out, int64_t out_stride,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_tiles,
     int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2, int window, int* status) {
@@ -212,6 +214,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     unsigned char* q_s = tiles;                                   // [NQ][FA_Q_BYTES]
     unsigned char* k_s = q_s + NQ * FA_Q_BYTES;                   // [KS][FA_KV_BYTES]
     unsigned char* v_s = k_s + KS * FA_KV_BYTES;                  // [VS][FA_KV_BYTES]
+    unsigned char* o_s = v_s + VS * FA_KV_BYTES;                  // [NQ][OUT_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::TILE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BARS);
     const uint32_t q_full = smem_u32(bars), q_empty = q_full + 8;
@@ -553,7 +556,59 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         // The item's result.  The loads of O are complete (tc_ld32 waits) before this warp signals its next P, and the
         // first P V of the next item, which overwrites O, waits for that signal of all four warps.
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done0 + 8 * w, (uint32_t)(t_n - 1) & 1u, status));
-        if (ok) {
+        if (out_tma) {
+            // the head's four warps meet at barriers below: they go on, or give up, together (a warp that gave up
+            // inside the item arrives here too, the others after their own waits have run out)
+            uint32_t all;
+            asm volatile(
+                "{\n"
+                ".reg .pred p, q;\n"
+                "setp.ne.u32 p, %1, 0;\n"
+                "bar.red.and.pred q, %2, 128, p;\n"
+                "selp.u32 %0, 1, 0, q;\n"
+                "}\n"
+                : "=r"(all)
+                : "r"((uint32_t)ok), "r"(1 + w)
+                : "memory");
+            ok = all != 0;
+        }
+        if (ok && out_tma && rows == FA_BM) {
+            // A full tile leaves through shared memory and TMA stores, 64 dims at a time: every thread storing 16 bytes
+            // to its own row of `out` (rows 8 KB apart) took about 3 us per item.  (A ragged tile keeps the stores below:
+            // a box of 128 rows would run into the next sequence's tokens.)
+            tc_fence_after_sync();
+            const float inv_l = l > 0.f ? 1.f / l : 0.f;
+            unsigned char* buf = o_s + w * Cfg::OUT_BYTES;
+            const bool storer = (warp & 3) == 0 && lane == 0;
+#pragma unroll 1
+            for (int sub = 0; sub < DH / 64; ++sub) {
+                if (storer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the buffer's last store has read it
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    float o[32];
+                    tc_ld32(o_tmem + (uint32_t)((2 * sub + cc) * 32), o);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        uint4 u;
+                        u.x = fa_pack(o[8 * t] * inv_l, o[8 * t + 1] * inv_l);
+                        u.y = fa_pack(o[8 * t + 2] * inv_l, o[8 * t + 3] * inv_l);
+                        u.z = fa_pack(o[8 * t + 4] * inv_l, o[8 * t + 5] * inv_l);
+                        u.w = fa_pack(o[8 * t + 6] * inv_l, o[8 * t + 7] * inv_l);
+                        *reinterpret_cast<uint4*>(buf + row * 128 + (((4 * cc + t) ^ (row & 7)) << 4)) = u;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+                if (storer) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_o),
+                                 "r"((it.head0 + w) * DH + sub * 64), "r"(it.tok0), "r"(smem_u32(buf))
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+            tc_fence_before_sync();
+        } else if (ok) {
             tc_fence_after_sync();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* o_row = out + (int64_t)(it.tok0 + row) * out_stride + (int64_t)(it.head0 + w) * DH;
@@ -576,6 +631,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             tc_fence_before_sync();
         }
         }
+        if (out_tma && (warp & 3) == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // `out` is written
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -620,7 +676,8 @@ IMP_API int imp_attn_prefill_tc_supported(int64_t q_stride, int64_t out_stride, 
 }
 
 template <int NQ>
-static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out, int64_t out_stride,
+static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, int out_tma,
+                     __nv_bfloat16* out, int64_t out_stride,
                      const int* block_table, int bt_stride, const int* seq_of_token, const int* positions,
                      const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv, int P,
                      int num_pages, float scale_log2, int window, int* status, cudaStream_t s) {
@@ -642,7 +699,7 @@ static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     }
     const int64_t grid = items < sms ? items : sms;
     cudaError_t e = imp_launch(attn_prefill_tc_kernel<NQ>, dim3((unsigned)grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, s, mq, mk,
-                               mv, out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows,
+                               mv, mo, out_tma, out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows,
                                n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status);
     if (e != cudaSuccess) { imp_set_error("imp_attn_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
@@ -674,7 +731,14 @@ IMP_API int imp_attn_prefill_tc(void* out, int64_t out_stride, const void* q, in
     if (int rc = fa_make_map(&mv, vc, kv_rows, DH, DH, P, "v")) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
-#define FA_ARGS mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, \
+    // full tiles of the result leave through TMA stores (boxes of 128 rows x 64 dims of `out`)
+    CUtensorMap mo{};
+    int out_tma = 0;
+    {
+        const char* env = getenv("IMP_B200_ATTN_TMA_STORE");
+        if (!(env && atoi(env) == 0)) out_tma = fa_make_map(&mo, out, n_tokens, Hq * DH, out_stride, FA_BM, "out") == 0 ? 1 : 0;
+    }
+#define FA_ARGS mq, mk, mv, mo, out_tma, (__nv_bfloat16*)out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, \
                 n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status, s
     // Two heads per item halve the K / V traffic; one head per item gives twice as many, half as long items.  With
     // fewer two-head items than half the SMs (a portion of a prompt late in a long sequence: few tiles, each with many
