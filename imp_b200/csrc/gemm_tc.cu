@@ -1388,7 +1388,9 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     int q_tma = 0;
     {
         const char* env = getenv("IMP_B200_TC_TMA_STORE");
-        if (!(env && atoi(env) == 0) && q_stride % 8 == 0) q_tma = make_map(&mq, q_out, M, Hq * Dh, q_stride, 128) == 0 ? 1 : 0;
+        const char* env_q = getenv("IMP_B200_TC_TMA_Q");
+        if (!(env && atoi(env) == 0) && !(env_q && atoi(env_q) == 0) && q_stride % 8 == 0)
+            q_tma = make_map(&mq, q_out, M, Hq * Dh, q_stride, 128) == 0 ? 1 : 0;
     }
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a, 1,
