@@ -23,6 +23,7 @@ the 126 MB L2, so no explicit L2 flush is needed between timed iterations ("inpu
 Other runs, each printing its own JSON line:
     python bench.py --only decode [--batch B] [--context C] [--page P] [--layers N] [--no-graphs]
     python bench.py --only prefill [--tokens T] [--chunk C] [--layers N]
+    IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C]   (a table, not JSON)
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
@@ -364,6 +365,91 @@ def library_arm_prefill(args):
         return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
+TIMELINE_KERNELS = {2: "sum of K parts", 3: "decode attention", 4: "add+norm (cluster)", 5: "few-rows product (mma.sync)",
+                    6: "add+norm (one CTA a row)", 7: "merge of key splits", 10: "few-rows product", 11: "few-rows product, K parts",
+                    12: "few-rows gate/up + SwiGLU"}
+
+
+def run_timeline(args):
+    """One decode step as its kernels saw it: needs a build with IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE, in which thread 0 of
+    every CTA of the decode kernels records the global timer at its start, after its wait for the kernel before it, and
+    at its end.  Prints, per kernel, the launches of one step with the mean time from the wait to the last CTA's end, the
+    mean gap between the end of the launch before and the wait, how long before the wait the CTAs were resident (and
+    fetching what does not depend on earlier kernels), and the spread of the CTAs' ends."""
+    import ctypes
+    import numpy as np
+    import torch
+    from imp_b200.ops import attention as A
+    from imp_b200.ops import library as L
+    if "-DIMP_TIMELINE" not in os.environ.get("IMP_B200_NVCC_FLAGS", ""):
+        print("bench.py --only timeline needs IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE (a diagnostic build of the library)")
+        return 2
+    cfgd = dict(MODEL)
+    n_layers = args.layers or MODEL["num_hidden_layers"]
+    cfgd["num_hidden_layers"] = n_layers
+    B, ctx = args.batch, args.context or CONTEXT
+    eng, _ = make_engine(cfgd, args, B, ctx)
+    rng = random.Random(0)
+    reqs = start_decoding(eng, rng, cfgd["vocab_size"], B, ctx - 4 * B - 16, 4 * B + 24)   # the early ones still run at the end
+    for _ in range(8):
+        eng.step()
+    torch.cuda.synchronize()
+    cap = 400000
+    buf = torch.zeros(cap * 4, dtype=torch.int64, device="cuda")
+    count = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for handle, name in ((L.load(), "imp_tl_set_gemm_tc"), (L.load(), "imp_tl_set_norm"), (L.load(), "imp_tl_set_gemm_stream"),
+                         (A.variant(cfgd["head_dim"]), "imp_tl_set_attention_mma")):
+        fn = getattr(handle, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]
+        assert fn(buf.data_ptr(), cap, count.data_ptr()) == 0, name
+    eng.step()
+    torch.cuda.synchronize()
+    count.zero_()
+    torch.cuda.synchronize()
+    eng.step()
+    torch.cuda.synchronize()
+    n = min(int(count.item()), cap)
+    rec = buf[: 4 * n].view(n, 4).cpu().numpy()
+    stop(eng, reqs)
+    kern = (rec[:, 0] >> 48) & 0xFFFF
+    t0, t1, t2 = rec[:, 1], rec[:, 2], rec[:, 3]
+    # a launch's CTAs all leave their wait after the launch before has ended: runs of one kernel in the order of the waits
+    launches = []
+    for i in np.argsort(t1, kind="stable"):
+        if not launches or launches[-1][0] != int(kern[i]):
+            launches.append((int(kern[i]), []))
+        launches[-1][1].append(i)
+    base = int(t0.min())
+    rows, prev_end = [], None
+    for k, idx in launches:
+        idx = np.array(idx)
+        wait, end = int(t1[idx].min()), int(t2[idx].max())
+        rows.append({"kernel": TIMELINE_KERNELS.get(k, str(k)), "ctas": len(idx), "wait_us": (wait - base) / 1e3,
+                     "busy_us": (end - wait) / 1e3, "gap_us": (wait - prev_end) / 1e3 if prev_end is not None else 0.0,
+                     "early_us": (wait - int(t0[idx].min())) / 1e3, "end_spread_us": (end - int(t2[idx].min())) / 1e3})
+        prev_end = end
+    print(f"batch {B}, context {ctx}, {n_layers} layers: {n} CTAs in {len(rows)} launches of the marked kernels, "
+          f"{(int(t2.max()) - base) / 1e3:.1f} us from the first start to the last end")
+    mid = len(rows) // 2
+    per_layer = max(1, len(rows) // n_layers)
+    print("one layer from the middle of the step:")
+    print(f"  {'kernel':<30} {'CTAs':>5} {'wait at':>9} {'wait->end':>9} {'gap before':>10} {'resident before wait':>20} {'spread of ends':>14}")
+    for r in rows[mid:mid + per_layer]:
+        print(f"  {r['kernel']:<30} {r['ctas']:5d} {r['wait_us']:9.2f} {r['busy_us']:9.2f} {r['gap_us']:10.2f} {r['early_us']:20.2f} {r['end_spread_us']:14.2f}")
+    print("means over the step's launches (us):")
+    names = []
+    for r in rows:
+        if r["kernel"] not in names:
+            names.append(r["kernel"])
+    for name in names:
+        sel = [r for r in rows if r["kernel"] == name]
+        mean = lambda key: sum(r[key] for r in sel) / len(sel)
+        print(f"  {name:<30} x{len(sel):<4d} wait->end {mean('busy_us'):6.2f}  gap before {mean('gap_us'):6.2f}  "
+              f"resident before wait {mean('early_us'):6.2f}  spread of ends {mean('end_spread_us'):5.2f}")
+    return 0
+
+
 def run_ours(args):
     peaks, peak_src = read_peaks()
     cfgd = dict(MODEL)
@@ -600,7 +686,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
@@ -621,6 +707,8 @@ def main():
         args.warmup = 3
     if args.workload:
         return run_workload(args)
+    if args.only == "timeline":
+        return run_timeline(args)
     return run_ours(args)
 
 

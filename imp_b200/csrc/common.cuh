@@ -73,6 +73,51 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 #endif
 }
 
+// ---- timeline of a step (diagnostic build only) ---------------------------------------------------
+// -DIMP_TIMELINE: thread 0 of every CTA of the kernels that carry the three marks below records the global timer
+// at its start, after its wait for the kernel before it, and at its end, with the SM it ran on.  A file that uses the
+// marks says IMP_TL_DEFINE(name) once: that makes its record buffer and the setter imp_tl_set_<name>(records, capacity,
+// counter).  A record is four 64-bit words: kernel << 48 | sm << 32 | CTA, then the three times in ns.  Without the
+// flag (every product build) the marks are empty.
+#ifdef IMP_TIMELINE
+struct ImpTl { unsigned long long* buf; unsigned cap; unsigned* count; };
+__device__ __forceinline__ unsigned long long imp_tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define IMP_TL_DEFINE(name)                                                                                       \
+    static __device__ ImpTl g_imp_tl;                                                                             \
+    IMP_API int imp_tl_set_##name(void* buf, unsigned cap, void* count) {                                         \
+        ImpTl h{(unsigned long long*)buf, cap, (unsigned*)count};                                                 \
+        return (int)cudaMemcpyToSymbol(g_imp_tl, &h, sizeof h);                                                   \
+    }
+#define IMP_TL_BEGIN(kernel_id)                                                                                   \
+    const bool tl_on = threadIdx.x == 0 && threadIdx.y == 0 && g_imp_tl.buf != nullptr;                           \
+    const int tl_kernel = (kernel_id);                                                                            \
+    unsigned long long tl_t0 = 0, tl_t1 = 0;                                                                      \
+    if (tl_on) tl_t0 = tl_t1 = imp_tl_now();
+#define IMP_TL_WAITED() if (tl_on) tl_t1 = imp_tl_now();
+#define IMP_TL_END()                                                                                              \
+    if (tl_on) {                                                                                                  \
+        const unsigned long long t2 = imp_tl_now();                                                               \
+        const unsigned i = atomicAdd(g_imp_tl.count, 1u);                                                         \
+        if (i < g_imp_tl.cap) {                                                                                   \
+            unsigned sm;                                                                                          \
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));                                                       \
+            const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                  \
+            unsigned long long* r = g_imp_tl.buf + 4ull * i;                                                      \
+            r[0] = ((unsigned long long)tl_kernel << 48) | ((unsigned long long)sm << 32) | cta;                  \
+            r[1] = tl_t0; r[2] = tl_t1; r[3] = t2;                                                                \
+        }                                                                                                         \
+    }
+#else
+#define IMP_TL_DEFINE(name)
+#define IMP_TL_BEGIN(kernel_id)
+#define IMP_TL_WAITED()
+#define IMP_TL_END()
+#endif
+
 // 1 unless the environment variable IMP_B200_NO_PDL is set (read once).
 int imp_pdl_enabled();
 

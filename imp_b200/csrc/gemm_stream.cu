@@ -20,6 +20,8 @@
 
 #include <cstdlib>
 
+IMP_TL_DEFINE(gemm_stream)
+
 constexpr int GS_WARPS = 4;
 constexpr int GS_KB = 64;                          // elements of K per warp and stage
 constexpr int GS_STAGE_K = GS_KB * GS_WARPS;       // 256 elements of K per stage
@@ -55,6 +57,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __r
                                                                     const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                     const __nv_bfloat16* __restrict__ W, int64_t ldw,
                                                                     int M, int N, int K) {
+    IMP_TL_BEGIN(5)
     extern __shared__ __align__(128) unsigned char gs_smem[];
     constexpr int STAGE_BYTES = gs_stage_bytes(NT, RG);
     constexpr int THREADS = GS_WARPS * 32 * RG, ROWS = 16 * RG, W_BYTES = gs_w_bytes(RG);
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __r
         q_issue = q0; i_tile = t0; i_stage = s0;
     }
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -193,6 +197,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __r
         // `red` is written again only after the next tile's steps, each of which passes a barrier
     }
     gs_wait_group<0>();
+    IMP_TL_END()
 }
 
 template <int NT, typename TO, bool SWIGLU, int STAGES, int RG>

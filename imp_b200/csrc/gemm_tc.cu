@@ -25,6 +25,8 @@
 
 #include <cstdlib>
 
+IMP_TL_DEFINE(gemm_tc)
+
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4, TC_UMMA_K = 16;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;   // 32 KiB
@@ -818,6 +820,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
                                                               int kb_per_split, int tile_rows, int* status,
                                                               uint32_t wait_limit, int skip_kb) {
     constexpr int TCS_STAGES = tcs_stages<BN>();
+    IMP_TL_BEGIN(10 + EPI)
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = tcs_stage_bytes<BN>();
@@ -865,6 +868,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
             tma_load_2d(smem_u32(tiles + i * STAGE), &map_w, (kb_lo + i) * TC_BK, n0, full0 + 8 * i);
         }
         pdl_wait();
+        IMP_TL_WAITED()
         for (int i = 0; i < early; ++i)
             tma_load_2d(smem_u32(tiles + i * STAGE) + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, 0, full0 + 8 * i);
         issued = early;
@@ -955,22 +959,34 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
         tc_fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
     }
+    IMP_TL_END()
 }
 
 // out[m, n] = sum over splits of part[s, m, n], in split order.
 template <typename TO>
 __global__ void gemm_tc_reduce_kernel(TO* __restrict__ out, int64_t ldc, const float* __restrict__ part, int64_t split_stride,
                                       int M, int N, int splits) {
+    IMP_TL_BEGIN(2)
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
     const int64_t total = (int64_t)M * N;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / N;
         const int n = (int)(i - m * N);
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += part[s * split_stride + i];
+        for (int s0 = 0; s0 < splits; s0 += 8) {      // eight parts requested together, added in split order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < splits) v[j] = part[(s0 + j) * split_stride + i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < splits) acc += v[j];
+        }
         out[m * ldc + n] = from_float<TO>(acc);
     }
+    IMP_TL_END()
 }
 
 // The same sums (each element in split order) four columns at a time, for the partial products of many rows.

@@ -8,7 +8,14 @@ namespace imp {
 
 namespace {
 constexpr int SMALL_M_MAX = 16;     // most rows the weight-streaming kernel takes
-constexpr int STREAM_M_MAX = 7;     // rows up to which it is the first choice (from 8 rows the tcgen05 swap-AB kernel wins)
+// Rows up to which it is the first choice; IMP_B200_STREAM_ROWS moves it.  Whole decode steps of the 8B shape measured
+// with both kernels: one row 3.39 ms against 3.47 with the tcgen05 swap-AB kernel, two rows 3.55 / 3.53, four 3.76 / 3.72,
+// six 4.03 / 3.91, seven 4.06 / 4.00.
+static int stream_m_max() {
+    static const int v = [] { const std::string e = env_string("IMP_B200_STREAM_ROWS", ""); return e.empty() ? 1 : std::atoi(e.c_str()); }();
+    return v;
+}
+#define STREAM_M_MAX stream_m_max()
 constexpr int TC_SWAP_MAX_M = 128;  // rows up to which the weights take the M side of the tcgen05 product
 
 // "tcgen05": this library's TMA + tcgen05 kernels.  "cublas": the library GEMM for products of more than 16

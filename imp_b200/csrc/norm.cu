@@ -11,6 +11,8 @@
 // a row does not depend on the batch it is in.
 #include "common.cuh"
 
+IMP_TL_DEFINE(norm)
+
 constexpr int NORM_BLOCK = 256;
 
 // h: [n_rows_total, d] 32-bit residual stream.
@@ -83,7 +85,9 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
                                                                      float weight_offset, int write_h,
                                                                      const float* __restrict__ part, int64_t split_stride,
                                                                      int n_splits) {
+    IMP_TL_BEGIN(6)
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -91,11 +95,14 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
     float* hrow = h + src * d;
     const TA* brow = (SPLIT || branch) ? branch + src * d : nullptr;   // with SPLIT only its null-ness is used
     const int nv = d >> 2;
-    float4 v[NV];
+    float4 v[NV], wv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * NORM_BLOCK;
-        if (c < nv) v[i] = Vec4<float>::load(hrow + 4 * c);
+        if (c < nv) {
+            v[i] = Vec4<float>::load(hrow + 4 * c);
+            wv[i] = Vec4<TW>::load(w + 4 * c);     // with the row, not after the sum: one trip to the L2 less on the way
+        }
     }
     if (SPLIT) {
         const float* prow = part + src * d;
@@ -104,9 +111,15 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
             const int c = threadIdx.x + i * NORM_BLOCK;
             if (c < nv) {
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int s = 0; s < n_splits; ++s) {
-                    const float4 b = Vec4<float>::load(prow + s * split_stride + 4 * c);
-                    acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+                constexpr int NB = 8;                 // parts requested together, added in split order
+                for (int s0 = 0; s0 < n_splits; s0 += NB) {
+                    float4 b[NB];
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+                        if (s0 + j < n_splits) b[j] = Vec4<float>::load(prow + (s0 + j) * split_stride + 4 * c);
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+                        if (s0 + j < n_splits) { acc.x += b[j].x; acc.y += b[j].y; acc.z += b[j].z; acc.w += b[j].w; }
                 }
                 v[i].x += to_float(from_float<TA>(acc.x));
                 v[i].y += to_float(from_float<TA>(acc.y));
@@ -143,15 +156,15 @@ __global__ void __launch_bounds__(NORM_BLOCK) add_rmsnorm_vec_kernel(float* __re
     for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * NORM_BLOCK;
         if (c < nv) {
-            const float4 wv = Vec4<TW>::load(w + 4 * c);     // the weight row stays in the caches: read when used
             float4 o;
-            o.x = v[i].x * inv * (wv.x + weight_offset);
-            o.y = v[i].y * inv * (wv.y + weight_offset);
-            o.z = v[i].z * inv * (wv.z + weight_offset);
-            o.w = v[i].w * inv * (wv.w + weight_offset);
+            o.x = v[i].x * inv * (wv[i].x + weight_offset);
+            o.y = v[i].y * inv * (wv[i].y + weight_offset);
+            o.z = v[i].z * inv * (wv[i].z + weight_offset);
+            o.w = v[i].w * inv * (wv[i].w + weight_offset);
             Vec4<TA>::store(orow + 4 * c, o);
         }
     }
+    IMP_TL_END()
 }
 
 IMP_API int imp_add_rmsnorm(float* h, const void* branch, const void* w, void* out, const int* rows,
@@ -214,7 +227,9 @@ __global__ void __launch_bounds__(CN_THREADS) add_rmsnorm_split_cluster_kernel(
     const int C = gridDim.x;
     // first half of "every CTA of the cluster is running"; the wait stands before the first remote store
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    IMP_TL_BEGIN(4)
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
     const int r = blockIdx.y;
     const int64_t src = rows ? rows[r] : r;
@@ -231,18 +246,17 @@ __global__ void __launch_bounds__(CN_THREADS) add_rmsnorm_split_cluster_kernel(
             wv[i] = Vec4<TW>::load(w + 4 * c);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             const float* p = prow + 4 * c;
-            int sp = 0;
-            for (; sp + 4 <= n_splits; sp += 4) {      // four rows requested together, added in split order
-                const float4 b0 = Vec4<float>::load(p + (sp + 0) * split_stride), b1 = Vec4<float>::load(p + (sp + 1) * split_stride);
-                const float4 b2 = Vec4<float>::load(p + (sp + 2) * split_stride), b3 = Vec4<float>::load(p + (sp + 3) * split_stride);
-                acc.x += b0.x; acc.y += b0.y; acc.z += b0.z; acc.w += b0.w;
-                acc.x += b1.x; acc.y += b1.y; acc.z += b1.z; acc.w += b1.w;
-                acc.x += b2.x; acc.y += b2.y; acc.z += b2.z; acc.w += b2.w;
-                acc.x += b3.x; acc.y += b3.y; acc.z += b3.z; acc.w += b3.w;
-            }
-            for (; sp < n_splits; ++sp) {
-                const float4 b = Vec4<float>::load(p + sp * split_stride);
-                acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            // up to twelve partial rows requested together (one trip to the L2 for the usual 6 to 9 splits), added in
+            // split order
+            constexpr int NB = 12;
+            for (int sp0 = 0; sp0 < n_splits; sp0 += NB) {
+                float4 b[NB];
+#pragma unroll
+                for (int j = 0; j < NB; ++j)
+                    if (sp0 + j < n_splits) b[j] = Vec4<float>::load(p + (sp0 + j) * split_stride);
+#pragma unroll
+                for (int j = 0; j < NB; ++j)
+                    if (sp0 + j < n_splits) { acc.x += b[j].x; acc.y += b[j].y; acc.z += b[j].z; acc.w += b[j].w; }
             }
             v[i].x += to_float(from_float<TA>(acc.x));
             v[i].y += to_float(from_float<TA>(acc.y));
@@ -281,6 +295,7 @@ __global__ void __launch_bounds__(CN_THREADS) add_rmsnorm_split_cluster_kernel(
             Vec4<TA>::store(orow + 4 * c, o);
         }
     }
+    IMP_TL_END()
 }
 
 template <typename TA, typename TW>

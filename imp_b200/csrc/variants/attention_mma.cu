@@ -27,6 +27,8 @@
 
 #include <cstdlib>
 
+IMP_TL_DEFINE(attention_mma)
+
 #ifndef IMP_ATTN_DH
 #error "compile with -DIMP_ATTN_DH=<head size>"
 #endif
@@ -626,7 +628,9 @@ constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t out_stride,
                                                          const float* __restrict__ part_o,
                                                          const float* __restrict__ part_ml, int Hq, int n_splits) {
+    IMP_TL_BEGIN(7)
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
     __shared__ float w_s[MERGE_MAX_SPLITS];
     __shared__ float inv_s;
@@ -673,6 +677,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restri
         for (; s < n_splits; ++s) acc += po[(int64_t)s * DH + d] * w_s[s];
         o[d] = __float2bfloat16_rn(acc * inv);
     }
+    IMP_TL_END()
 }
 
 static int check_common(const void* out, const void* q, const void* kc, const void* vc, const int* bt,
@@ -957,6 +962,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     // merge their results in the first CTA's shared memory: no partial results in global memory, no merge kernel.
     // pdl_wait() comes later: the batch arrays and the keys before this step's position do not depend on the
     // kernel before this one, so the first stages are requested while it still runs.
+    IMP_TL_BEGIN(3)
     extern __shared__ __align__(128) unsigned char dt_smem[];
     __shared__ __align__(8) uint64_t dt_bars[2 * DT_STAGES];     // [0,S) full, [S,2S) empty
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1068,6 +1074,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     } else {
         // -------------------------------------------------------------------- consumers
         pdl_wait();
+        IMP_TL_WAITED()
         RowInfo rows[2];
         const __nv_bfloat16* qrow[2];
 #pragma unroll
@@ -1179,7 +1186,10 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         }
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (warp != 0 || split != 0) return;
+        if (warp != 0 || split != 0) {
+            IMP_TL_END()
+            return;
+        }
         for (int w = 1; w < n_splits; ++w) {
             const float* src = xch + (size_t)(w - 1) * PER_WARP * 32;
 #pragma unroll
@@ -1226,6 +1236,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
             }
         }
     }
+    IMP_TL_END()
 }
 
 // Most key splits that merge inside a cluster.  Measured on the whole decode step (8B shape, context 4096): two

@@ -1034,8 +1034,8 @@ def test_linear_defers_only_when_asked_and_only_split_products(K):
     assert isinstance(got, K.SplitSum) and torch.equal(got.summed(), out)
     big = rnd(32000, 4096, dtype=torch.bfloat16, seed=70).to(DEV)       # enough weight-row tiles: no split, a tensor
     assert isinstance(K.linear(torch.empty(8, 32000, dtype=torch.bfloat16, device=DEV), a, big, may_defer=True), torch.Tensor)
-    a2 = a[:2]                                                          # two rows: the weight-streaming kernel
-    assert isinstance(K.linear(torch.empty(2, 4096, dtype=torch.bfloat16, device=DEV), a2, w, may_defer=True), torch.Tensor)
+    a1 = a[:1]                                                          # one row: the weight-streaming kernel
+    assert isinstance(K.linear(torch.empty(1, 4096, dtype=torch.bfloat16, device=DEV), a1, w, may_defer=True), torch.Tensor)
 
 
 # ------------------------------------------------------------------ decode attention from the raw q,k,v rows
