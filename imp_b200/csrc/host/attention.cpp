@@ -183,6 +183,8 @@ std::vector<TilingSpec> attention_tilings() {
 constexpr double B200_SMS = 148.0;   // the part the model's constant was fitted on
 
 int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count) {
+    static const int forced = [] { const std::string e = env_string("IMP_B200_DECODE_SPLITS", ""); return e.empty() ? 0 : std::atoi(e.c_str()); }();
+    if (forced > 0) return std::min(forced, DECODE_MAX_SPLITS);    // for measurements
     const int sms = sm_count > 0 ? sm_count : std::max(1, imp_device_sm_count());
     const int base = std::max(1, n_tokens * n_kv_heads * ((group + 15) / 16));
     if (page_size % 16) return std::max(1, std::min(DECODE_MAX_SPLITS, sms * 3 / base));

@@ -660,21 +660,30 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restri
         }
         if (lane == 0) inv_s = L > 0.f ? 1.f / L : 0.f;
     }
+    // The partial outputs do not depend on the weights: every thread asks for its dimension of the first 32 splits
+    // before the barrier, so that they arrive while warp 0 works; further chunks (and dimensions) follow in the loop.
+    constexpr int MB = 32;
+    float v[MB];
+    if (threadIdx.x < DH) {
+#pragma unroll
+        for (int j = 0; j < MB; ++j)
+            if (j < n_splits) v[j] = po[(int64_t)j * DH + threadIdx.x];
+    }
     __syncthreads();
     const float inv = inv_s;
     __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
     for (int d = threadIdx.x; d < DH; d += 128) {
         float acc = 0.f;
-        int s = 0;
-        for (; s + 4 <= n_splits; s += 4) {
-            const float a0 = po[(int64_t)s * DH + d], a1 = po[(int64_t)(s + 1) * DH + d];
-            const float a2 = po[(int64_t)(s + 2) * DH + d], a3 = po[(int64_t)(s + 3) * DH + d];
-            acc += a0 * w_s[s];
-            acc += a1 * w_s[s + 1];
-            acc += a2 * w_s[s + 2];
-            acc += a3 * w_s[s + 3];
+        for (int s0 = 0; s0 < n_splits; s0 += MB) {          // split order
+            if (s0 > 0 || d != (int)threadIdx.x) {
+#pragma unroll
+                for (int j = 0; j < MB; ++j)
+                    if (s0 + j < n_splits) v[j] = po[(int64_t)(s0 + j) * DH + d];
+            }
+#pragma unroll
+            for (int j = 0; j < MB; ++j)
+                if (s0 + j < n_splits) acc += v[j] * w_s[s0 + j];
         }
-        for (; s < n_splits; ++s) acc += po[(int64_t)s * DH + d] * w_s[s];
         o[d] = __float2bfloat16_rn(acc * inv);
     }
     IMP_TL_END()
@@ -1242,7 +1251,10 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
 // Most key splits that merge inside a cluster.  Measured on the whole decode step (8B shape, context 4096): two
 // splits (16 sequences) 4.74 against 4.87 ms with the merge kernel, four (8 sequences) 3.97 against 3.98, eight
 // (4 sequences) 3.81 against 3.76: larger clusters wait longer for their slowest member than the kernel saves.
-constexpr int DT_CLUSTER_MAX = 4;
+#ifndef IMP_DT_CLUSTER_MAX
+#define IMP_DT_CLUSTER_MAX 4
+#endif
+constexpr int DT_CLUSTER_MAX = IMP_DT_CLUSTER_MAX;
 
 // *merged is set when the key splits merged inside the kernel (a cluster per (token, kv head)): no merge kernel then.
 template <int NR>
