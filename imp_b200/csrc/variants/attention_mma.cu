@@ -907,12 +907,18 @@ __device__ __forceinline__ void dec_q_norm_rope(uint32_t (&qa)[KSTEPS][4], const
     }
 }
 
-// The token's own key and value: k normalised and rotated, both written to row `pos` of their page and to the
-// rows `ksm_row` / `vsm_row` of this warp's copy of the page in shared memory.  One warp; lane l holds the pairs
-// (2l, 2l+1) of both rotary halves (and the next 64 dimensions for head sizes above 128), as the rotary kernel does.
-__device__ __forceinline__ void dec_write_own_key(const DecFused& fz, const __nv_bfloat16* __restrict__ kraw,
-                                                  const __nv_bfloat16* __restrict__ vraw, int64_t page_row_off, int pos,
-                                                  unsigned char* ksm_row, unsigned char* vsm_row, int lane) {
+// The token's own key and value: k normalised and rotated, both written to row `pos` of their page at once (dec_make_own_key,
+// before the warp's loop over the stages, so that the trip for the raw rows runs beside the one for q) and, once the
+// stage that holds the row has landed, to the rows `ksm_row` / `vsm_row` of this warp's copy of the page in shared memory
+// (dec_patch_own_key; the producer fetched that row as it was).  One warp; lane l holds the pairs (2l, 2l+1) of both rotary
+// halves (and the next 64 dimensions for head sizes above 128), as the rotary kernel does.
+struct OwnKey {
+    uint32_t lo[2], hi[2];     // rotated key: first and second half of the head, pairs lane and lane + 32
+    uint2 v[2];                // value: dimensions 4 lane .. 4 lane + 3, and the same 128 further on
+};
+
+__device__ __forceinline__ void dec_make_own_key(OwnKey& own, const DecFused& fz, const __nv_bfloat16* __restrict__ kraw,
+                                                 const __nv_bfloat16* __restrict__ vraw, int64_t page_row_off, int pos, int lane) {
     constexpr int HALF = DH / 2;
     const float* cs = fz.cos_tab + (int64_t)pos * HALF;
     const float* sn = fz.sin_tab + (int64_t)pos * HALF;
@@ -929,6 +935,11 @@ __device__ __forceinline__ void dec_write_own_key(const DecFused& fz, const __nv
         }
     }
 #pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int i = lane * 4 + 128 * r;
+        own.v[r] = i < DH ? *reinterpret_cast<const uint2*>(vraw + i) : make_uint2(0u, 0u);
+    }
+#pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float inv = fz.k_norm_w ? rsqrtf(ss / (float)DH + fz.eps) : 1.f;
     __nv_bfloat16* kdst = fz.k_pages + page_row_off;
@@ -936,6 +947,7 @@ __device__ __forceinline__ void dec_write_own_key(const DecFused& fz, const __nv
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int j = lane + 32 * r;
+        own.lo[r] = own.hi[r] = 0u;
         if (2 * j >= HALF) continue;
         float2 av = make_float2(a[r].x * inv, a[r].y * inv), bv = make_float2(b[r].x * inv, b[r].y * inv);
         if (fz.k_norm_w) {
@@ -943,17 +955,29 @@ __device__ __forceinline__ void dec_write_own_key(const DecFused& fz, const __nv
             bv.x *= fz.k_norm_w[2 * j + HALF]; bv.y *= fz.k_norm_w[2 * j + 1 + HALF];
         }
         const float2 c = *reinterpret_cast<const float2*>(cs + 2 * j), sv = *reinterpret_cast<const float2*>(sn + 2 * j);
-        const uint32_t lo = pack_bf16(av.x * c.x - bv.x * sv.x, av.y * c.y - bv.y * sv.y);
-        const uint32_t hi = pack_bf16(av.x * sv.x + bv.x * c.x, av.y * sv.y + bv.y * c.y);
-        reinterpret_cast<uint32_t*>(ksm_row)[j] = lo;
-        reinterpret_cast<uint32_t*>(ksm_row + HALF * 2)[j] = hi;
-        reinterpret_cast<uint32_t*>(kdst)[j] = lo;
-        reinterpret_cast<uint32_t*>(kdst + HALF)[j] = hi;
+        own.lo[r] = pack_bf16(av.x * c.x - bv.x * sv.x, av.y * c.y - bv.y * sv.y);
+        own.hi[r] = pack_bf16(av.x * sv.x + bv.x * c.x, av.y * sv.y + bv.y * c.y);
+        reinterpret_cast<uint32_t*>(kdst)[j] = own.lo[r];
+        reinterpret_cast<uint32_t*>(kdst + HALF)[j] = own.hi[r];
     }
-    for (int i = lane * 4; i < DH; i += 128) {
-        const uint2 v = *reinterpret_cast<const uint2*>(vraw + i);
-        *reinterpret_cast<uint2*>(vsm_row + 2 * i) = v;
-        *reinterpret_cast<uint2*>(vdst + i) = v;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int i = lane * 4 + 128 * r;
+        if (i < DH) *reinterpret_cast<uint2*>(vdst + i) = own.v[r];
+    }
+}
+
+__device__ __forceinline__ void dec_patch_own_key(const OwnKey& own, unsigned char* ksm_row, unsigned char* vsm_row, int lane) {
+    constexpr int HALF = DH / 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int j = lane + 32 * r;
+        if (2 * j < HALF) {
+            reinterpret_cast<uint32_t*>(ksm_row)[j] = own.lo[r];
+            reinterpret_cast<uint32_t*>(ksm_row + HALF * 2)[j] = own.hi[r];
+        }
+        const int i = lane * 4 + 128 * r;
+        if (i < DH) *reinterpret_cast<uint2*>(vsm_row + 2 * i) = own.v[r];
     }
     // the slot is refilled by a bulk copy later: order these ordinary stores before it
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1099,23 +1123,32 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         if constexpr (DH % 64 == 0) {
             if (fz.qkv) dec_q_norm_rope<NR>(qa, fz, pos, t4);
         }
+        // The warp whose 16 keys include the token's own makes that key and value now and writes them to their page
+        // (the raw rows travel beside q); the stage's copy in shared memory is patched when it has landed.
+        OwnKey own;
+        int own_stage = -1;
+        if constexpr (DH % 64 == 0) {
+            const int s_own = (pos - first_al) / DT_KEYS;
+            if (fz.qkv && s_own >= stage_lo && s_own < stage_hi && ((pos - first_al) % DT_KEYS) / 16 == warp) {
+                const int page = bt[pos / P];
+                if (page >= 0 && page < num_pages) {     // else the producer reports it
+                    const __nv_bfloat16* kraw = fz.qkv + (int64_t)tok * fz.stride + (int64_t)(Hq + hk) * DH;
+                    dec_make_own_key(own, fz, kraw, kraw + (int64_t)Hkv * DH, (((int64_t)page * Hkv + hk) * P + (pos % P)) * DH,
+                                     pos, lane);
+                    own_stage = s_own;
+                }
+            }
+        }
         for (int s = stage_lo; s < stage_hi; ++s) {
             const int it = s - stage_lo, slot = it % DT_STAGES;
             const bool ok = __all_sync(0xffffffffu, dt_wait(full0 + 8 * slot, (uint32_t)(it / DT_STAGES) & 1u, status));
             if (!ok) break;
             const int j0 = first_al + DT_KEYS * s + 16 * warp;
             if constexpr (DH % 64 == 0) {
-                if (fz.qkv && pos >= j0 && pos < j0 + 16) {
-                    // this warp's 16 keys include the token's own: its key and value are made here
-                    const int page = bt[pos / P];
-                    if (page >= 0 && page < num_pages) {     // else the producer has reported it already
-                        unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
-                        const __nv_bfloat16* kraw = fz.qkv + (int64_t)tok * fz.stride + (int64_t)(Hq + hk) * DH;
-                        dec_write_own_key(fz, kraw, kraw + (int64_t)Hkv * DH,
-                                          (((int64_t)page * Hkv + hk) * P + (pos % P)) * DH, pos,
-                                          sb + warp * DT_RUN_BYTES + (pos - j0) * DH * 2,
-                                          sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES + (pos - j0) * DH * 2, lane);
-                    }
+                if (s == own_stage) {
+                    unsigned char* sb = dt_smem + slot * DT_STAGE_BYTES;
+                    dec_patch_own_key(own, sb + warp * DT_RUN_BYTES + (pos - j0) * DH * 2,
+                                      sb + (DT_CONSUMERS + warp) * DT_RUN_BYTES + (pos - j0) * DH * 2, lane);
                 }
             }
             if (j0 <= pos && j0 + 15 >= first) {
