@@ -711,10 +711,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
             void* Cz = EPI == TC_OUT_F32 ? (void*)(reinterpret_cast<float*>(Cv) + (int64_t)z * split_stride) : Cv;
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC2_BN;
+            // TMA stores only for a CTA's 128 rows that all lie inside C (and whole 64-column pieces): a store that the
+            // tensor map clips measured far slower than the threads' own stores (2048 x 24576 outputs cut at 320 rows:
+            // 97 us against 78), so the last, partly filled row block of a matrix takes the plain path.
+            const bool whole = m0 + 128 <= M && n0 + TC2_BN <= N;
             if (EPI == TC_OUT_QKV_ROPE) {
-                const QkvStage stg{tma_store ? out_stage : nullptr, &map_c, storer, quarter * 32 + lane, m0};
+                const QkvStage stg{tma_store && m0 + 128 <= M ? out_stage : nullptr, &map_c, storer, quarter * 32 + lane, m0};
                 qkv_rope_row(qkv, taddr, row, n0, N, row < M, status, stg);
-            } else if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store) {
+            } else if ((EPI == TC_OUT_BF16 || EPI == TC_OUT_SWIGLU_BF16) && tma_store && whole) {
                 constexpr int SUBS = EPI == TC_OUT_SWIGLU_BF16 ? 2 : 4;     // sub-tiles of 64 output columns
                 const int x0 = EPI == TC_OUT_SWIGLU_BF16 ? n0 >> 1 : n0;
                 const int r = quarter * 32 + lane;                          // row in the CTA's half of the tile
@@ -962,6 +966,168 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     IMP_TL_END()
 }
 
+// ---- few rows on CTA pairs (33 to 128 activation rows) ---------------------------------------------------
+// From 33 rows on, a CTA of the kernel above reads nearly as many bytes of activations as of weights (64 rows: 8 KiB beside
+// 12 to 16 KiB a K block; 128 rows: 16 KiB), all CTAs the same ones through the L2, and the product is bound by what the
+// L2 can hand to the SMs, not by the memory (gate/up of the 8B shape: 42 us at 64 rows, 73 us at 128, against 35 at 8).
+// Here the two CTAs of a cluster take neighbouring tiles of weight rows and share one MMA (cta_group::2, M = 256: each
+// CTA's 128 accumulator lanes are its own weight rows, all BN tokens wide); each loads its own weight rows and HALF of
+// the activation tile, which the MMA reads from both.  Stages of 16 KiB + BN / 2 rows of activations, two CTAs an SM.
+// Barriers as in gemm_tc_pair_kernel: `full` lives in the even CTA and counts both CTAs' copies, `empty` and the
+// accumulator barrier exist in both and get their arrivals from multicast commits.
+template <int BN> constexpr int tcsp_stages() { return BN <= 64 ? 5 : 4; }
+template <int BN> constexpr int tcsp_stage_bytes() { return TCS_W_BYTES + (BN / 2) * TC_BK * 2; }
+template <int BN> constexpr int tcsp_smem_bytes() { return tcsp_stages<BN>() * tcsp_stage_bytes<BN>() + 1024 + 256; }
+
+template <int BN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+    gemm_tc_swap_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                             void* __restrict__ Cv, int64_t ldc, int64_t split_stride, int M, int N, int K, int kb_per_split,
+                             int tile_rows, int* status) {
+    constexpr int STAGES = tcsp_stages<BN>();
+    constexpr int STAGE = tcsp_stage_bytes<BN>();
+    IMP_TL_BEGIN(13 + EPI)
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                    // == blockIdx.x & 1
+    const int n0 = blockIdx.x * tile_rows;                   // this CTA's weight rows (may lie past N in the last pair)
+    const uint32_t stage_tx = (uint32_t)(tile_rows + BN / 2) * (TC_BK * 2);   // bytes this CTA's two boxes bring
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_lo = blockIdx.z * kb_per_split;
+    const int kb_hi = min(total_kb, kb_lo + kb_per_split);
+    const int k_blocks = max(kb_hi - kb_lo, 0);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum_bar = smem_u32(bars + 2 * STAGES);
+
+    // Nothing before pdl_wait() reads or writes what an earlier kernel of the stream may still be working on.
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs, the same slot offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();        // the partner's barriers are initialised before anything can arrive on them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------- producer (one per CTA, for its own boxes)
+        int issued = 0;
+        bool ok = true;
+        const int early = k_blocks < STAGES ? k_blocks : STAGES;
+        for (int i = 0; i < early; ++i) {     // weights do not depend on the kernel before this one
+            if (rank == 0) mbar_expect_tx(full0 + 8 * i, 2 * stage_tx);            // both CTAs' copies
+            tma_load_2d_pair(smem_u32(tiles + i * STAGE), &map_w, (kb_lo + i) * TC_BK, n0, cluster_map(full0 + 8 * i, 0));
+        }
+        pdl_wait();
+        IMP_TL_WAITED()
+        for (int i = 0; i < early; ++i)
+            tma_load_2d_pair(smem_u32(tiles + i * STAGE) + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, (int)rank * (BN / 2),
+                             cluster_map(full0 + 8 * i, 0));
+        issued = early;
+        for (int i = early; i < k_blocks; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / STAGES) & 1u) ^ 1u, status);
+            if (!ok) break;
+            const uint32_t w_dst = smem_u32(tiles + s * STAGE), full_even = cluster_map(full0 + 8 * s, 0);
+            if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * stage_tx);
+            tma_load_2d_pair(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full_even);
+            tma_load_2d_pair(w_dst + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, (int)rank * (BN / 2), full_even);
+            issued = i + 1;
+        }
+        if (!ok && rank == 0)   // a bounded chance for the copies still in flight to land
+            for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+                mbar_wait(full0 + 8 * (i % STAGES), (uint32_t)(i / STAGES) & 1u, nullptr);
+    } else {
+        pdl_wait();
+    }
+    if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------------------------------------------------------- MMA issuer (even CTA)
+        const uint32_t idesc = tc_instr_desc(256, BN);
+        bool ok = true;
+        for (int i = 0; i < k_blocks && ok; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(full0 + 8 * s, (uint32_t)(i / STAGES) & 1u, status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t w_addr = smem_u32(tiles + s * STAGE), x_addr = w_addr + TCS_W_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                tc_mma_pair(tmem_base, tc_smem_desc(w_addr + k * TC_UMMA_K * 2), tc_smem_desc(x_addr + k * TC_UMMA_K * 2), idesc,
+                            (i > 0 || k > 0) ? 1u : 0u);
+            tc_commit_pair(empty0 + 8 * s);
+        }
+        tc_commit_pair(accum_bar);     // also after a wait that gave up: the epilogues of both CTAs are released
+    }
+    __syncwarp();
+
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, status));
+    tc_fence_after_sync();
+    if (acc_ok) {
+        const int r = warp * 32 + lane;             // accumulator lane = weight row of the tile
+        const int col = n0 + r;                     // output column
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            float v[32];
+            if (k_blocks > 0) {
+                tc_ld32(lane_base + (uint32_t)(c * 32), v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;   // an empty K range contributes nothing
+            }
+            if (EPI == TC_OUT_SWIGLU_BF16) {
+                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
+                const bool is_gate = (r & 8) == 0;
+                const int ocol = (col >> 4) * 8 + (r & 7);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float up = __shfl_xor_sync(0xffffffffu, v[i], 8);   // lane r + 8 holds the matching up row
+                    const int tok = c * 32 + i;
+                    if (is_gate && tok < M && col + 8 < N && r < tile_rows)
+                        base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
+                }
+            } else if (col < N && r < tile_rows) {
+                if (EPI == TC_OUT_F32) {
+                    float* base = reinterpret_cast<float*>(Cv) + (int64_t)blockIdx.z * split_stride;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int tok = c * 32 + i;
+                        if (tok < M) base[(int64_t)tok * ldc + col] = v[i];
+                    }
+                } else {
+                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int tok = c * 32 + i;
+                        if (tok < M) base[(int64_t)tok * ldc + col] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();        // neither CTA leaves while the other may still read its memory or signal its barriers
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+    IMP_TL_END()
+}
+
 // out[m, n] = sum over splits of part[s, m, n], in split order.
 template <typename TO>
 __global__ void gemm_tc_reduce_kernel(TO* __restrict__ out, int64_t ldc, const float* __restrict__ part, int64_t split_stride,
@@ -1177,6 +1343,14 @@ IMP_API int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda
 #define TCS_MIN_KB_PER_SPLIT 6     // blocks of K a split has at least
 #endif
 static int tcs_sms() { return imp_sm_count(); }
+// From 65 rows on the few-rows product runs on CTA pairs (gemm_tc_swap_pair_kernel); IMP_B200_TCS_PAIR=0 keeps single CTAs.
+static bool tcs_pair_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("IMP_B200_TCS_PAIR"); v = e ? atoi(e) : 1; }
+    return v != 0;
+}
+// CTAs resident at once: two an SM up to 64 rows, and on CTA pairs (whose stages are smaller) up to 128.
+static int tcs_slots(int M) { return (M <= 64 || tcs_pair_enabled()) ? 2 * tcs_sms() : tcs_sms(); }
 
 // Weight rows of a CTA's tile when K is not split.  All CTAs are resident at once (two per SM up to 64 tokens),
 // handed out round robin, so the SM with the most CTAs sets the time: 192 tiles of 128 rows put two tiles on 44 SMs
@@ -1188,7 +1362,7 @@ static int tcs_tile_rows(int M, int N, int splits) {
     if (fixed >= 16 && fixed <= 128 && fixed % 16 == 0) return fixed;
     if (splits > 1) return 128;
     const int sms = tcs_sms();
-    const int slots = M <= 64 ? 2 * sms : sms;
+    const int slots = tcs_slots(M);
     int best = 128, best_load = -1;
     for (int rows = 128; rows >= 64; rows -= 16) {
         const int ctas = (N + rows - 1) / rows;
@@ -1201,8 +1375,7 @@ static int tcs_tile_rows(int M, int N, int splits) {
 
 static int tcs_splits(int M, int N, int K, int epilogue) {
     if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
-    const int sms = tcs_sms();
-    const int slots = M <= 64 ? 2 * sms : sms;          // resident CTAs: two per SM with 64-column tiles
+    const int slots = tcs_slots(M);                      // resident CTAs
     const int tiles = (N + 127) / 128;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int splits = slots / tiles;                          // as many CTAs as fit in one wave
@@ -1234,6 +1407,24 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
     return 0;
 }
 
+template <int BN, int EPI>
+static int launch_tcsp(void* C, int64_t ldc, int64_t split_stride, const CUtensorMap& mw, const CUtensorMap& mx, int M, int N,
+                       int K, int splits, int kb_per_split, int tile_rows, int* status, cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tcsp_smem_bytes<BN>());
+        if (e != cudaSuccess) { imp_set_error("gemm_tc_swap (pairs): %s", cudaGetErrorString(e)); return (int)e; }
+        attr_set = true;
+    }
+    const int tiles = (N + tile_rows - 1) / tile_rows;
+    dim3 grid(2 * ((tiles + 1) / 2), 1, splits);          // whole pairs: the last CTA of an odd count works on rows past N
+    cudaError_t e = imp_launch(gemm_tc_swap_pair_kernel<BN, EPI>, grid, dim3(128), (size_t)tcsp_smem_bytes<BN>(), s, mw, mx, C, ldc,
+                               split_stride, M, N, K, kb_per_split, tile_rows, status);
+    if (e != cudaSuccess) { imp_set_error("gemm_tc_swap (pairs): %s", cudaGetErrorString(e)); return (int)e; }
+    return 0;
+}
+
 // C = A[M,K] * W[N,K]^T for 1 <= M <= 128 with the weights on the M side of the MMA.
 // epilogue as for imp_gemm_bf16_tc.  `scratch` must hold imp_gemm_bf16_tc_swap_scratch_floats() floats.
 static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
@@ -1253,14 +1444,19 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
     if (bn32 < 0) { const char* e = getenv("IMP_B200_TCS_BN32"); bn32 = e ? atoi(e) : 1; }
     const int BN = (M <= 32 && bn32) ? 32 : (M <= 64 ? 64 : 128);
     const int tile_rows = tcs_tile_rows(M, N, splits);
+    // Pairs from 65 rows on (gate/up of the 8B shape at 128 rows: 51 us against 73); at 33 to 64 rows they measured no
+    // faster than single CTAs (42 us either way: what the halved activation traffic gains, waiting for two CTAs' copies loses).
+    const bool pair = BN == 128 && tcs_pair_enabled();       // each CTA of a pair loads half of the activation tile
     CUtensorMap mw, mx;
     if (int rc = make_map(&mw, W, N, K, ldw, tile_rows)) return rc;
-    if (int rc = make_map(&mx, A, M, K, lda, BN)) return rc;
+    if (int rc = make_map(&mx, A, M, K, lda, pair ? BN / 2 : BN)) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = 0;
     if (splits > 1) {
         const int64_t split_stride = (int64_t)M * N;
-        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
+        rc = pair ? (BN == 64 ? launch_tcsp<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
+                              : launch_tcsp<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s))
+           : BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
            : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
                       : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s);
         if (rc) return rc;
@@ -1276,6 +1472,15 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
             e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc,
                            (const float*)scratch, split_stride, M, N, splits);
         if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
+    } else if (pair) {
+        rc = epilogue == TC_OUT_BF16
+                 ? (BN == 64 ? launch_tcsp<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                             : launch_tcsp<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s))
+             : epilogue == TC_OUT_F32
+                 ? (BN == 64 ? launch_tcsp<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                             : launch_tcsp<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s))
+                 : (BN == 64 ? launch_tcsp<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                             : launch_tcsp<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s));
     } else if (epilogue == TC_OUT_BF16) {
         rc = BN == 32 ? launch_tcs<32, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
            : BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
