@@ -1234,7 +1234,9 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
             if (e2 != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e2)); pair_mode = -1; return (int)e2; }
         }
     }
-    if (mode == 0 && pair_mode == 1 && M >= 256) {
+    static int pair_min_rows = -1;   // IMP_B200_TC_PAIR_ROWS: rows from which CTA pairs take the product (default 129)
+    if (pair_min_rows < 0) { const char* e = getenv("IMP_B200_TC_PAIR_ROWS"); pair_min_rows = e ? atoi(e) : 129; }
+    if (mode == 0 && pair_mode == 1 && M >= pair_min_rows) {
         const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
         const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
         // bfloat16 outputs leave through TMA stores where C's rows allow them (16-byte strides)
