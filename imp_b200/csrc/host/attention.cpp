@@ -176,13 +176,17 @@ std::vector<TilingSpec> attention_tilings() {
 
 // The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with fewer
 // (token, kv head) pairs than such slots the keys are split until the slots are full.  With more, the
-// split count with the least modelled time is taken.  The model (fitted to measurements at 40 to 128
-// sequences on a B200): a CTA alone streams about 1/150 of what its 148 SMs can, so a wave of CTAs runs
-// at full speed from about one CTA per SM up, and a last wave of fewer runs as slowly as each of its
-// CTAs; splitting costs the merge kernel and the partial results, about a tenth of one CTA's work.
+// split count with the least modelled time is taken.  The model (fitted to whole decode steps at 36 to 112
+// sequences and contexts of 1,024 and 4,096 on a B200; it picks the fastest split count at 15 of those 16
+// points and loses 1 % at the other): a CTA alone streams about 1/150 of what its 148 SMs can, so a wave of
+// CTAs runs at full speed from about one CTA per SM up, and a last wave of fewer runs as slowly as each of
+// its CTAs; a CTA's time is its share of the keys (context / splits, in units of 4,096 keys) plus a fixed
+// part for its start, its end and the merge: 0.02 unsplit, 0.04 with two splits, 0.05 with more.  So short
+// contexts are never split (the fixed part dominates) and long ones are split wherever that fills the last wave.
+// `context`: the sequences' typical length (0: 4,096).
 constexpr double B200_SMS = 148.0;   // the part the model's constant was fitted on
 
-int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count) {
+int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count, int context) {
     static const int forced = [] { const std::string e = env_string("IMP_B200_DECODE_SPLITS", ""); return e.empty() ? 0 : std::atoi(e.c_str()); }();
     if (forced > 0) return std::min(forced, DECODE_MAX_SPLITS);    // for measurements
     const int sms = sm_count > 0 ? sm_count : std::max(1, imp_device_sm_count());
@@ -198,12 +202,13 @@ int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm
         return p;
     }
     const double saturating = sms * (150.0 / B200_SMS);   // scaled with the SMs the device has
+    const double keys = (context > 0 ? context : 4096) / 4096.0;
     int best = 1;
     double best_t = 0;
     for (int s = 1; s <= 8; ++s) {
         const int ctas = base * s, full = ctas / slots, tail = ctas % slots;
         double t = full * slots / saturating + (tail ? tail / std::min(saturating, (double)tail) : 0.0);
-        t = t / s + (s > 1 ? 0.1 + 0.01 * s : 0.0);
+        t *= (s == 1 ? 0.02 : s == 2 ? 0.04 : 0.05) + keys / s;
         if (s == 1 || t < best_t) {
             best = s;
             best_t = t;
@@ -222,7 +227,7 @@ static void decode_attention(Step& st, Tensor out, const Tensor& q, const Attent
     MmaVariant& lib = mma_variant(g.dh);
     const ImpCacheView& c = cache.view;
     const int T = (int)rows(q);
-    const int n_splits = decode_splits(T, g.hkv, g.hq / g.hkv, c.page_size, rt.sm_count);
+    const int n_splits = decode_splits(T, g.hkv, g.hq / g.hkv, c.page_size, rt.sm_count, st.context);
     const int64_t n_floats = lib.scratch_floats(T, g.hq, n_splits);
     float* scratch = n_floats ? (float*)rt.arena->alloc((size_t)n_floats * 4) : nullptr;
     check_variant(rt,
@@ -242,7 +247,7 @@ bool decode_attention_fused(Step& st, Tensor out, const Tensor& qkv, const Atten
          "fused decode attention: bfloat16 rows of q | k | v and a rotation over the whole head");
     MmaVariant& lib = mma_variant(g.dh);
     const int T = (int)rows(qkv);
-    const int n_splits = decode_splits(T, g.hkv, g.hq / g.hkv, c.page_size, rt.sm_count);
+    const int n_splits = decode_splits(T, g.hkv, g.hq / g.hkv, c.page_size, rt.sm_count, st.context);
     const int64_t n_floats = lib.scratch_floats(T, g.hq, n_splits);
     float* scratch = n_floats ? (float*)rt.arena->alloc((size_t)n_floats * 4) : nullptr;
     const int rc = lib.decode_fused(out.data, out.stride0, qkv.data, qkv.stride0, c.k_pages, c.v_pages, c.block_table, c.bt_stride,

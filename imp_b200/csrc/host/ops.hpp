@@ -80,7 +80,7 @@ void qk_norm_rope_kv_write(Step& st, Tensor qkv, const AttentionGeometry& g, con
 
 // Key splits of the decode kernel: a function of the batch size alone (a captured graph must not depend
 // on the context length).
-int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count);
+int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count, int context = 0);
 
 // Where the per-head-size attention libraries are found: a function that returns the path of the
 // library built from `source` ("attention_mma.cu" / "attention_tc.cu") for a head size, or NULL.

@@ -93,8 +93,8 @@ IMP_EXPORT int imp_op_add_rmsnorm(const ImpTensor* h, const ImpTensor* branch, c
     });
 }
 
-IMP_EXPORT int imp_op_decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count) {
-    return decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count);
+IMP_EXPORT int imp_op_decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm_count, int context) {
+    return decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count, context);
 }
 
 }  // extern "C"

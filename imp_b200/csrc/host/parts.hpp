@@ -86,6 +86,8 @@ struct Step {
     std::vector<Tiles> tiles;                  // per tiling the model declared (empty in decode-only steps)
     struct Diagnostics* diag = nullptr;        // stage timers / statistics when a debugging switch is set
     int layer = -1;                            // index of the layer that is running (for stage names)
+    int context = 0;                           // the sequences' mean length after this step, rounded to a power of two: what
+                                               // launch choices may depend on (a decode graph is kept per batch size and context)
     int T() const { return view.n_tokens; }
     int B() const { return view.n_seqs; }
     int R() const { return view.n_rows; }

@@ -120,11 +120,13 @@ Step& Stepper::prepare(const StepEntryView* entries, int B) {
     st.starts.assign((size_t)B, 0);
     st.slots.assign((size_t)B, 0);
     st.rids.assign((size_t)B, 0);
+    int64_t total_len = 0;
     for (int i = 0; i < B; ++i) {
         const auto& e = entries[i];
         st.rids[(size_t)i] = e.rid;
         st.q_lens[(size_t)i] = e.n_tokens;
         st.starts[(size_t)i] = cache_->has(e.rid) ? cache_->length(e.rid) : 0;
+        total_len += st.starts[(size_t)i] + e.n_tokens;
         if (e.tokens)
             for (int t = 0; t < e.n_tokens; ++t)
                 if (e.tokens[t] < 0 || e.tokens[t] >= vocab_)
@@ -144,6 +146,12 @@ Step& Stepper::prepare(const StepEntryView* entries, int B) {
     if (new_slots > cache_->slots().n_free())
         throw OutOfPages(std::to_string(new_slots) + " new requests but only " + std::to_string(cache_->slots().n_free()) + " free state slots");
 
+    {   // the mean length, rounded to the nearest power of two (in the logarithm)
+        const double mean = (double)total_len / B;
+        int c = 1;
+        while ((double)c * 1.41421356 < mean && c < (1 << 30)) c <<= 1;
+        st.context = c;
+    }
     for (int i = 0; i < B; ++i) {
         const int64_t rid = entries[i].rid;
         if (!cache_->has(rid)) cache_->zero_state(cache_->add_request(rid), rt_->stream);
@@ -270,10 +278,13 @@ Tensor Stepper::step(const StepEntryView* entries, int n, const int32_t* device_
 // first step of a size runs eagerly (it sizes the workspace and sets kernel attributes), the second is
 // captured.  The returned logits are the graph's own: read them before the next step.
 Tensor Stepper::forward_decode_graph(Step& st) {
-    const int B = st.B();
-    auto hit = graphs_.find(B);
+    // one graph per batch size and context class: the decode attention's key splits depend on both
+    int ctx_class = 0;
+    while ((1 << ctx_class) < st.context && ctx_class < 30) ++ctx_class;
+    const int B = st.B(), key = B * 32 + ctx_class;
+    auto hit = graphs_.find(key);
     if (hit == graphs_.end()) {
-        const int uses = graph_uses_[B]++;
+        const int uses = graph_uses_[key]++;
         if (uses == 0) {
             ++eager_steps;
             return model_->forward(st);
@@ -292,7 +303,7 @@ Tensor Stepper::forward_decode_graph(Step& st) {
             cudaStreamEndCapture(rt_->stream, &graph);
             if (graph) cudaGraphDestroy(graph);
             (void)cudaGetLastError();
-            graph_uses_[B] = 0;          // try again after an eager step has sized the workspace
+            graph_uses_[key] = 0;        // try again after an eager step has sized the workspace
             rt_->arena->begin_step(rt_->stream);
             ++eager_steps;
             return model_->forward(st);
@@ -309,7 +320,7 @@ Tensor Stepper::forward_decode_graph(Step& st) {
         if (e != cudaSuccess) fail(IMP_ERROR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
         if (gen != rt_->arena->generation()) fail(IMP_ERROR_INTERNAL, "the workspace moved during graph capture");
         ++graph_captures;
-        hit = graphs_.emplace(B, g).first;
+        hit = graphs_.emplace(key, g).first;
     }
     rt_->arena->restore(hit->second.mark);
     IMP_CUDA(cudaGraphLaunch(hit->second.exec, rt_->stream));

@@ -118,11 +118,11 @@ def _check(lib, rc: int, what: str) -> None:
         raise L.KernelError(f"{what} failed ({rc}): {lib.imp_last_error().decode(errors='replace')}")
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16, sm_count: int = 0) -> int:
-    """Key splits of the decode kernel as the library chooses them (csrc/host/attention.cpp `decode_splits`):
-    a function of the batch size alone, since a captured graph must not depend on the context length.
-    `sm_count` 0 asks the device."""
-    return int(L.load().imp_op_decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count))
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, page_size: int = 16, sm_count: int = 0, context: int = 0) -> int:
+    """Key splits of the decode kernel as the library chooses them (csrc/host/attention.cpp `decode_splits`): a function
+    of the batch size and of the sequences' typical length (`context`, 0: 4,096; the engine keeps one captured graph
+    per batch size and context class).  `sm_count` 0 asks the device."""
+    return int(L.load().imp_op_decode_splits(n_tokens, n_kv_heads, group, page_size, sm_count, context))
 
 
 def decode_attention(out, q, n_q_heads, n_kv_heads, head_dim, k_cache, v_cache, block_table, seq_of_token, positions,

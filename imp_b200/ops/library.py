@@ -85,7 +85,7 @@ _SIGNATURES.update({
     "imp_op_linear_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "imp_op_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                    c_int, c_void_p]),
-    "imp_op_decode_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "imp_op_decode_splits": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
 })
 
 # Entry points that newer sources add; declared when present so an older build still loads in tools

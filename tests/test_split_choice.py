@@ -1,4 +1,4 @@
-"""Key splits of the decode attention: chosen from the batch alone, within bounds, and as measured."""
+"""Key splits of the decode attention: chosen from the batch size and the context class, within bounds, and as measured."""
 from functools import partial
 
 from imp_b200.ops.attention import DECODE_MAX_SPLITS
@@ -42,3 +42,18 @@ def test_the_rule_scales_with_the_number_of_sms():
             if base <= slots:
                 assert base * s <= slots and (base * s * 2 > slots or s == DECODE_MAX_SPLITS)
     assert device_splits(8, 8, 4, 16, sm_count=74) == 2
+
+
+def test_large_batches_split_by_context_as_measured():
+    """Whole decode steps of the 8B shape (8 kv heads of 128) were timed at 36 to 112 sequences with 1 to 8 splits:
+    at contexts of 1,024 the unsplit kernel won everywhere; at 4,096 splits won where the last wave of CTAs is short."""
+    for batch in (36, 40, 48, 56, 72, 80, 96, 112, 128):
+        assert decode_splits(batch, 8, 4, 16, context=1024) == 1
+        assert decode_splits(batch, 8, 4, 16, context=256) == 1
+    fastest = {36: 1, 40: 3, 48: 2, 72: 1, 80: 2, 96: 1, 112: 2}
+    for batch, splits in fastest.items():
+        assert decode_splits(batch, 8, 4, 16, context=4096) == splits
+        assert decode_splits(batch, 8, 4, 16) == splits                  # no context given: 4,096
+    # long contexts: the fixed cost of a split vanishes, a short last wave is always worth splitting
+    assert decode_splits(40, 8, 4, 16, context=32768) > 1
+    assert decode_splits(74, 8, 4, 16, context=32768) == 1               # 592 CTAs: two full waves
