@@ -367,8 +367,8 @@ def library_arm_prefill(args):
 
 TIMELINE_KERNELS = {2: "sum of K parts", 3: "decode attention", 4: "add+norm (cluster)", 5: "few-rows product (mma.sync)",
                     6: "add+norm (one CTA a row)", 7: "merge of key splits", 10: "few-rows product", 11: "few-rows product, K parts",
-                    12: "few-rows gate/up + SwiGLU", 13: "few-rows product (pairs)", 14: "few-rows product (pairs), K parts",
-                    15: "few-rows gate/up + SwiGLU (pairs)"}
+                    12: "few-rows gate/up + SwiGLU", 20: "many-rows product (pairs)", 21: "many-rows product (pairs), K parts",
+                    22: "many-rows gate/up + SwiGLU (pairs)", 23: "many-rows q,k,v + norm + rotation (pairs)"}
 
 
 def run_timeline(args):

@@ -583,6 +583,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     // (boxes of 128 rows x 64 columns, clipped at the matrix edges) instead of 16-byte stores from every thread.
     // splits > 1 (32-bit output only): the K range is cut into `splits` parts, each (tile, part) is a unit of work of its
     // own and writes its partial product split_stride elements after the part before; the caller adds the parts in order.
+    IMP_TL_BEGIN(20 + EPI)
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* out_stage = tiles + TC2_RING_BYTES;
@@ -623,6 +624,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
     // Up to here nothing read or wrote what an earlier kernel of the stream may still be working on.
     pdl_wait();
+    IMP_TL_WAITED()
     pdl_launch_dependents();
 
     if (warp == 0) {
@@ -786,6 +788,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TCP_TMEM_COLS)
                      : "memory");
     }
+    IMP_TL_END()
 }
 
 // ------------------------------------------------------- few rows: weights on the M side
@@ -806,13 +809,20 @@ constexpr int TCS_W_BYTES = 128 * TC_BK * 2;   // 16 KiB
 static uint32_t g_tcs_wait_limit = TC_WAIT_LIMIT;
 static int g_tcs_skip_kb = -1;
 
-// Ring depth.  Up to 32 tokens: five stages of 20 KiB; up to 64: four of 24 KiB; both so that two CTAs share an SM
-// (and its memory pipes).  More tokens: six stages of 32 KiB, one CTA per SM.  (Five stages measured 0.7 % faster
-// than four on the whole decode step at 8 to 32 rows; six would leave room for one CTA only.)
+// Ring depth.  Up to 32 tokens: five stages of 20 KiB; up to 64: four of 24 KiB; more: three of 32 KiB; all so that
+// two CTAs share an SM (and its memory pipes).  (Five stages measured 0.7 % faster than four on the whole decode step
+// at 8 to 32 rows; six would leave room for one CTA only.  At 65 to 128 tokens six stages and one CTA an SM put gate/up
+// of the 8B shape in two waves of 128-row tiles: 64 to 73 us; three stages and 256 resident tiles of 96 rows: 45 to 51,
+// whole decode steps at batch 128 10.47 -> 9.95 ms.  The same product on CTA pairs (cta_group::2, each CTA loading
+// half of the activation tile) gained nothing beyond that, and with two CTAs an SM its paired tensor-memory
+// allocations, each holding its SM's permit while waiting for its partner, hung a step once: it was taken out.)
 #ifndef IMP_TCS_STAGES32
 #define IMP_TCS_STAGES32 5
 #endif
-template <int BN> constexpr int tcs_stages() { return BN <= 32 ? IMP_TCS_STAGES32 : (BN <= 64 ? 4 : 6); }
+#ifndef IMP_TCS_STAGES128
+#define IMP_TCS_STAGES128 3
+#endif
+template <int BN> constexpr int tcs_stages() { return BN <= 32 ? IMP_TCS_STAGES32 : (BN <= 64 ? 4 : IMP_TCS_STAGES128); }
 template <int BN> constexpr int tcs_stage_bytes() { return TCS_W_BYTES + BN * TC_BK * 2; }
 template <int BN> constexpr int tcs_smem_bytes() { return tcs_stages<BN>() * tcs_stage_bytes<BN>() + 1024 + 256; }
 
@@ -962,168 +972,6 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
     if (warp == 1) {
         tc_fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
-    }
-    IMP_TL_END()
-}
-
-// ---- few rows on CTA pairs (33 to 128 activation rows) ---------------------------------------------------
-// From 33 rows on, a CTA of the kernel above reads nearly as many bytes of activations as of weights (64 rows: 8 KiB beside
-// 12 to 16 KiB a K block; 128 rows: 16 KiB), all CTAs the same ones through the L2, and the product is bound by what the
-// L2 can hand to the SMs, not by the memory (gate/up of the 8B shape: 42 us at 64 rows, 73 us at 128, against 35 at 8).
-// Here the two CTAs of a cluster take neighbouring tiles of weight rows and share one MMA (cta_group::2, M = 256: each
-// CTA's 128 accumulator lanes are its own weight rows, all BN tokens wide); each loads its own weight rows and HALF of
-// the activation tile, which the MMA reads from both.  Stages of 16 KiB + BN / 2 rows of activations, two CTAs an SM.
-// Barriers as in gemm_tc_pair_kernel: `full` lives in the even CTA and counts both CTAs' copies, `empty` and the
-// accumulator barrier exist in both and get their arrivals from multicast commits.
-template <int BN> constexpr int tcsp_stages() { return BN <= 64 ? 5 : 4; }
-template <int BN> constexpr int tcsp_stage_bytes() { return TCS_W_BYTES + (BN / 2) * TC_BK * 2; }
-template <int BN> constexpr int tcsp_smem_bytes() { return tcsp_stages<BN>() * tcsp_stage_bytes<BN>() + 1024 + 256; }
-
-template <int BN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
-    gemm_tc_swap_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                             void* __restrict__ Cv, int64_t ldc, int64_t split_stride, int M, int N, int K, int kb_per_split,
-                             int tile_rows, int* status) {
-    constexpr int STAGES = tcsp_stages<BN>();
-    constexpr int STAGE = tcsp_stage_bytes<BN>();
-    IMP_TL_BEGIN(13 + EPI)
-    extern __shared__ unsigned char tc_smem_raw[];
-    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_rank();                    // == blockIdx.x & 1
-    const int n0 = blockIdx.x * tile_rows;                   // this CTA's weight rows (may lie past N in the last pair)
-    const uint32_t stage_tx = (uint32_t)(tile_rows + BN / 2) * (TC_BK * 2);   // bytes this CTA's two boxes bring
-    const int total_kb = (K + TC_BK - 1) / TC_BK;
-    const int kb_lo = blockIdx.z * kb_per_split;
-    const int kb_hi = min(total_kb, kb_lo + kb_per_split);
-    const int k_blocks = max(kb_hi - kb_lo, 0);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum_bar = smem_u32(bars + 2 * STAGES);
-
-    // Nothing before pdl_wait() reads or writes what an earlier kernel of the stream may still be working on.
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
-        }
-        mbar_init(accum_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {   // the same warp of both CTAs, the same slot offset
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();        // the partner's barriers are initialised before anything can arrive on them
-    tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0 && lane == 0) {
-        // ---------------------------------------------------- producer (one per CTA, for its own boxes)
-        int issued = 0;
-        bool ok = true;
-        const int early = k_blocks < STAGES ? k_blocks : STAGES;
-        for (int i = 0; i < early; ++i) {     // weights do not depend on the kernel before this one
-            if (rank == 0) mbar_expect_tx(full0 + 8 * i, 2 * stage_tx);            // both CTAs' copies
-            tma_load_2d_pair(smem_u32(tiles + i * STAGE), &map_w, (kb_lo + i) * TC_BK, n0, cluster_map(full0 + 8 * i, 0));
-        }
-        pdl_wait();
-        IMP_TL_WAITED()
-        for (int i = 0; i < early; ++i)
-            tma_load_2d_pair(smem_u32(tiles + i * STAGE) + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, (int)rank * (BN / 2),
-                             cluster_map(full0 + 8 * i, 0));
-        issued = early;
-        for (int i = early; i < k_blocks; ++i) {
-            const int s = i % STAGES;
-            ok = mbar_wait(empty0 + 8 * s, ((uint32_t)(i / STAGES) & 1u) ^ 1u, status);
-            if (!ok) break;
-            const uint32_t w_dst = smem_u32(tiles + s * STAGE), full_even = cluster_map(full0 + 8 * s, 0);
-            if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * stage_tx);
-            tma_load_2d_pair(w_dst, &map_w, (kb_lo + i) * TC_BK, n0, full_even);
-            tma_load_2d_pair(w_dst + TCS_W_BYTES, &map_x, (kb_lo + i) * TC_BK, (int)rank * (BN / 2), full_even);
-            issued = i + 1;
-        }
-        if (!ok && rank == 0)   // a bounded chance for the copies still in flight to land
-            for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
-                mbar_wait(full0 + 8 * (i % STAGES), (uint32_t)(i / STAGES) & 1u, nullptr);
-    } else {
-        pdl_wait();
-    }
-    if (warp == 1 && lane == 0 && rank == 0) {
-        // ---------------------------------------------------------------- MMA issuer (even CTA)
-        const uint32_t idesc = tc_instr_desc(256, BN);
-        bool ok = true;
-        for (int i = 0; i < k_blocks && ok; ++i) {
-            const int s = i % STAGES;
-            ok = mbar_wait(full0 + 8 * s, (uint32_t)(i / STAGES) & 1u, status);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t w_addr = smem_u32(tiles + s * STAGE), x_addr = w_addr + TCS_W_BYTES;
-#pragma unroll
-            for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
-                tc_mma_pair(tmem_base, tc_smem_desc(w_addr + k * TC_UMMA_K * 2), tc_smem_desc(x_addr + k * TC_UMMA_K * 2), idesc,
-                            (i > 0 || k > 0) ? 1u : 0u);
-            tc_commit_pair(empty0 + 8 * s);
-        }
-        tc_commit_pair(accum_bar);     // also after a wait that gave up: the epilogues of both CTAs are released
-    }
-    __syncwarp();
-
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, status));
-    tc_fence_after_sync();
-    if (acc_ok) {
-        const int r = warp * 32 + lane;             // accumulator lane = weight row of the tile
-        const int col = n0 + r;                     // output column
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-            float v[32];
-            if (k_blocks > 0) {
-                tc_ld32(lane_base + (uint32_t)(c * 32), v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;   // an empty K range contributes nothing
-            }
-            if (EPI == TC_OUT_SWIGLU_BF16) {
-                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
-                const bool is_gate = (r & 8) == 0;
-                const int ocol = (col >> 4) * 8 + (r & 7);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float up = __shfl_xor_sync(0xffffffffu, v[i], 8);   // lane r + 8 holds the matching up row
-                    const int tok = c * 32 + i;
-                    if (is_gate && tok < M && col + 8 < N && r < tile_rows)
-                        base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
-                }
-            } else if (col < N && r < tile_rows) {
-                if (EPI == TC_OUT_F32) {
-                    float* base = reinterpret_cast<float*>(Cv) + (int64_t)blockIdx.z * split_stride;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int tok = c * 32 + i;
-                        if (tok < M) base[(int64_t)tok * ldc + col] = v[i];
-                    }
-                } else {
-                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(Cv);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int tok = c * 32 + i;
-                        if (tok < M) base[(int64_t)tok * ldc + col] = __float2bfloat16_rn(v[i]);
-                    }
-                }
-            }
-        }
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();        // neither CTA leaves while the other may still read its memory or signal its barriers
-    if (warp == 1) {
-        tc_fence_after_sync();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
     }
     IMP_TL_END()
 }
@@ -1345,14 +1193,8 @@ IMP_API int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda
 #define TCS_MIN_KB_PER_SPLIT 6     // blocks of K a split has at least
 #endif
 static int tcs_sms() { return imp_sm_count(); }
-// From 65 rows on the few-rows product runs on CTA pairs (gemm_tc_swap_pair_kernel); IMP_B200_TCS_PAIR=0 keeps single CTAs.
-static bool tcs_pair_enabled() {
-    static int v = -1;
-    if (v < 0) { const char* e = getenv("IMP_B200_TCS_PAIR"); v = e ? atoi(e) : 1; }
-    return v != 0;
-}
-// CTAs resident at once: two an SM up to 64 rows, and on CTA pairs (whose stages are smaller) up to 128.
-static int tcs_slots(int M) { return (M <= 64 || tcs_pair_enabled()) ? 2 * tcs_sms() : tcs_sms(); }
+// CTAs resident at once: two an SM (the 128-token variant by its three stages of 32 KiB).
+static int tcs_slots(int M) { (void)M; return 2 * tcs_sms(); }
 
 // Weight rows of a CTA's tile when K is not split.  All CTAs are resident at once (two per SM up to 64 tokens),
 // handed out round robin, so the SM with the most CTAs sets the time: 192 tiles of 128 rows put two tiles on 44 SMs
@@ -1409,24 +1251,6 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
     return 0;
 }
 
-template <int BN, int EPI>
-static int launch_tcsp(void* C, int64_t ldc, int64_t split_stride, const CUtensorMap& mw, const CUtensorMap& mx, int M, int N,
-                       int K, int splits, int kb_per_split, int tile_rows, int* status, cudaStream_t s) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             tcsp_smem_bytes<BN>());
-        if (e != cudaSuccess) { imp_set_error("gemm_tc_swap (pairs): %s", cudaGetErrorString(e)); return (int)e; }
-        attr_set = true;
-    }
-    const int tiles = (N + tile_rows - 1) / tile_rows;
-    dim3 grid(2 * ((tiles + 1) / 2), 1, splits);          // whole pairs: the last CTA of an odd count works on rows past N
-    cudaError_t e = imp_launch(gemm_tc_swap_pair_kernel<BN, EPI>, grid, dim3(128), (size_t)tcsp_smem_bytes<BN>(), s, mw, mx, C, ldc,
-                               split_stride, M, N, K, kb_per_split, tile_rows, status);
-    if (e != cudaSuccess) { imp_set_error("gemm_tc_swap (pairs): %s", cudaGetErrorString(e)); return (int)e; }
-    return 0;
-}
-
 // C = A[M,K] * W[N,K]^T for 1 <= M <= 128 with the weights on the M side of the MMA.
 // epilogue as for imp_gemm_bf16_tc.  `scratch` must hold imp_gemm_bf16_tc_swap_scratch_floats() floats.
 static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
@@ -1446,19 +1270,14 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
     if (bn32 < 0) { const char* e = getenv("IMP_B200_TCS_BN32"); bn32 = e ? atoi(e) : 1; }
     const int BN = (M <= 32 && bn32) ? 32 : (M <= 64 ? 64 : 128);
     const int tile_rows = tcs_tile_rows(M, N, splits);
-    // Pairs from 65 rows on (gate/up of the 8B shape at 128 rows: 51 us against 73); at 33 to 64 rows they measured no
-    // faster than single CTAs (42 us either way: what the halved activation traffic gains, waiting for two CTAs' copies loses).
-    const bool pair = BN == 128 && tcs_pair_enabled();       // each CTA of a pair loads half of the activation tile
     CUtensorMap mw, mx;
     if (int rc = make_map(&mw, W, N, K, ldw, tile_rows)) return rc;
-    if (int rc = make_map(&mx, A, M, K, lda, pair ? BN / 2 : BN)) return rc;
+    if (int rc = make_map(&mx, A, M, K, lda, BN)) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = 0;
     if (splits > 1) {
         const int64_t split_stride = (int64_t)M * N;
-        rc = pair ? (BN == 64 ? launch_tcsp<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
-                              : launch_tcsp<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s))
-           : BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
+        rc = BN == 32 ? launch_tcs<32, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
            : BN == 64 ? launch_tcs<64, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s)
                       : launch_tcs<128, TC_OUT_F32>(scratch, N, split_stride, mw, mx, M, N, K, splits, kb_per_split, tile_rows, status, s);
         if (rc) return rc;
@@ -1474,15 +1293,6 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
             e = imp_launch(gemm_tc_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (__nv_bfloat16*)C, ldc,
                            (const float*)scratch, split_stride, M, N, splits);
         if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
-    } else if (pair) {
-        rc = epilogue == TC_OUT_BF16
-                 ? (BN == 64 ? launch_tcsp<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-                             : launch_tcsp<128, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s))
-             : epilogue == TC_OUT_F32
-                 ? (BN == 64 ? launch_tcsp<64, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-                             : launch_tcsp<128, TC_OUT_F32>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s))
-                 : (BN == 64 ? launch_tcsp<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-                             : launch_tcsp<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s));
     } else if (epilogue == TC_OUT_BF16) {
         rc = BN == 32 ? launch_tcs<32, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
            : BN == 64 ? launch_tcs<64, TC_OUT_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)

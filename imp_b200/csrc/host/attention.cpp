@@ -197,6 +197,8 @@ int decode_splits(int n_tokens, int n_kv_heads, int group, int page_size, int sm
         // the largest power of two that keeps every CTA resident at once (measured: 16 splits beat 18 at two
         // sequences, 8 beat 9 at four, although the latter fill more slots)
         int s = std::max(1, std::min(DECODE_MAX_SPLITS, slots / base));
+        // a split of fewer than 128 keys (two stages of the ring) is all start and end: short contexts get fewer
+        if (context > 0) s = std::max(1, std::min(s, context / 128));
         int p = 1;
         while (p * 2 <= s) p *= 2;
         return p;

@@ -57,3 +57,8 @@ def test_large_batches_split_by_context_as_measured():
     # long contexts: the fixed cost of a split vanishes, a short last wave is always worth splitting
     assert decode_splits(40, 8, 4, 16, context=32768) > 1
     assert decode_splits(74, 8, 4, 16, context=32768) == 1               # 592 CTAs: two full waves
+
+
+def test_short_contexts_get_fewer_splits_at_small_batches():
+    assert decode_splits(1, 8, 4, 16, context=256) == 2 and decode_splits(1, 8, 4, 16, context=1024) == 8
+    assert decode_splits(1, 8, 4, 16, context=4096) == 32 and decode_splits(8, 8, 4, 16, context=128) == 1
