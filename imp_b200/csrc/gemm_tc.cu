@@ -1145,11 +1145,14 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
 #ifndef TC2_MAX_SPLITS
 #define TC2_MAX_SPLITS 4
 #endif
+#ifndef TC2_SPLIT_MIN_ROWS
+#define TC2_SPLIT_MIN_ROWS 129     // from where CTA pairs take the product (decode at 160 sequences: 12.87 -> 11.76 ms a step
+#endif                             // once the down projection's 16 tiles are cut in four)
 IMP_API int imp_gemm_bf16_tc_splits(int M, int N, int K) {
     static int enabled = -1;       // IMP_B200_TC_SPLIT=0: never
     if (enabled < 0) { const char* e = getenv("IMP_B200_TC_SPLIT"); enabled = e ? atoi(e) : 1; }
     const char* pair_env = getenv("IMP_B200_TC_PAIR");
-    if (!enabled || M < 256 || getenv("IMP_B200_TC_SIMPLE") || (pair_env && atoi(pair_env) == 0)) return 1;
+    if (!enabled || M < TC2_SPLIT_MIN_ROWS || getenv("IMP_B200_TC_SIMPLE") || (pair_env && atoi(pair_env) == 0)) return 1;
     const int tiles2 = ((M + TC2_BM - 1) / TC2_BM) * ((N + TC2_BN - 1) / TC2_BN);
     const int pairs = imp_sm_count() / 2;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;

@@ -280,7 +280,7 @@ def test_gemm_bf16_tcgen05_fused_swiglu(K, M, F, K_):
     close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
 
 
-@pytest.mark.parametrize("M,N,K_", [(512, 4096, 12288), (300, 1024, 6144), (256, 520, 9224), (1000, 2048, 6208)])
+@pytest.mark.parametrize("M,N,K_", [(512, 4096, 12288), (300, 1024, 6144), (256, 520, 9224), (1000, 2048, 6208), (160, 2048, 6208)])
 @pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
 def test_linear_with_the_k_range_in_parts(K, M, N, K_, odtype):
     """A portion of a prompt times a weight with few rows and a long K: fewer 256 x 256 tiles than half the CTA pairs,
