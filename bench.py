@@ -23,7 +23,7 @@ the 126 MB L2, so no explicit L2 flush is needed between timed iterations ("inpu
 Other runs, each printing its own JSON line:
     python bench.py --only decode [--batch B] [--context C] [--page P] [--layers N] [--no-graphs]
     python bench.py --only prefill [--tokens T] [--chunk C] [--layers N]
-    IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C]   (a table, not JSON)
+    IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C] [--workload 0.6b|14b]   (a table, not JSON)
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
@@ -385,8 +385,8 @@ def run_timeline(args):
     if "-DIMP_TIMELINE" not in os.environ.get("IMP_B200_NVCC_FLAGS", ""):
         print("bench.py --only timeline needs IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE (a diagnostic build of the library)")
         return 2
-    cfgd = dict(MODEL)
-    n_layers = args.layers or MODEL["num_hidden_layers"]
+    cfgd = dict({"0.6b": MODEL_06B, "14b": MODEL_14B}.get(args.workload, MODEL))
+    n_layers = args.layers or cfgd["num_hidden_layers"]
     cfgd["num_hidden_layers"] = n_layers
     B, ctx = args.batch, args.context or CONTEXT
     eng, _ = make_engine(cfgd, args, B, ctx)
@@ -706,10 +706,10 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload:
-        return run_workload(args)
     if args.only == "timeline":
         return run_timeline(args)
+    if args.workload:
+        return run_workload(args)
     return run_ours(args)
 
 

@@ -15,7 +15,6 @@ static int stream_m_max() {
     static const int v = [] { const std::string e = env_string("IMP_B200_STREAM_ROWS", ""); return e.empty() ? 1 : std::atoi(e.c_str()); }();
     return v;
 }
-#define STREAM_M_MAX stream_m_max()
 constexpr int TC_SWAP_MAX_M = 128;  // rows up to which the weights take the M side of the tcgen05 product
 
 // "tcgen05": this library's TMA + tcgen05 kernels.  "cublas": the library GEMM for products of more than 16
@@ -197,7 +196,7 @@ Branch linear(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w, bool ma
     if (M <= SMALL_M_MAX) {
         // The weight-streaming kernel, except where the swap-AB tcgen05 kernel measured faster: from 8 rows up,
         // and at any row count for products with a long contraction and few output columns (K split over CTAs).
-        if (!lib && (M > STREAM_M_MAX || (K >= 2 * N && N >= 1024))) {
+        if (!lib && (M > stream_m_max() || (K >= 2 * N && N >= 1024))) {
             if (defer && gemm_tc_swap_partials(rt, out, x, w, &b)) return b;
             if (gemm_tc_swap(rt, out, x, w)) return Branch::of(out);
         }
@@ -222,7 +221,7 @@ void linear_swiglu(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w) {
     if (M == 0) return;
     const bool bf16 = x.dtype == BF16 && w.dtype == BF16 && out.dtype == BF16;
     const bool lib = use_library_gemm();
-    if (bf16 && M > STREAM_M_MAX && M <= SMALL_M_MAX && !lib && gemm_tc_swap(rt, out, x, w, TC_OUT_SWIGLU)) return;
+    if (bf16 && M > stream_m_max() && M <= SMALL_M_MAX && !lib && gemm_tc_swap(rt, out, x, w, TC_OUT_SWIGLU)) return;
     if (bf16 && M <= SMALL_M_MAX) {
         const int rc = imp_gemm_bf16_stream_swiglu(out.data, out.stride0, x.data, x.stride0, w.data, w.stride0, (int)M, (int)(2 * F),
                                                    (int)cols(x), rt.stream);
