@@ -170,8 +170,12 @@ void set_variant_resolver(VariantResolver fn) {
     g_resolver = fn;
 }
 
+// All sequences in tiles of 32 tokens; those with 64 tokens and more in tiles of 128; the others in tiles of 32; and the
+// first and the third again without the sequences that bring a single token (those go to the decode kernel when they
+// stand at the head of a mixed batch).
 std::vector<TilingSpec> attention_tilings() {
-    return {TilingSpec{TILE, 0, 0}, TilingSpec{WIDE_TILE, WIDE_MIN, 0}, TilingSpec{TILE, 0, WIDE_MIN}};
+    return {TilingSpec{TILE, 0, 0}, TilingSpec{WIDE_TILE, WIDE_MIN, 0}, TilingSpec{TILE, 0, WIDE_MIN},
+            TilingSpec{TILE, 2, 0}, TilingSpec{TILE, 2, WIDE_MIN}};
 }
 
 // The bulk-copy kernel (page sizes that are multiples of 16) keeps two CTAs resident per SM: with fewer
@@ -299,10 +303,21 @@ void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeome
         decode_attention(st, out, q, g, cache);
         return;
     }
-    need(tiling_ids.size() == 3, "attention: the step holds no tilings for this mixer");
-    const Tiles& all = st.tiles.at((size_t)tiling_ids[0]);
+    need(tiling_ids.size() == 5, "attention: the step holds no tilings for this mixer");
+    // Sequences that decode beside the portions of prompts: as a tile of one row each, a CTA walks all their keys alone
+    // (8 decoding sequences at context 4,096 beside a 512-token portion: 19.2 ms a step against 4.0 + 9.1 for the two
+    // alone).  The scheduler puts them first, one token each, so they are the batch's first rows: the split-key decode
+    // kernel takes those rows, the tiled kernels the rest.  (IMP_B200_ATTN_MIXED_DECODE=0: tiles of one row as before.)
+    static const bool split_singles = env_flag("IMP_B200_ATTN_MIXED_DECODE", true);
+    int n_single = 0;
+    while (n_single < st.B() && st.q_lens[(size_t)n_single] == 1) ++n_single;
+    bool singles = split_singles && n_single > 0;
+    for (int i = n_single; singles && i < st.B(); ++i)
+        if (st.q_lens[(size_t)i] == 1) singles = false;      // single tokens further on: no leading block, the tiled kernels take all
+    if (singles) decode_attention(st, first_rows(out, n_single), first_rows(q, n_single), g, cache);
+    const Tiles& all = st.tiles.at((size_t)tiling_ids[singles ? 3 : 0]);
     const Tiles& wide = st.tiles.at((size_t)tiling_ids[1]);
-    const Tiles& rest = st.tiles.at((size_t)tiling_ids[2]);
+    const Tiles& rest = st.tiles.at((size_t)tiling_ids[singles ? 4 : 2]);
     if (wide.count && prefill_tc_supported(q, out, g, c)) {
         TcVariant& lib = tc_variant(g.dh);
         check_variant(rt,
@@ -313,7 +328,7 @@ void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeome
         if (rest.count) prefill_attention(st, out, q, g, cache, rest);
         return;
     }
-    prefill_attention(st, out, q, g, cache, all);
+    if (all.count) prefill_attention(st, out, q, g, cache, all);
 }
 
 bool linear_qkv_rope(Step& st, Tensor q_out, const Tensor& x, const Tensor& w, const AttentionGeometry& g, const LayerCache& cache,

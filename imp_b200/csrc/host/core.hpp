@@ -87,6 +87,12 @@ inline Tensor col_slice(const Tensor& t, int64_t c0, int64_t n) {
     s.shape[1] = n;
     return s;
 }
+// Rows [0, n) of a tensor.
+inline Tensor first_rows(const Tensor& t, int64_t n) {
+    Tensor s = t;
+    s.shape[0] = n;
+    return s;
+}
 std::string shape_string(const Tensor& t);
 
 // ------------------------------------------------------------------------------ device memory
