@@ -1333,7 +1333,15 @@ static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_s
         }
         if (placeable[n_splits] > 0) { cluster_merge = 1; n_attr = 1; }
     }
-    if (imp_pdl_enabled()) {
+    // The call without the fused rotary work (decoding sequences beside prompt portions) is launched as an ordinary
+    // dependent of the kernels before it.  With the programmatic attribute, 2 of 8 runs of a workload of such steps (8
+    // sequences decoding beside 2,048-token portions, 14B shape) ended with a position error from this kernel's own
+    // check before its wait; 12 of 12 ran clean without it (and 10 of 10 with the attribute off everywhere).  What it
+    // read too early was not found; the start that the attribute buys is small beside a prompt portion's work.
+    // IMP_B200_ATTN_PLAIN_SERIAL=0 brings the attribute back for study.
+    static int serial_plain = -1;
+    if (serial_plain < 0) { const char* e = getenv("IMP_B200_ATTN_PLAIN_SERIAL"); serial_plain = e ? atoi(e) : 1; }
+    if (imp_pdl_enabled() && !(serial_plain && fz.qkv == nullptr)) {
         attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
         ++n_attr;
