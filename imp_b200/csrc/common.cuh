@@ -138,6 +138,12 @@ inline cudaError_t imp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// -DIMP_TAG_STATUS (a diagnostic build): a reported code carries 100 x the tag of the check that raised it.
+#ifdef IMP_TAG_STATUS
+#define IMP_TAGGED(code, tag) ((code) + 100 * (tag))
+#else
+#define IMP_TAGGED(code, tag) (code)
+#endif
 __device__ __forceinline__ void imp_report(int* status, int code) {
     if (status) atomicCAS(status, 0, code);
 }

@@ -404,7 +404,7 @@ __device__ __forceinline__ void qkv_rope_row(const QkvRopeArgs& a, uint32_t tadd
             imp_report(status, IMP_BAD_SEQUENCE);
             live = false;
         } else if (pos < 0 || pos >= a.max_pos || pos / a.page_size >= a.bt_stride) {
-            imp_report(status, IMP_BAD_POSITION);
+            imp_report(status, IMP_TAGGED(IMP_BAD_POSITION, 5));
             live = false;
         } else {
             const int slot_page = pos / a.page_size;

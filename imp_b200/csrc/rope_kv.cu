@@ -54,7 +54,7 @@ __global__ void qk_norm_rope_kv_kernel(
             }
             const int slot_page = pos / page_size;
             if (pos < 0 || slot_page >= bt_stride) {
-                if (lane == 0) imp_report(status, IMP_BAD_POSITION);
+                if (lane == 0) imp_report(status, IMP_TAGGED(IMP_BAD_POSITION, 6));
                 return;
             }
             const int page = block_table[(int64_t)seq * bt_stride + slot_page];
@@ -85,7 +85,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const int half = rot_dim >> 1;
     const bool rotate = cos_tab != nullptr && half > 0;
     if (rotate && (pos < 0 || pos >= max_pos)) {
-        if (lane == 0) imp_report(status, IMP_BAD_POSITION);
+        if (lane == 0) imp_report(status, IMP_TAGGED(IMP_BAD_POSITION, 6));
         return;
     }
     TA* out = is_q ? x : (dst ? dst : x);
@@ -151,7 +151,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(
             }
             const int slot_page = pos / page_size;
             if (pos < 0 || slot_page >= bt_stride) {
-                if (lane == 0) imp_report(status, IMP_BAD_POSITION);
+                if (lane == 0) imp_report(status, IMP_TAGGED(IMP_BAD_POSITION, 6));
                 return;
             }
             const int page = block_table[(int64_t)seq * bt_stride + slot_page];
@@ -170,7 +170,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     const int half = rot_dim >> 1;
     const bool rotate = cos_tab != nullptr && half > 0;
     if (rotate && (pos < 0 || pos >= max_pos)) {
-        if (lane == 0) imp_report(status, IMP_BAD_POSITION);
+        if (lane == 0) imp_report(status, IMP_TAGGED(IMP_BAD_POSITION, 6));
         return;
     }
     // pairs j = lane, lane + 32 of each half (half <= 128 elements = 64 pairs)

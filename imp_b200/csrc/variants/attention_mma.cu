@@ -514,7 +514,7 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
     const int seq = seq_of_token[tok];
     const int pos = positions[tok];
     if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride) {
-        if (threadIdx.x == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        if (threadIdx.x == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_TAGGED(IMP_BAD_SEQUENCE, 1) : IMP_TAGGED(IMP_BAD_POSITION, 1));
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;
@@ -1009,7 +1009,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
     const int seq = seq_of_token[tok];
     const int pos = positions[tok];
     if (seq < 0 || seq >= n_seqs || pos < 0 || pos / P >= bt_stride || (fz.qkv && pos >= fz.max_pos)) {
-        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_TAGGED(IMP_BAD_SEQUENCE, 2) : IMP_TAGGED(IMP_BAD_POSITION, 2));
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;
@@ -1334,11 +1334,12 @@ static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_s
         if (placeable[n_splits] > 0) { cluster_merge = 1; n_attr = 1; }
     }
     // The call without the fused rotary work (decoding sequences beside prompt portions) is launched as an ordinary
-    // dependent of the kernels before it.  With the programmatic attribute, 2 of 8 runs of a workload of such steps (8
-    // sequences decoding beside 2,048-token portions, 14B shape) ended with a position error from this kernel's own
-    // check before its wait; 12 of 12 ran clean without it (and 10 of 10 with the attribute off everywhere).  What it
-    // read too early was not found; the start that the attribute buys is small beside a prompt portion's work.
-    // IMP_B200_ATTN_PLAIN_SERIAL=0 brings the attribute back for study.
+    // dependent of the kernels before it.  With the programmatic attribute, 2 of the first 8 runs of a workload of such
+    // steps (8 sequences decoding beside 2,048-token portions, 14B shape) ended with a position error reported by one of
+    // the step's kernels; 23 runs without the attribute here, 10 without it anywhere and 12 without this path ran clean,
+    // but so did 57 later runs WITH it (a build that tags the reporting check saw nothing to tag), so the attribute is
+    // not shown to be the cause.  It stays off here because the start it buys is small beside a prompt portion's work.
+    // IMP_B200_ATTN_PLAIN_SERIAL=0 brings it back; -DIMP_TAG_STATUS makes a reported code name its check.
     static int serial_plain = -1;
     if (serial_plain < 0) { const char* e = getenv("IMP_B200_ATTN_PLAIN_SERIAL"); serial_plain = e ? atoi(e) : 1; }
     if (imp_pdl_enabled() && !(serial_plain && fz.qkv == nullptr)) {
@@ -1485,7 +1486,7 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
     const int pos0 = positions[tok0];
     const int pos_last = pos0 + n_rows - 1;
     if (seq < 0 || seq >= n_seqs || pos0 < 0 || pos_last / P >= bt_stride || n_rows < 1 || n_rows > 32) {
-        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        if (tid == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_TAGGED(IMP_BAD_SEQUENCE, 3) : IMP_TAGGED(IMP_BAD_POSITION, 3));
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;

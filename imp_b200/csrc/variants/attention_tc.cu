@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         FaItem it;
         for (int pass = 0; ok && load_item(pass, it); ++pass) {
             if (!it.geometry_ok && lane == 0)
-                imp_report(status, it.seq < 0 || it.seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+                imp_report(status, it.seq < 0 || it.seq >= n_seqs ? IMP_TAGGED(IMP_BAD_SEQUENCE, 4) : IMP_TAGGED(IMP_BAD_POSITION, 4));
             if (it.n_kt <= 0) continue;
             const int* bt = block_table + (int64_t)it.seq * bt_stride;
             for (int i = 0; i < it.n_kt && ok; ++i) {
