@@ -176,10 +176,23 @@ int Scheduler::largest_fit(const Request* r, int n, int free) const {
     return std::max(fit, 0);
 }
 
+// A portion that does not end its prompt is cut so that the step's rows so far plus the portion are a multiple of 256:
+// the products of 129 rows and more work in tiles of 256 rows, and a last tile that holds the 64 rows of the decoding
+// sequences beside a 512-token portion costs as much as a full one (576 rows: three tiles; 512: two).  Only portions
+// of 256 tokens and more, never below half of what was asked.  IMP_B200_SCHED_ALIGN=0 keeps portions as asked.
+static int aligned_portion(int n, int remaining, int rows_so_far) {
+    static const bool on = env_flag("IMP_B200_SCHED_ALIGN", true);
+    constexpr int TILE_ROWS = 256;
+    if (!on || n >= remaining || n < TILE_ROWS) return n;
+    const int whole = (rows_so_far + n) / TILE_ROWS * TILE_ROWS - rows_so_far;
+    return (whole >= n / 2 && whole > 0) ? whole : n;
+}
+
 int Scheduler::serve_running(Request* r, StepPlan& plan, int budget, int chunk) {
     const int remaining = r->n_total() - r->n_computed;
     const bool decoding = remaining == 1;
     int n = decoding ? 1 : std::min({remaining, chunk, budget});
+    if (!decoding) n = aligned_portion(n, remaining, max_batch_tokens - budget);
     while (true) {
         const int free = free_after(plan);
         if (pages_needed(r, r->n_computed + n) <= free) break;
@@ -234,6 +247,7 @@ StepPlan Scheduler::schedule() {
             if (!cache_->has(e.request->rid)) ++new_in_plan;
         if (cache_->slots().n_free() - new_in_plan <= 0) break;
         int n = std::min({r->n_total(), chunk, budget});
+        n = aligned_portion(n, r->n_total(), max_batch_tokens - budget);
         const int free = free_after(plan);
         // Keep one page in hand per running request so that decoding can go on.
         const int usable = running.empty() ? free : free - (int)running.size();

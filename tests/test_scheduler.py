@@ -213,3 +213,34 @@ def test_random_workloads_finish_and_leave_the_pool_whole():
             assert steps < 5000, "scheduler does not make progress"
         assert all(r.status == RequestStatus.FINISHED for r in reqs)
         assert cache.free_pages() == num_pages and cache.slots.n_free == cache.slots.num_pages
+
+
+def test_long_portions_end_a_step_on_a_multiple_of_256_rows():
+    """The products of many rows work in tiles of 256 rows: a portion that does not end its prompt is shortened so that
+    the decoding sequences before it and the portion fill whole tiles (64 + 512 rows would be three tiles, 64 + 448 two)."""
+    cache, s = make(num_pages=4096, page=16, max_batch=80, budget=576, chunk=512, max_seq=8192)
+    for i in range(64):
+        s.add(req(f"d{i}", 3, 40))
+    log = []
+    run_step(cache, s, log=log)                         # the 64 short prompts, whole
+    assert len(log[0]) == 64
+    s.add(req("long", 3000, 2))
+    run_step(cache, s, log=log)
+    rows = log[1]
+    assert [e[2] for e in rows[:64]] == [1] * 64 and rows[64][0] == "long"
+    assert rows[64][2] == 448 and sum(e[2] for e in rows) == 512
+    run_step(cache, s, log=log)
+    assert log[2][64][1:3] == (448, 448)                # goes on where it stopped, again to a whole tile
+    # a portion that ends its prompt is never shortened, and short portions are left alone
+    cache2, s2 = make(num_pages=4096, page=16, max_batch=8, budget=600, chunk=512, max_seq=8192)
+    s2.add(req("a", 3, 40))
+    log2 = []
+    run_step(cache2, s2, log=log2)
+    s2.add(req("b", 500, 2))
+    run_step(cache2, s2, log=log2)
+    assert log2[1][1][2] == 500
+    cache3, s3 = make(num_pages=64, budget=8, chunk=6)
+    s3.add(req("c", 20, 2))
+    log3 = []
+    run_step(cache3, s3, log=log3)
+    assert log3[0][0][2] == 6
