@@ -23,6 +23,7 @@ the 126 MB L2, so no explicit L2 flush is needed between timed iterations ("inpu
 Other runs, each printing its own JSON line:
     python bench.py --only decode [--batch B] [--context C] [--page P] [--layers N] [--no-graphs]
     python bench.py --only prefill [--tokens T] [--chunk C] [--layers N]
+    python bench.py --only mixed [--batch B] [--chunk C] [--context X]     B sequences decoding beside a prompt's portions
     IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C] [--workload 0.6b|14b]   (a table, not JSON)
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
@@ -451,6 +452,47 @@ def run_timeline(args):
     return 0
 
 
+def run_mixed(args):
+    """Steps in which `--batch` sequences decode (contexts near `--context`) beside one portion of `--chunk` tokens of a
+    long prompt: the decode-only step, the mixed step, and the portion the scheduler actually cut (it ends a step on a
+    multiple of 256 rows).  One JSON line."""
+    from imp_b200 import Engine, EngineConfig, GenerateParams
+    B, C, ctx = args.batch, args.chunk or 512, args.context or 2048
+    cfgd = dict(MODEL)
+    cfgd["max_position_embeddings"] = 16384
+    n_layers = args.layers or MODEL["num_hidden_layers"]
+    cfgd["num_hidden_layers"] = n_layers
+    ecfg = EngineConfig(max_batch_size=B + 1, max_seq_len=16384, kv_block_size=args.page or PAGE,
+                        kv_cache_tokens=(B + 1) * (ctx + 600) + 16384, max_batch_tokens=B + C, prefill_chunk_size=C,
+                        compute_dtype="bfloat16", enable_cuda_graphs=not args.no_graphs)
+    eng = Engine.from_random(cfgd, ecfg, seed=0, std=0.02)
+    rng = random.Random(0)
+    V = cfgd["vocab_size"]
+    reqs = start_decoding(eng, rng, V, B, ctx, 400)
+    for _ in range(5):
+        eng.step()
+    eng.timer_start()
+    for _ in range(10):
+        eng.step()
+    decode_ms = eng.timer_stop() / 10
+    long_prompt = 14 * C
+    eng.submit(random_prompt(rng, V, long_prompt), GenerateParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    eng.step()
+    eng.step()
+    n = 8
+    before = eng.info()
+    eng.timer_start()
+    for _ in range(n):
+        eng.step()
+    mixed_ms = eng.timer_stop() / n
+    info = eng.info()
+    print(json.dumps({"only": "mixed", "layers": n_layers, "decoding": B, "context": ctx, "portion_asked": C,
+                      "decode_only_ms": round(decode_ms, 3), "mixed_ms": round(mixed_ms, 3),
+                      "launches_per_mixed_step": (info["launches"] - before["launches"]) / n,
+                      "fallback_calls": info["fallback_calls"]}))
+    return 0
+
+
 def run_ours(args):
     peaks, peak_src = read_peaks()
     cfgd = dict(MODEL)
@@ -687,7 +729,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
@@ -708,6 +750,8 @@ def main():
         args.warmup = 3
     if args.only == "timeline":
         return run_timeline(args)
+    if args.only == "mixed":
+        return run_mixed(args)
     if args.workload:
         return run_workload(args)
     return run_ours(args)
